@@ -1,0 +1,73 @@
+"""ctypes binding of ``libwarpy_b200.so`` (declared in ``include/warpy_b200.h``).
+
+This plays the role of the reference's TVM-FFI call (``warpy_kernels/utils/__init__.py:44-52``): the
+single place where Python hands raw device pointers to compiled kernels.  There is no fallback: if the
+library is missing the import of any kernel wrapper fails with an explicit error.
+"""
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libwarpy_b200.so")
+
+_i32, _i64, _ptr, _str = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_char_p
+
+WK_BF16, WK_F32 = 0, 1
+
+# name -> (restype, argtypes); must list every function the header declares
+SIGNATURES = {
+    "wk_query": (_i32, [_str]),
+    "wk_status": (_i32, []),
+    "wk_error_string": (_str, [_i32]),
+    "wk_quantize_mx": (_i32, [_ptr, _i32, _i64, _i64, _i64, _ptr, _ptr, _ptr]),
+    "wk_gemm_bf16": (_i32, [_ptr, _ptr, _ptr, _i32, _i32, _i32, _ptr]),
+}
+
+_lib = None
+
+
+def lib():
+    """Return the loaded library, loading it on first use.
+
+    Raises:
+        RuntimeError: If ``libwarpy_b200.so`` has not been built (run ``python -c "import __graft_entry__ as g;
+            g.build()"`` or ``make -C warpy_kernels_b200/csrc``). There is deliberately no CPU or PyTorch fallback.
+    """
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `make -C {os.path.join(_HERE, 'csrc')}`; "
+                "warpy_kernels has no fallback path"
+            )
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def stream_ptr(device=None):
+    """``cudaStream_t`` of torch's current stream on ``device`` as an integer."""
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def check(code, what):
+    """Turn a negative return code of the C ABI into a Python exception."""
+    if code == 0:
+        return
+    text = lib().wk_error_string(code).decode()
+    if code == -1:
+        raise ValueError(f"{what}: {text}")
+    raise RuntimeError(f"{what}: {text} (code {code})")
+
+
+def device_status():
+    """Synchronise the current device and raise if a kernel gave up on a bounded wait."""
+    code = lib().wk_status()
+    if code != 0:
+        raise RuntimeError(f"warpy_kernels device status {code}: {lib().wk_error_string(code).decode()}")

@@ -1,0 +1,233 @@
+// BF16 GEMM for sm_100a: out[M,N] = a[M,K] . b[N,K]^T, fp32 accumulation in tensor
+// memory, bf16 output.
+//
+// Persistent, warp-specialised CTA (one per SM), 128 x 256 output tile:
+//   warp 0      TMA producer: A (128 x 64) and B (256 x 64) bf16 tiles, 128-byte
+//               swizzle, into a 4-stage shared-memory ring (48 KiB per stage)
+//   warp 1      allocates 512 TMEM columns and issues tcgen05.mma kind::f16
+//               (M128 N256 K16, four per stage); two 256-column accumulators so the
+//               epilogue of tile i overlaps the main loop of tile i+1
+//   warps 2-5   epilogue: tcgen05.ld (32 lanes x 32 columns), fp32 -> bf16, 64-byte
+//               row segments straight to global memory
+// Tiles are visited in groups of `group_m` row blocks that sweep all column blocks
+// (the reference's L2-friendly order, warpy_kernels/utils/sched.py:8-16).
+//
+// Tensor-core bound: 2*M*N*K flops per launch.
+#include "common.cuh"
+#include "host_common.h"
+
+namespace wk {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+
+struct TileCoord {
+  int m_blk, n_blk;
+};
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int group_m) {
+  const int per_group = group_m * num_n;
+  const int g = tile / per_group;
+  const int first_m = g * group_m;
+  const int gsz = min(group_m, num_m - first_m);
+  const int local = tile - g * per_group;
+  TileCoord c;
+  c.m_blk = first_m + local % gsz;
+  c.n_blk = local / gsz;
+  return c;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 __nv_bfloat16* __restrict__ out, int M, int N, int K, int group_m, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  // barriers: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then the TMEM base slot
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const int num_m = M / BM;
+  const int num_n = (N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = K / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    mbar_fence_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, status, WK_ERR_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, full_bar(stage), kb * BK, tc.m_blk * BM);
+          tma_load_2d(sa + A_BYTES, &tmap_b, full_bar(stage), kb * BK, tc.n_blk * BN);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(1, 1, 0, 0, BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, status, WK_ERR_TIMEOUT_TMEM)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, status, WK_ERR_TIMEOUT_LOAD)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint64_t a_desc = smem_desc_sw128(sa, 16, 1024);
+          const uint64_t b_desc = smem_desc_sw128(sa + A_BYTES, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // 16 bf16 = 32 bytes along K inside the 128-byte swizzle span
+            mma_f16_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(tfull_bar(acc));
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are visible to this warp
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait_warp(tfull_bar(acc), acc_phase, status, WK_ERR_TIMEOUT_MMA)) break;
+      tc_fence_after();
+      const int row = tc.m_blk * BM + quad * 32 + lane;
+      __nv_bfloat16* out_row = out + static_cast<int64_t>(row) * N + tc.n_blk * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, v);
+        tc_wait_ld();
+        if (tc.n_blk * BN + c * 32 < N) {
+          uint4* dst = reinterpret_cast<uint4*>(out_row + c * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
+            w.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
+            w.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
+            w.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
+            dst[i] = w;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+}  // namespace wk
+
+extern "C" int wk_gemm_bf16(const void* a, const void* b, void* out, int m, int n, int k,
+                            void* stream) {
+  using namespace wk;
+  if (m < 0 || n < 0 || k < 0 || m % BM || n % 128 || k % BK) return WK_E_ARG;
+  if (m == 0 || n == 0) return 0;
+  if (k == 0) return WK_E_ARG;
+  if (!a || !b || !out || !aligned16(a) || !aligned16(b) || !aligned16(out)) return WK_E_ARG;
+  int* status = status_word();
+  if (!status) return WK_E_CUDA;
+
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
+    const uint32_t box[2] = {BK, BM};
+    int r = encode_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, dims, strides, box,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r) return r;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
+    const uint32_t box[2] = {BK, BN};
+    int r = encode_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b, dims, strides, box,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r) return r;
+  }
+  if (allow_smem(reinterpret_cast<const void*>(gemm_bf16_kernel), SMEM_BYTES)) return WK_E_CUDA;
+  const int num_tiles = (m / BM) * ((n + BN - 1) / BN);
+  const int sms = sm_count();
+  if (sms <= 0) return WK_E_CUDA;
+  const int grid = num_tiles < sms ? num_tiles : sms;
+  gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+      ta, tb, static_cast<__nv_bfloat16*>(out), m, n, k, 8, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
+}
