@@ -1,0 +1,404 @@
+"""Benchmark of the warpy-kernels hot path on B200.
+
+Default workload (N = 1): FP8 causal attention forward, batch 4, 32 heads, sequence 4096, head dim 128 (the
+configuration the headline metric is quoted on).  ``--workload`` selects the other hot-path kernels:
+``attn_bwd`` (backward of the same shape), ``gemm_mx`` (MXFP8 GEMM 8192 x 14336 x 4096), ``gemm_bf16`` (2048^3),
+``attn_gqa`` (B1 Hq64 Hkv8 N32768) and ``quant`` (MXFP8 quantiser, [8192, 4096] bf16).
+
+Multi-GPU (launched by ``torch.distributed.run``): the work shards with no data-path collective -- attention by
+batch x head (by KV-head group for GQA), GEMM and quantiser by rows -- so each rank runs the full per-GPU workload
+(weak scaling) and the reported value is the sum over ranks divided by the slowest rank's time.
+
+``--impl reference`` times the reference's CPU path (its torch fp32 test oracle, restated under ``oracle/``) on the
+host cores for a bounded sample of the same workload.
+"""
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+NOMINAL = {"fp8": 4500.0, "bf16": 2250.0}  # dense TFLOP/s, B200 data sheet
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------------------------
+# clocks sampling during the timed region
+# ------------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------------------
+# workloads: each returns dict(step=callable on device inputs, e2e_step=callable with host buffers, units, ...)
+# ------------------------------------------------------------------------------------------------------------
+def quantize_per_tensor(x):
+    scale = x.abs().amax().clamp_min(1e-12) / 448.0
+    return (x / scale).to(torch.float8_e4m3fn), scale
+
+
+def make_attn(dev, B, Hq, Hkv, N, d, causal, seed, backward=False):
+    import warpy_kernels as wk
+    from warpy_kernels.attn import make_attn_fwd
+
+    g = torch.Generator(device=dev).manual_seed(seed)
+    mk = lambda h: torch.randn(B, h, N, d, device=dev, generator=g).bfloat16().float()
+    q, k, v = mk(Hq), mk(Hkv), mk(Hkv)
+    q8, sq = quantize_per_tensor(q)
+    k8, sk = quantize_per_tensor(k)
+    v8, sv = quantize_per_tensor(v)
+    del q, k, v
+    full = lambda s: torch.full((B, Hkv), float(s), device=dev)
+    dsq, dsk, dsv = full(sq), full(sk), full(sv)
+    flops = 4.0 * B * Hq * N * N * d * (0.5 if causal else 1.0)
+    launch, out, lse, pmax = make_attn_fwd(q8, k8, v8, dsq, dsk, dsv, causal=causal)
+
+    # end to end: host e4m3 inputs in pinned memory -> device -> kernel -> bf16 output back to the host
+    hq, hk, hv = [x.view(torch.uint8).cpu().pin_memory() for x in (q8, k8, v8)]
+    dq8, dk8, dv8 = [torch.empty_like(x.view(torch.uint8)) for x in (q8, k8, v8)]
+    hout = torch.empty(out.shape, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        dq8.copy_(hq, non_blocking=True)
+        dk8.copy_(hk, non_blocking=True)
+        dv8.copy_(hv, non_blocking=True)
+        o, _, _ = wk.attn_fwd(dq8.view(torch.float8_e4m3fn), dk8.view(torch.float8_e4m3fn),
+                              dv8.view(torch.float8_e4m3fn), dsq, dsk, dsv, causal=causal)
+        hout.copy_(o, non_blocking=True)
+
+    return dict(step=launch, e2e_step=e2e_step, work=flops, bound="tensor", dtype="fp8", launches=1,
+                h2d=hq.numel() + hk.numel() + hv.numel(), d2h=hout.numel() * 2,
+                resident_bytes=3 * q8.numel() + out.numel() * 2,
+                check=lambda: None, tensors=(q8, k8, v8, dsq, dsk, dsv, out, lse))
+
+
+def make_gemm_bf16(dev, m, n, k, seed):
+    import warpy_kernels as wk
+
+    g = torch.Generator(device=dev).manual_seed(seed)
+    a = torch.randn(m, k, device=dev, generator=g).bfloat16()
+    b = torch.randn(n, k, device=dev, generator=g).bfloat16()
+    launch, out = wk.make_gemm(a, b)
+    ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
+    da, db = torch.empty_like(a), torch.empty_like(b)
+    hout = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        da.copy_(ha, non_blocking=True)
+        db.copy_(hb, non_blocking=True)
+        hout.copy_(wk.gemm(da, db), non_blocking=True)
+
+    return dict(step=launch, e2e_step=e2e_step, work=2.0 * m * n * k, bound="tensor", dtype="bf16", launches=1,
+                h2d=(ha.numel() + hb.numel()) * 2, d2h=hout.numel() * 2, tensors=(a, b, out))
+
+
+def make_quant(dev, m, k, seed):
+    import warpy_kernels as wk
+
+    g = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+    q = torch.empty(m, k, dtype=torch.float8_e4m3fn, device=dev)
+    s = torch.empty(m, k // 32, dtype=torch.uint8, device=dev)
+    hx = x.cpu().pin_memory()
+    dx = torch.empty_like(x)
+    hq = torch.empty(m, k, dtype=torch.uint8).pin_memory()
+    hs = torch.empty(m, k // 32, dtype=torch.uint8).pin_memory()
+
+    def e2e_step():
+        dx.copy_(hx, non_blocking=True)
+        wk.quantize_mx(dx, q, s)
+        hq.copy_(q.view(torch.uint8), non_blocking=True)
+        hs.copy_(s, non_blocking=True)
+
+    return dict(step=lambda: wk.quantize_mx(x, q, s), e2e_step=e2e_step, work=m * k * (2 + 1 + 1 / 32),
+                bound="hbm", dtype="u8", launches=1, h2d=hx.numel() * 2, d2h=hq.numel() + hs.numel(),
+                tensors=(x, q, s))
+
+
+WORKLOADS = {
+    "attn_fwd": dict(desc="FP8 causal attention forward B4 H32 N4096 d128", unit="TFLOP/s",
+                     make=lambda dev: make_attn(dev, 4, 32, 32, 4096, 128, True, 0)),
+    "attn_gqa": dict(desc="FP8 GQA causal attention forward B1 Hq64 Hkv8 N32768 d128", unit="TFLOP/s",
+                     make=lambda dev: make_attn(dev, 1, 64, 8, 32768, 128, True, 0)),
+    "gemm_bf16": dict(desc="BF16 GEMM M=N=K=2048", unit="TFLOP/s",
+                      make=lambda dev: make_gemm_bf16(dev, 2048, 2048, 2048, 0)),
+    "gemm_bf16_8k": dict(desc="BF16 GEMM M=N=K=8192", unit="TFLOP/s",
+                         make=lambda dev: make_gemm_bf16(dev, 8192, 8192, 8192, 0)),
+    "quant": dict(desc="MXFP8 quantiser [8192, 14336] bf16", unit="GB/s",
+                  make=lambda dev: make_quant(dev, 8192, 14336, 0)),
+}
+
+
+# ------------------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's torch fp32 oracle on the host cores, bounded sample
+# ------------------------------------------------------------------------------------------------------------
+def cpu_baseline(workload, budget_s=15.0):
+    from oracle import c_oracle
+    from oracle import reference_math as R
+
+    threads = torch.get_num_threads()
+    if workload in ("attn_fwd", "attn_gqa"):
+        N = 4096 if workload == "attn_fwd" else 32768
+        d, heads, done, t_used = 128, 0, 0.0, 0.0
+        g = torch.Generator().manual_seed(0)
+        q = torch.randn(1, 1, min(N, 4096), d, generator=g)
+        k = torch.randn(1, 1, N, d, generator=g)
+        v = torch.randn(1, 1, N, d, generator=g)
+        # one query head, the LAST 4096 queries of the sequence (for N=32768 this is the most expensive slice)
+        rows = q.shape[2]
+        while t_used < budget_s and heads < 4:
+            t0 = time.perf_counter()
+            R.attention_reference_chunked(q, k, v, True, q_chunk=1024)
+            t_used += time.perf_counter() - t0
+            heads += 1
+        # flops of that slice: rows x visible keys (bottom-right causal)
+        vis = sum(min(N, r + N - rows + 1) for r in range(rows))
+        flops = 4.0 * vis * d * heads
+        return {"value": flops / t_used / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "sample": f"{heads} (batch, head) slices of {rows} queries x {N} keys, causal, torch fp32 oracle"}
+    if workload.startswith("gemm_bf16"):
+        m = n = k = 2048
+        g = torch.Generator().manual_seed(0)
+        a = torch.randn(m, k, generator=g).bfloat16()
+        b = torch.randn(n, k, generator=g).bfloat16()
+        R.gemm_reference(a, b)
+        reps, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < min(budget_s, 5.0):
+            R.gemm_reference(a, b).bfloat16()
+            reps += 1
+        dt = time.perf_counter() - t0
+        return {"value": 2.0 * m * n * k * reps / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "sample": f"{reps} x (a.float() @ b.float().T) at 2048^3"}
+    if workload == "quant":
+        import numpy as np
+
+        m, k = 8192, 4096
+        x = torch.randn(m, k, generator=torch.Generator().manual_seed(0)).bfloat16()
+        xb = x.view(torch.int16).numpy().view(np.uint16)
+        cores = os.cpu_count() or 1
+        c_oracle.quantize_mx(xb, threads=cores)
+        reps, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < min(budget_s, 5.0):
+            c_oracle.quantize_mx(xb, threads=cores)
+            reps += 1
+        dt = time.perf_counter() - t0
+        return {"value": m * k * (2 + 1 + 1 / 32) * reps / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                "sample": f"{reps} x C restatement on [8192, 4096] bf16, {cores} pthreads"}
+    raise ValueError(workload)
+
+
+# ------------------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="attn_fwd", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    wl = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        steps = max(1, args.steps)
+        vals = []
+        for _ in range(min(steps, 3)):
+            vals.append(cpu_baseline(args.workload, budget_s=8.0))
+        best = max(vals, key=lambda c: c["value"])
+        line = {
+            "impl": "reference", "metric": f"{wl['desc']} throughput", "value": best["value"], "unit": best["unit"],
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": wl["desc"], "note": "reference CPU path = its torch fp32 test oracle on host cores"},
+            "cpu_baseline": best,
+            "e2e": {"value": best["value"], "unit": best["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    from warpy_kernels_b200 import _lib
+
+    w = wl["make"](dev)
+    stream = torch.cuda.current_stream()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        ev[0].record(stream)
+        for i in range(steps):
+            fn()
+            ev[i + 1].record(stream)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        total_ms = ev[0].elapsed_time(ev[-1])
+        per = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
+        return total_ms, per
+
+    # inputs + outputs of one step exceed the 126 MB L2 for every workload but gemm_bf16 2048^3; that one gets an
+    # explicit L2 flush between iterations
+    flush = None
+    if args.workload == "gemm_bf16":
+        flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        flush = lambda: flush_buf.zero_()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    if flush is None:
+        total_ms, per = timed(w["step"], args.steps, max(3, args.warmup))
+        kernel_ms = total_ms / args.steps
+    else:
+        # time each launch on its own between flushes
+        for _ in range(max(3, args.warmup)):
+            w["step"]()
+        torch.cuda.synchronize()
+        per = []
+        for _ in range(args.steps):
+            flush()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            w["step"]()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            per.append(e0.elapsed_time(e1))
+        kernel_ms = sum(per) / len(per)
+        total_ms = sum(per)
+    e2e_total_ms, _ = timed(w["e2e_step"], max(3, args.steps // 4), 2)
+    e2e_ms = e2e_total_ms / max(3, args.steps // 4)
+    clocks = sampler.stop()
+    _lib.device_status()
+
+    t = torch.tensor([kernel_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    kernel_ms, e2e_ms = t.tolist()
+
+    if rank == 0:
+        scale = 1e12 if wl["unit"] == "TFLOP/s" else 1e9
+        per_gpu = w["work"] / (kernel_ms * 1e-3) / scale
+        peaks = measured_peaks()
+        if w["bound"] == "tensor":
+            # no measured fp8 peak exists; the measured bf16 cuBLAS burst figure is doubled for fp8 operands
+            peak = peaks["bf16_tflops"] * (2.0 if w["dtype"] == "fp8" else 1.0)
+            unit = "TFLOP/s"
+        else:
+            peak, unit = peaks["hbm_gbs"], "GB/s"
+        line = {
+            "metric": f"{wl['desc']} throughput",
+            "value": per_gpu * world,
+            "unit": wl["unit"],
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(3, args.warmup),
+            "ms_per_step": kernel_ms,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": w["dtype"],
+            "data": "synthetic",
+            "config": {"workload": wl["desc"], "l2": "explicit flush between launches" if flush else
+                       "inputs and outputs larger than L2", "sharding": "independent per-rank shards, no collective"},
+            "roofline": {"bound": w["bound"], "achieved": per_gpu, "peak": peak, "unit": unit,
+                         "frac": per_gpu / peak, "traffic": None,
+                         "peak_source": f"{peaks['source']}" + (" bf16 cuBLAS burst x2 for fp8" if w["dtype"] == "fp8" else ""),
+                         "frac_of_nominal": per_gpu / NOMINAL[w["dtype"]] if w["dtype"] in NOMINAL else None},
+            "e2e": {"value": w["work"] / (e2e_ms * 1e-3) / scale * world, "unit": wl["unit"],
+                    "h2d_bytes_per_step": w["h2d"], "d2h_bytes_per_step": w["d2h"]},
+            "gpu_launches": w["launches"] * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            base = "attn_fwd" if args.workload == "attn_fwd" else args.workload
+            line["cpu_baseline"] = cpu_baseline(base if base in ("attn_fwd", "attn_gqa", "quant") else "gemm_bf16")
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -66,6 +66,47 @@ int wk_quantize_mx(const void* x, int dtype, int64_t rows, int64_t cols, int64_t
  * K % 64 == 0. */
 int wk_gemm_bf16(const void* a, const void* b, void* out, int m, int n, int k, void* stream);
 
+/* FP8 attention forward.  Replaces the launch built in
+ * warpy_kernels/attn/fwd_api.py:344-390 (kernel: warpy_kernels/attn/fwd_base.py:670-758 with the
+ * e4m3 overrides of warpy_kernels/attn/fwd_sm120.py:81-136).
+ *   q [B,Hq,Nq,d], k,v [B,Hkv,Nk,d]  e4m3 bytes; *_strides = element (= byte) strides of
+ *       dims (B, H, N), the last dimension is contiguous; every stride and base address
+ *       a multiple of 16; d == 128; Hq % Hkv == 0
+ *   out [B,Hq,Nq,d] bf16, out_strides in elements (multiples of 8), base 16-byte aligned
+ *   lse, pmax  fp32, element strides lse_strides = (B, H) with rows contiguous; may be
+ *       NULL when write_lse == 0
+ *   q/k/v_descale  fp32 [B,Hkv] contiguous
+ *   causal: bottom-right aligned mask (key j visible to query i iff j <= i + Nk - Nq,
+ *       with Nk replaced by seqused_k[b] when that is given)
+ *   softmax_scale > 0
+ * Outputs: out = softmax(scale . q k^T) v on the dequantised inputs; lse = base-2
+ * log-sum-exp of the scaled logits (+inf for rows without a visible key, which get
+ * out = 0 and pmax = 0); pmax = largest probability of the row. */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  float* lse;
+  float* pmax;
+  const float* q_descale;
+  const float* k_descale;
+  const float* v_descale;
+  int64_t q_strides[3];
+  int64_t k_strides[3];
+  int64_t v_strides[3];
+  int64_t out_strides[3];
+  int64_t lse_strides[2];
+  int32_t B, Hq, Hkv, Nq, Nk, d;
+  int32_t causal;
+  int32_t write_lse;
+  int32_t lse_natural;      /* 1: lse is written in natural log units instead of base 2 */
+  const int32_t* seqused_k; /* optional [B] int32: keys each batch item attends to (<= Nk) */
+  float softmax_scale;
+} wk_attn_fwd_args;
+
+int wk_attn_fwd_fp8(const wk_attn_fwd_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

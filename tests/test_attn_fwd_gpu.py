@@ -1,0 +1,147 @@
+"""GPU: FP8 attention forward against the fp32 oracle.
+
+Tolerances: the north-star gates (cosine >= 0.999, max-abs <= 2e-2) and the reference's own
+(``tests/attn/test_fwd.py:21``: out rel-L2 <= 6e-2, lse max-abs <= 5e-2).
+"""
+
+import os
+
+import pytest
+import torch
+
+from oracle import reference_math as R
+from tests.helpers import fwd_errors, load_golden, randn_qkv, sink_qkv
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = ["attn_mha_causal", "attn_gqa_ragged_causal", "attn_gqa_noncausal", "attn_short_q_causal"]
+# the d = 128 shapes of the reference's forward test (tests/attn/test_fwd.py:23-31): (B, Hq, Hkv, Nq, Nk, d)
+SHAPES = [
+    (1, 1, 1, 128, 64, 128),
+    (2, 4, 2, 1000, 1000, 128),
+    (1, 2, 2, 512, 1024, 128),
+    (1, 2, 1, 512, 128, 128),
+    (1, 8, 2, 384, 640, 128),
+]
+
+
+def check(errs):
+    assert errs["out"] <= 6e-2, errs
+    assert errs["lse"] <= 5e-2, errs
+    assert errs["cos"] >= 0.999, errs
+    assert errs["max_abs"] <= 2e-2, errs
+
+
+@pytest.mark.parametrize("name", GOLDEN)
+def test_against_reference_fixture(cuda, golden_dir, name):
+    from warpy_kernels import attn_fwd
+
+    t = load_golden(os.path.join(golden_dir, f"{name}.npz"), cuda)
+    out, lse, pmax = attn_fwd(t["q8"], t["k8"], t["v8"], t["sq"], t["sk"], t["sv"], causal=t["causal"])
+    assert out.dtype == torch.bfloat16 and out.shape == t["q8"].shape
+    Nq, Nk = t["q8"].shape[2], t["k8"].shape[2]
+    check(fwd_errors(out, lse, t["out"], t["lse"], Nq, Nk, t["causal"]))
+    # pmax = largest probability of the row
+    qd, kd, vd = R.dequantize_qkv(t["q8"].cpu(), t["k8"].cpu(), t["v8"].cpu(), t["sq"].cpu(), t["sk"].cpu(), t["sv"].cpu())
+    rep = qd.shape[1] // kd.shape[1]
+    s = (qd @ kd.repeat_interleave(rep, 1).transpose(-1, -2)) / (128**0.5)
+    if t["causal"]:
+        row = torch.arange(Nq)[:, None]
+        col = torch.arange(Nk)[None, :]
+        s = s.masked_fill(col > row + Nk - Nq, float("-inf"))
+    want = torch.softmax(s, -1).amax(-1)
+    vis = torch.isfinite(t["lse"])
+    assert (pmax.cpu()[vis] - want[vis]).abs().max().item() <= 0.05 * want[vis].max().item() + 1e-3
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_reference_shapes(cuda, shape, causal):
+    from warpy_kernels import attn_fwd
+
+    q, k, v = randn_qkv(*shape, device=cuda)
+    q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+    out, lse, _ = attn_fwd(q8, k8, v8, sq, sk, sv, causal=causal)
+    qd, kd, vd = R.dequantize_qkv(q8.cpu(), k8.cpu(), v8.cpu(), sq.cpu(), sk.cpu(), sv.cpu())
+    out_ref, lse_ref = R.attention_reference(qd, kd, vd, causal)
+    check(fwd_errors(out, lse, out_ref, lse_ref, shape[3], shape[4], causal))
+
+
+def test_repeat_is_bit_identical(cuda):
+    from warpy_kernels import attn_fwd
+
+    q, k, v = randn_qkv(1, 4, 2, 640, 640, 128, seed=3, device=cuda)
+    q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+    a = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
+    b = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+def test_layouts_bit_equal(cuda):
+    """``[B, N, H, d]``-strided views, ``out=`` reuse and ``return_lse=False`` (``tests/attn/test_layout.py:24-80``)."""
+    from warpy_kernels import attn_fwd
+
+    B, H, N, d = 2, 4, 300, 128
+    q, k, v = randn_qkv(B, H, H, N, N, d, seed=5, device=cuda)
+    q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+    base = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
+    tq, tk, tv = [x.transpose(1, 2).contiguous().transpose(1, 2) for x in (q8, k8, v8)]  # [B, N, H, d] storage
+    out, lse, pmax = attn_fwd(tq, tk, tv, sq, sk, sv, causal=True)
+    assert out.stride() == tq.stride()  # out keeps q's memory layout
+    assert torch.equal(out, base[0]) and torch.equal(lse, base[1]) and torch.equal(pmax, base[2])
+    qkv = torch.stack([q8.view(torch.uint8), k8.view(torch.uint8), v8.view(torch.uint8)], dim=3).view(torch.float8_e4m3fn)
+    out2, _, _ = attn_fwd(qkv[:, :, :, 0], qkv[:, :, :, 1], qkv[:, :, :, 2], sq, sk, sv, causal=True)  # fused QKV
+    assert torch.equal(out2, base[0])
+    buf = torch.empty_like(base[0])
+    out3, l3, p3 = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True, out=buf, return_lse=False)
+    assert out3 is buf and l3 is None and p3 is None and torch.equal(buf, base[0])
+
+
+def test_seqused_and_natural_lse(cuda):
+    """``seqused_k`` equals truncating K/V; ``lse_natural`` is ``lse * ln 2`` (``tests/attn/test_seqused.py:13-88``)."""
+    from warpy_kernels import attn_fwd
+
+    q, k, v = randn_qkv(2, 2, 1, 256, 512, 128, seed=9, device=cuda)
+    q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+    used = torch.tensor([200, 512], dtype=torch.int32, device=cuda)
+    for causal in (False, True):
+        out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=causal, seqused_k=used)
+        for b, n in enumerate(used.tolist()):
+            o1, l1, p1 = attn_fwd(q8[b : b + 1], k8[b : b + 1, :, :n], v8[b : b + 1, :, :n], sq[b : b + 1],
+                                  sk[b : b + 1], sv[b : b + 1], causal=causal)
+            assert torch.equal(out[b : b + 1], o1) and torch.equal(lse[b : b + 1], l1)
+    _, lse2, _ = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
+    _, lsen, _ = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True, lse_natural=True)
+    assert torch.allclose(lsen, lse2 * 0.6931471805599453, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("gap", [8])
+def test_sink_long_tail(cuda, gap):
+    """One dominant key over a 32768-key tail (``tests/attn/test_fwd.py:104-114``, gate 2e-2)."""
+    from warpy_kernels import attn_fwd
+
+    q, k, v = sink_qkv(256, 32768, 128, gap, device=cuda)
+    q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+    out, _, _ = attn_fwd(q8, k8, v8, sq, sk, sv)
+    ref, _ = R.attention_reference(*R.dequantize_qkv(q8, k8, v8, sq, sk, sv), False)
+    assert R.rel_l2(out, ref) <= 2e-2
+
+
+def test_validation_errors(cuda):
+    from warpy_kernels import attn_fwd
+
+    q = torch.zeros(1, 2, 128, 128, device=cuda).to(torch.float8_e4m3fn)
+    kv = torch.zeros(1, 1, 128, 128, device=cuda).to(torch.float8_e4m3fn)
+    with pytest.raises(ValueError):
+        attn_fwd(q, kv.bfloat16(), kv)
+    with pytest.raises(ValueError):
+        attn_fwd(q, kv[:, :, :, :64], kv)
+    with pytest.raises(ValueError):
+        attn_fwd(q, kv, kv, q_descale=torch.ones(1, 2, device=cuda))
+    with pytest.raises(ValueError):
+        attn_fwd(q, kv, kv, seqused_k=torch.ones(1, device=cuda))
+    with pytest.raises(NotImplementedError):
+        attn_fwd(q.bfloat16(), kv.bfloat16(), kv.bfloat16())
+    with pytest.raises(ValueError):
+        attn_fwd(q, kv, kv, out=torch.empty(1, 2, 128, 128, device=cuda))

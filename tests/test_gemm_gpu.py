@@ -41,7 +41,7 @@ def test_bf16_structured_operands(cuda):
     b[torch.arange(n), (torch.arange(n) * 7) % k] = (torch.arange(n, device=cuda) % 53 + 1).float()
     out = gemm(a.bfloat16(), b.bfloat16())
     want = a @ b.T
-    assert torch.equal(out.float(), want)
+    assert torch.equal(out, want.bfloat16())  # single products: exact up to the bf16 rounding of the output
 
 
 def test_bf16_out_buffer_and_errors(cuda):

@@ -1,6 +1,11 @@
-def attn_fwd(*args, **kwargs):
-    raise NotImplementedError("attention forward is being built")
+from .bwd_api import attn_bwd, autotune_attn_bwd, make_attn_bwd
+from .fwd_api import attn_fwd, autotune_attn_fwd, make_attn_fwd
 
-
-def attn_bwd(*args, **kwargs):
-    raise NotImplementedError("attention backward is being built")
+__all__ = [
+    "attn_bwd",
+    "attn_fwd",
+    "autotune_attn_bwd",
+    "autotune_attn_fwd",
+    "make_attn_bwd",
+    "make_attn_fwd",
+]
