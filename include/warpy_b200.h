@@ -66,6 +66,39 @@ int wk_quantize_mx(const void* x, int dtype, int64_t rows, int64_t cols, int64_t
  * K % 64 == 0. */
 int wk_gemm_bf16(const void* a, const void* b, void* out, int m, int n, int k, void* stream);
 
+/* MXFP8 block-scaled GEMM,
+ *   out[M,N] = scale_a . scale_b . (a . 2^(a_scale_mx-127)) @ (b . 2^(b_scale_mx-127))^T,
+ * e4m3 operands, fp32 accumulation, bf16 output.  Replaces the launch of GemmSm120 for
+ * fp8 inputs, warpy_kernels/gemm/api.py:216-267 (block-scaled MMA path:
+ * warpy_kernels/gemm/sm120.py:121-146; MX output epilogue: warpy_kernels/gemm/sm89.py:65-93).
+ *   a [M,K], b [N,K]           e4m3 bytes, contiguous, 16-byte aligned
+ *   a_scale_mx [M,K/32]        ue8m0 bytes, contiguous, 4-byte aligned, or NULL for unit scales
+ *   b_scale_mx [N,K/32]        same for b (the reference scales only a; NULL reproduces it)
+ *   scale_a, scale_b           optional device pointers to one fp32 each (NULL = 1)
+ *   out [M,N] bf16             contiguous, 16-byte aligned
+ *   q_mx [M,N] e4m3, s_mx [M,N/32] ue8m0   optional (both or neither): the fp32 results
+ *                              quantised per row and 32 columns before the bf16 rounding
+ *   workspace                  scratch of at least wk_gemm_mxfp8_workspace_bytes(M,N,K) bytes,
+ *                              16-byte aligned; holds the re-tiled scale factors of this call
+ * M % 128 == 0, N % 128 == 0, K % 128 == 0. */
+typedef struct {
+  const void* a;
+  const void* b;
+  const void* a_scale_mx;
+  const void* b_scale_mx;
+  const float* scale_a;
+  const float* scale_b;
+  void* out;
+  void* q_mx;
+  void* s_mx;
+  void* workspace;
+  int64_t workspace_bytes;
+  int32_t m, n, k;
+} wk_gemm_mx_args;
+
+int64_t wk_gemm_mxfp8_workspace_bytes(int m, int n, int k);
+int wk_gemm_mxfp8(const wk_gemm_mx_args* args, void* stream);
+
 /* FP8 attention forward.  Replaces the launch built in
  * warpy_kernels/attn/fwd_api.py:344-390 (kernel: warpy_kernels/attn/fwd_base.py:670-758 with the
  * e4m3 overrides of warpy_kernels/attn/fwd_sm120.py:81-136).

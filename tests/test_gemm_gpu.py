@@ -62,3 +62,127 @@ def test_bf16_out_buffer_and_errors(cuda):
         gemm(a.t(), b.t())  # not contiguous
     with pytest.raises(ValueError):
         gemm(a, b, out=torch.empty(128, 64, device=cuda, dtype=torch.bfloat16))
+
+
+# ---- fp8 / MXFP8 --------------------------------------------------------------------------------------------
+FP8 = torch.float8_e4m3fn
+FP8_SHAPES = [(256, 512, 1024), (4096, 4096, 2048), (128, 128, 128), (384, 640, 384)]
+
+
+@pytest.mark.parametrize("shape", FP8_SHAPES)
+def test_fp8_unit_scales_match_fp32_product(cuda, shape):
+    """Plain e4m3 inputs (no MX scales): the reference's ``matches_cublas`` for fp8 (``tests/gemm/test_gemm.py:214-241``)."""
+    from warpy_kernels import gemm
+
+    m, n, k = shape
+    g = torch.Generator(device=cuda).manual_seed(0)
+    a = torch.randn(m, k, device=cuda, generator=g).to(FP8)
+    b = torch.randn(n, k, device=cuda, generator=g).to(FP8)
+    out = gemm(a, b)
+    want = R.gemm_reference(a.cpu(), b.cpu())
+    assert R.rel_l2(out.cpu(), want.bfloat16()) <= 1e-3
+    assert torch.equal(gemm(a, b), out)
+
+
+@pytest.mark.parametrize("shape", FP8_SHAPES)
+def test_mx_input_random_scale_bytes(cuda, shape):
+    """Random scale bytes 118..135 on A plus a scalar on B (``tests/gemm/test_gemm.py:192-205``), then on both."""
+    from warpy_kernels import gemm
+
+    m, n, k = shape
+    g = torch.Generator(device=cuda).manual_seed(0)
+    a = torch.randn(m, k, device=cuda, generator=g).to(FP8)
+    b = torch.randn(n, k, device=cuda, generator=g).to(FP8)
+    sa = torch.randint(118, 136, (m, k // 32), device=cuda, generator=g, dtype=torch.uint8)
+    sb = torch.randint(120, 134, (n, k // 32), device=cuda, generator=g, dtype=torch.uint8)
+    beta = torch.tensor([0.75], device=cuda)
+    got = gemm(a, b, a_scale_mx=sa, scale_b=beta)
+    want = R.gemm_reference(a.cpu(), b.cpu(), a_scale_mx=sa.cpu(), alpha=0.75)
+    assert R.rel_l2(got.cpu(), want) <= 1e-2
+    got2 = gemm(a, b, a_scale_mx=sa, b_scale_mx=sb)
+    want2 = R.gemm_reference(a.cpu(), b.cpu(), a_scale_mx=sa.cpu(), b_scale_mx=sb.cpu())
+    assert R.rel_l2(got2.cpu(), want2) <= 1e-2
+    assert R.rel_l2(got2.cpu(), want2.bfloat16()) <= 1e-3
+
+
+def test_mx_golden_fixture(cuda, golden_dir):
+    import os
+
+    import numpy as np
+
+    from warpy_kernels import gemm
+
+    z = np.load(os.path.join(golden_dir, "gemm_mx.npz"))
+    f8 = lambda x: torch.from_numpy(x).to(cuda).view(FP8)
+    a, b = f8(z["a8"]), f8(z["b8"])
+    sa, sb = torch.from_numpy(z["sa"]).to(cuda), torch.from_numpy(z["sb"]).to(cuda)
+    assert R.rel_l2(gemm(a, b, a_scale_mx=sa).cpu(), torch.from_numpy(z["want_a"]).bfloat16()) <= 1e-3
+    assert R.rel_l2(gemm(a, b, a_scale_mx=sa, b_scale_mx=sb).cpu(), torch.from_numpy(z["want_ab"]).bfloat16()) <= 1e-3
+
+
+def test_mx_scale_layout_is_exact(cuda):
+    """Power-of-two data with one distinct scale byte per (row, K block): every output is exact, so any mistake in
+    the scale-factor tiling shows up as a wrong integer."""
+    from warpy_kernels import gemm
+
+    m, n, k = 256, 384, 512
+    a = torch.zeros(m, k, device=cuda)
+    b = torch.zeros(n, k, device=cuda)
+    kb = k // 32
+    # row i of a has a single 1 in K block (i % kb); row j of b has a single 1 at the same position of block (j % kb)
+    a[torch.arange(m), (torch.arange(m) % kb) * 32 + 3] = 1.0
+    b[torch.arange(n), (torch.arange(n) % kb) * 32 + 3] = 1.0
+    sa = (120 + (torch.arange(m, device=cuda)[:, None] * 3 + torch.arange(kb, device=cuda)[None, :] * 5) % 9).to(torch.uint8)
+    sb = (124 + (torch.arange(n, device=cuda)[:, None] + torch.arange(kb, device=cuda)[None, :] * 2) % 7).to(torch.uint8)
+    got = gemm(a.to(FP8), b.to(FP8), a_scale_mx=sa, b_scale_mx=sb).float()
+    want = R.gemm_reference(a.to(FP8).cpu(), b.to(FP8).cpu(), a_scale_mx=sa.cpu(), b_scale_mx=sb.cpu())
+    assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 1024), (4096, 4096, 2048)])
+def test_mx_output_and_chain(cuda, shape):
+    """``out_mx`` (``tests/gemm/test_gemm.py:151-175``) and the MX-out -> MX-in chain (``:206-211``)."""
+    import numpy as np
+
+    from oracle import c_oracle
+    from warpy_kernels import gemm, quantize_mx
+
+    m, n, k = shape
+    g = torch.Generator(device=cuda).manual_seed(0)
+    a = torch.randn(m, k, device=cuda, generator=g).to(FP8)
+    b = torch.randn(n, k, device=cuda, generator=g).to(FP8)
+    out, q, sc = gemm(a, b, out_mx=True)
+    assert R.rel_l2(R.mx_dequant(q, sc), out.float()) <= 4e-2
+    peak = q.float().abs().view(m, n // 32, 32).amax(-1)
+    assert bool(((peak >= 224) & (peak <= 448)).all()), "block scales are not tight"
+    # the epilogue quantiser and the standalone kernel share their arithmetic: on the exact fp32 product of a small
+    # integer-valued problem both must give the same bytes as the CPU oracle
+    ai = torch.randint(-3, 4, (128, 128), device=cuda, generator=g).float()
+    bi = torch.randint(-3, 4, (256, 128), device=cuda, generator=g).float()
+    o2, q2, s2 = gemm(ai.to(FP8), bi.to(FP8), out_mx=True)
+    exact = ai @ bi.T
+    wq, ws = c_oracle.quantize_mx(exact.cpu().numpy())
+    assert np.array_equal(q2.view(torch.uint8).cpu().numpy(), wq) and np.array_equal(s2.cpu().numpy(), ws)
+    q3, s3 = quantize_mx(exact)
+    assert torch.equal(q3.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s3, s2)
+    # chain: the MX output of one product is the A operand of the next
+    x = torch.randn(m, k, device=cuda, generator=g).to(FP8)
+    w2 = torch.randn(n, n, device=cuda, generator=g).to(FP8)
+    h, hq, hs = gemm(x, b, out_mx=True)
+    y = gemm(hq, w2, a_scale_mx=hs).float()
+    assert R.rel_l2(y, h.float() @ w2.float().T) <= 5e-2
+
+
+def test_fp8_rejects_bad_arguments(cuda):
+    from warpy_kernels import gemm
+
+    a = torch.zeros(128, 256, device=cuda).to(FP8)
+    b = torch.zeros(128, 256, device=cuda).to(FP8)
+    with pytest.raises(ValueError):
+        gemm(a, b, a_scale_mx=torch.zeros(128, 4, device=cuda, dtype=torch.uint8))  # wrong scale shape
+    with pytest.raises(ValueError):
+        gemm(a, b, a_scale_mx=torch.zeros(128, 8, device=cuda))  # wrong dtype
+    with pytest.raises(ValueError):
+        gemm(a[:, :64].contiguous(), b[:, :64].contiguous())  # K not a multiple of 128
+    with pytest.raises(NotImplementedError):
+        gemm(a, b, act="gelu")

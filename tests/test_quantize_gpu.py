@@ -79,9 +79,11 @@ def test_reference_properties_at_full_size(cuda):
     assert R.rel_l2(deq, x.float()) <= 4e-2
     peak = q.float().abs().view(8192, 128, 32).amax(-1)
     assert bool(((peak >= 224) & (peak <= 448)).all())
-    # idempotence: quantising the dequantised tensor reproduces codes and scales
+    # fixed point: quantising the dequantised tensor reproduces the same values (a block whose peak code is
+    # exactly 224 moves to the next smaller scale with doubled codes, so compare values, not bytes)
     q2, s2 = quantize_mx(deq)
-    assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8)) and torch.equal(s2, s)
+    deq2 = q2.float() * torch.exp2(s2.float() - 127).repeat_interleave(32, dim=1)
+    assert torch.equal(deq2, deq)
 
 
 def test_rejects_bad_shapes(cuda):

@@ -1,0 +1,363 @@
+// MXFP8 block-scaled GEMM for sm_100a:
+//   out[M,N] = alpha . (a8 . 2^(sa-127)) . (b8 . 2^(sb-127))^T      bf16 output, fp32 accumulation
+// a8 [M,K], b8 [N,K] e4m3; sa [M,K/32], sb [N,K/32] ue8m0 bytes (one per row and 32
+// elements along K); either scale tensor may be absent (unit scales).  Optionally the
+// fp32 results are also written as MXFP8 (codes + scale byte per 32 columns) before
+// they are rounded to bf16.
+//
+// Two kernels:
+//  1. swizzle_scales_kernel re-tiles the row-major scale bytes into the 512-byte
+//     atoms tcgen05.mma reads them in (128 rows x 4 K-blocks: byte offset
+//     (row % 32) * 16 + (row / 32 % 4) * 4 + kblock % 4), one atom per 128 rows and 128
+//     K elements, atoms ordered [row block][K block].  This is the kernel's scratch.
+//  2. gemm_mxfp8_kernel: persistent, warp-specialised, 128 x 256 tile, 128 K-bytes per
+//     stage.  Warp 0: TMA for A/B (128-byte swizzle) plus bulk copies of the scale
+//     atoms.  Warp 1: tcgen05.cp of the atoms into TMEM, then four
+//     tcgen05.mma kind::mxf8f6f4.block_scale (K = 32 each; the scale-factor id selects
+//     the byte of the K block).  Warps 2-5: epilogue from TMEM.
+//
+// Arithmetic follows the reference's block-scaled path (warpy_kernels/gemm/sm120.py:121-146:
+// e4m3 products scaled by 2^(sfa-127) per row and 32-element K block, fp32 accumulate)
+// and its MX output epilogue (warpy_kernels/gemm/sm89.py:65-93).
+//
+// Tensor-core bound: 2*M*N*K flops per launch.
+#include "common.cuh"
+#include "host_common.h"
+
+namespace wk {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;  // bytes == e4m3 elements
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK;
+constexpr int B_BYTES = BN * BK;
+constexpr int SF_ATOM = 512;
+constexpr int SFA_BYTES = SF_ATOM;
+constexpr int SFB_BYTES = 2 * SF_ATOM;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int ACC_COL = 0;
+constexpr int SF_COL = 256;        // scale-factor columns start here
+constexpr int SF_SLOTS = 4;        // one slot per smem stage
+constexpr int SF_SLOT_COLS = 12;   // 4 (A: 128 rows) + 8 (B: 256 rows)
+
+// ---------------------------------------------------------------------------
+// scale pre-swizzle
+// ---------------------------------------------------------------------------
+// One thread per (row, 128-element K block): reads 4 scale bytes, writes one 32-bit word.
+__global__ void swizzle_scales_kernel(const uint8_t* __restrict__ s, uint32_t* __restrict__ out,
+                                      int rows, int kblocks128) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(rows) * kblocks128;
+  if (idx >= total) return;
+  const int kb = static_cast<int>(idx % kblocks128);
+  const int row = static_cast<int>(idx / kblocks128);
+  uint32_t w = 0x7f7f7f7fu;  // unit scales when the caller gave none
+  if (s) w = *reinterpret_cast<const uint32_t*>(s + static_cast<int64_t>(row) * kblocks128 * 4 + kb * 4);
+  const int rb = row / 128;
+  const int r = row % 128;
+  const int64_t atom = static_cast<int64_t>(rb) * kblocks128 + kb;
+  out[atom * (SF_ATOM / 4) + (r % 32) * 4 + (r / 32)] = w;
+}
+
+struct TileCoord {
+  int m_blk, n_blk;
+};
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int group_m) {
+  const int per_group = group_m * num_n;
+  const int g = tile / per_group;
+  const int first_m = g * group_m;
+  const int gsz = min(group_m, num_m - first_m);
+  const int local = tile - g * per_group;
+  TileCoord c;
+  c.m_blk = first_m + local % gsz;
+  c.n_blk = local / gsz;
+  return c;
+}
+
+struct GemmParams {
+  __nv_bfloat16* out;
+  uint8_t* q_mx;        // optional [M,N] e4m3
+  uint8_t* s_mx;        // optional [M,N/32]
+  const uint8_t* sfa;   // swizzled atoms [M/128][K/128][512]
+  const uint8_t* sfb;   // swizzled atoms [N/128][K/128][512]
+  const float* scale_a; // optional scalar
+  const float* scale_b; // optional scalar
+  int M, N, K;
+  int group_m;
+  int* status;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  const uint32_t tfull_bar = bar_base + 8u * (2 * STAGES);
+  const uint32_t tempty_bar = bar_base + 8u * (2 * STAGES + 1);
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 2);
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const int num_m = p.M / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = p.K / BK;
+  const int n_atoms_total = p.N / 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, 4);
+    mbar_fence_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, num_m, num_n, p.group_m);
+        const int nb_atoms = min(2, n_atoms_total - tc.n_blk * 2);  // 1 on a 128-wide edge tile
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          const uint32_t ssfa = sb + B_BYTES;
+          const uint32_t ssfb = ssfa + SFA_BYTES;
+          mbar_expect_tx(full_bar(stage), A_BYTES + B_BYTES + SFA_BYTES + nb_atoms * SF_ATOM);
+          tma_load_2d(sa, &tmap_a, full_bar(stage), kb * BK, tc.m_blk * BM);
+          tma_load_2d(sb, &tmap_b, full_bar(stage), kb * BK, tc.n_blk * BN);
+          bulk_load(ssfa, p.sfa + (static_cast<int64_t>(tc.m_blk) * num_kb + kb) * SF_ATOM, SF_ATOM,
+                    full_bar(stage));
+          for (int a = 0; a < nb_atoms; ++a) {
+            bulk_load(ssfb + a * SF_ATOM,
+                      p.sfb + (static_cast<int64_t>(tc.n_blk * 2 + a) * num_kb + kb) * SF_ATOM, SF_ATOM,
+                      full_bar(stage));
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local) {
+        if (!mbar_wait(tempty_bar, (local & 1) ^ 1, p.status, WK_ERR_TIMEOUT_TMEM)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + ACC_COL;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, p.status, WK_ERR_TIMEOUT_LOAD)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          const uint32_t ssfa = sb + B_BYTES;
+          const uint32_t ssfb = ssfa + SFA_BYTES;
+          const uint32_t sf_tmem = tmem_base + SF_COL + stage * SF_SLOT_COLS;
+          // 32 rows x 16 bytes per copy; the shared-memory source is a plain (unswizzled) block
+          tmem_cp_32x128b_warpx4(sf_tmem + 0, smem_desc_plain(ssfa, 16, 128));
+          tmem_cp_32x128b_warpx4(sf_tmem + 4, smem_desc_plain(ssfb, 16, 128));
+          tmem_cp_32x128b_warpx4(sf_tmem + 8, smem_desc_plain(ssfb + SF_ATOM, 16, 128));
+          const uint64_t a_desc = smem_desc_sw128(sa, 16, 1024);
+          const uint64_t b_desc = smem_desc_sw128(sb, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k) {
+            mma_mxf8_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, make_idesc_mx(BM, BN, k, k), sf_tmem,
+                        sf_tmem + 4, (kb | k) != 0);
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(tfull_bar);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quad = warp & 3;
+    float alpha = 1.f;
+    if (p.scale_a) alpha *= *p.scale_a;
+    if (p.scale_b) alpha *= *p.scale_b;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const TileCoord tc = tile_coord(tile, num_m, num_n, p.group_m);
+      if (!mbar_wait_warp(tfull_bar, local & 1, p.status, WK_ERR_TIMEOUT_MMA)) break;
+      tc_fence_after();
+      const int row = tc.m_blk * BM + quad * 32 + lane;
+      const int64_t row_off = static_cast<int64_t>(row) * p.N + tc.n_blk * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ACC_COL + c * 32, v);
+        tc_wait_ld();
+        if (tc.n_blk * BN + c * 32 < p.N) {
+          float f[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]) * alpha;
+          uint4* dst = reinterpret_cast<uint4*>(p.out + row_off + c * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack_bf16x2(f[8 * i + 0], f[8 * i + 1]);
+            w.y = pack_bf16x2(f[8 * i + 2], f[8 * i + 3]);
+            w.z = pack_bf16x2(f[8 * i + 4], f[8 * i + 5]);
+            w.w = pack_bf16x2(f[8 * i + 6], f[8 * i + 7]);
+            dst[i] = w;
+          }
+          if (p.q_mx) {
+            // this thread's 32 consecutive columns are exactly one MX block
+            uint32_t amax = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) amax = max(amax, __float_as_uint(f[i]) & 0x7fffffffu);
+            int e = static_cast<int>((amax + 0x1fffffu) >> 23) - 8;
+            e = min(max(e, 0), 254);
+            const float inv = __uint_as_float(static_cast<uint32_t>(max(254 - e, 1)) << 23);
+            uint4* qdst = reinterpret_cast<uint4*>(p.q_mx + row_off + c * 32);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              uint4 w;
+              w.x = pack_e4m3x4(__fmul_rn(f[16 * i + 0], inv), __fmul_rn(f[16 * i + 1], inv),
+                                __fmul_rn(f[16 * i + 2], inv), __fmul_rn(f[16 * i + 3], inv));
+              w.y = pack_e4m3x4(__fmul_rn(f[16 * i + 4], inv), __fmul_rn(f[16 * i + 5], inv),
+                                __fmul_rn(f[16 * i + 6], inv), __fmul_rn(f[16 * i + 7], inv));
+              w.z = pack_e4m3x4(__fmul_rn(f[16 * i + 8], inv), __fmul_rn(f[16 * i + 9], inv),
+                                __fmul_rn(f[16 * i + 10], inv), __fmul_rn(f[16 * i + 11], inv));
+              w.w = pack_e4m3x4(__fmul_rn(f[16 * i + 12], inv), __fmul_rn(f[16 * i + 13], inv),
+                                __fmul_rn(f[16 * i + 14], inv), __fmul_rn(f[16 * i + 15], inv));
+              qdst[i] = w;
+            }
+            p.s_mx[static_cast<int64_t>(row) * (p.N / 32) + (tc.n_blk * BN + c * 32) / 32] =
+                static_cast<uint8_t>(e);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+int swizzle(const void* s, void* dst, int rows, int k, cudaStream_t st) {
+  const int kb128 = k / 128;
+  const int64_t total = static_cast<int64_t>(rows) * kb128;
+  const int threads = 256;
+  const int64_t blocks = (total + threads - 1) / threads;
+  swizzle_scales_kernel<<<static_cast<unsigned>(blocks), threads, 0, st>>>(
+      static_cast<const uint8_t*>(s), static_cast<uint32_t*>(dst), rows, kb128);
+  return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
+}
+
+}  // namespace
+}  // namespace wk
+
+extern "C" int64_t wk_gemm_mxfp8_workspace_bytes(int m, int n, int k) {
+  if (m < 0 || n < 0 || k < 0) return WK_E_ARG;
+  return (static_cast<int64_t>(m) + n) * (k / 32) + 32;
+}
+
+extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
+  using namespace wk;
+  if (!a) return WK_E_ARG;
+  const int m = a->m, n = a->n, k = a->k;
+  if (m < 0 || n < 0 || k < 0 || m % BM || n % 128 || k % BK) return WK_E_ARG;
+  if (m == 0 || n == 0) return 0;
+  if (k == 0) return WK_E_ARG;
+  if (!a->a || !a->b || !a->out || !a->workspace) return WK_E_ARG;
+  if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->out) || !aligned16(a->workspace)) return WK_E_ARG;
+  if (a->a_scale_mx && (reinterpret_cast<uintptr_t>(a->a_scale_mx) & 3)) return WK_E_ARG;
+  if (a->b_scale_mx && (reinterpret_cast<uintptr_t>(a->b_scale_mx) & 3)) return WK_E_ARG;
+  if ((a->q_mx == nullptr) != (a->s_mx == nullptr)) return WK_E_ARG;
+  if (a->q_mx && !aligned16(a->q_mx)) return WK_E_ARG;
+  if (a->workspace_bytes < wk_gemm_mxfp8_workspace_bytes(m, n, k)) return WK_E_ARG;
+  int* status = status_word();
+  if (!status) return WK_E_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  uint8_t* sfa = static_cast<uint8_t*>(a->workspace);
+  uint8_t* sfb = sfa + ((static_cast<int64_t>(m) * (k / 32) + 15) / 16) * 16;
+  int r = swizzle(a->a_scale_mx, sfa, m, k, st);
+  if (r) return r;
+  r = swizzle(a->b_scale_mx, sfb, n, k, st);
+  if (r) return r;
+
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k)};
+    const uint32_t box[2] = {BK, BM};
+    r = encode_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r) return r;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k)};
+    const uint32_t box[2] = {BK, BN};
+    r = encode_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r) return r;
+  }
+  GemmParams p;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.q_mx = static_cast<uint8_t*>(a->q_mx);
+  p.s_mx = static_cast<uint8_t*>(a->s_mx);
+  p.sfa = sfa;
+  p.sfb = sfb;
+  p.scale_a = a->scale_a;
+  p.scale_b = a->scale_b;
+  p.M = m;
+  p.N = n;
+  p.K = k;
+  p.group_m = 8;
+  p.status = status;
+  if (allow_smem(reinterpret_cast<const void*>(gemm_mxfp8_kernel), SMEM_BYTES)) return WK_E_CUDA;
+  const int num_tiles = (m / BM) * ((n + BN - 1) / BN);
+  const int sms = sm_count();
+  if (sms <= 0) return WK_E_CUDA;
+  const int grid = num_tiles < sms ? num_tiles : sms;
+  gemm_mxfp8_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
+}

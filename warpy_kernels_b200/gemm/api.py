@@ -7,6 +7,8 @@ setmaxnreg``) are accepted so existing call sites keep working; the sm_100a kern
 ignore them, except that ``bn`` and ``bk`` still define the divisibility the reference enforces.
 """
 
+import ctypes
+
 import torch
 
 from .. import _lib
@@ -15,6 +17,16 @@ from ..utils import time_candidates
 
 _TYPES = {torch.bfloat16: "bf16", torch.float16: "f16"}
 BM = 128
+
+
+class _MxArgs(ctypes.Structure):
+    _fields_ = [
+        ("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("a_scale_mx", ctypes.c_void_p),
+        ("b_scale_mx", ctypes.c_void_p), ("scale_a", ctypes.c_void_p), ("scale_b", ctypes.c_void_p),
+        ("out", ctypes.c_void_p), ("q_mx", ctypes.c_void_p), ("s_mx", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64),
+        ("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32),
+    ]
 
 
 def _gemm_arch(a, fp8, act, accum, mx_in, mx_out):
@@ -159,7 +171,25 @@ def make_gemm(
             _lib.check(code, "gemm (bf16)")
 
     else:
-        raise NotImplementedError("fp8 gemm is being built")
+        ws_bytes = lib.wk_gemm_mxfp8_workspace_bytes(m, n, k)
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)  # re-tiled scale factors
+        args = _MxArgs()
+        args.a, args.b, args.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
+        args.a_scale_mx = a_scale_mx.data_ptr() if a_scale_mx is not None else None
+        args.b_scale_mx = b_scale_mx.data_ptr() if b_scale_mx is not None else None
+        args.scale_a = scale_a.data_ptr() if scale_a is not None else None
+        args.scale_b = scale_b.data_ptr() if scale_b is not None else None
+        args.q_mx = q_mx.data_ptr() if out_mx else None
+        args.s_mx = s_mx.data_ptr() if out_mx else None
+        args.workspace, args.workspace_bytes = workspace.data_ptr(), ws_bytes
+        args.m, args.n, args.k = m, n, k
+        keep = (a, b, a_scale_mx, b_scale_mx, scale_a, scale_b, workspace)
+
+        def launch():
+            with torch.cuda.device(dev):
+                code = lib.wk_gemm_mxfp8(ctypes.byref(args), _lib.stream_ptr(dev))
+            _lib.check(code, "gemm (fp8)")
+            return keep
 
     mx = (q_mx, s_mx) if out_mx else ()
     return (launch, out, *mx)
