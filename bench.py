@@ -154,6 +154,28 @@ def make_gemm_bf16(dev, m, n, k, seed):
                 h2d=(ha.numel() + hb.numel()) * 2, d2h=hout.numel() * 2, tensors=(a, b, out))
 
 
+def make_gemm_mx(dev, m, n, k, seed):
+    import warpy_kernels as wk
+
+    g = torch.Generator(device=dev).manual_seed(seed)
+    a8, sa = wk.quantize_mx(torch.randn(m, k, device=dev, generator=g).bfloat16())
+    b8, sb = wk.quantize_mx(torch.randn(n, k, device=dev, generator=g).bfloat16())
+    launch, out = wk.make_gemm(a8, b8, a_scale_mx=sa, b_scale_mx=sb)
+    host = [x.view(torch.uint8).cpu().pin_memory() for x in (a8, b8, sa, sb)]
+    devb = [torch.empty_like(x.view(torch.uint8)) for x in (a8, b8, sa, sb)]
+    hout = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        for d_, h_ in zip(devb, host):
+            d_.copy_(h_, non_blocking=True)
+        o = wk.gemm(devb[0].view(torch.float8_e4m3fn), devb[1].view(torch.float8_e4m3fn), a_scale_mx=devb[2],
+                    b_scale_mx=devb[3])
+        hout.copy_(o, non_blocking=True)
+
+    return dict(step=launch, e2e_step=e2e_step, work=2.0 * m * n * k, bound="tensor", dtype="fp8", launches=3,
+                h2d=sum(h.numel() for h in host), d2h=hout.numel() * 2, tensors=(a8, b8, sa, sb, out))
+
+
 def make_quant(dev, m, k, seed):
     import warpy_kernels as wk
 
@@ -186,6 +208,10 @@ WORKLOADS = {
                       make=lambda dev: make_gemm_bf16(dev, 2048, 2048, 2048, 0)),
     "gemm_bf16_8k": dict(desc="BF16 GEMM M=N=K=8192", unit="TFLOP/s",
                          make=lambda dev: make_gemm_bf16(dev, 8192, 8192, 8192, 0)),
+    "gemm_mx": dict(desc="MXFP8 GEMM M8192 N14336 K4096 (E8M0 scales on A and B)", unit="TFLOP/s",
+                    make=lambda dev: make_gemm_mx(dev, 8192, 14336, 4096, 0)),
+    "gemm_mx_b": dict(desc="MXFP8 GEMM M8192 N4096 K14336 (E8M0 scales on A and B)", unit="TFLOP/s",
+                      make=lambda dev: make_gemm_mx(dev, 8192, 4096, 14336, 0)),
     "quant": dict(desc="MXFP8 quantiser [8192, 14336] bf16", unit="GB/s",
                   make=lambda dev: make_quant(dev, 8192, 14336, 0)),
 }
@@ -395,6 +421,8 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             base = "attn_fwd" if args.workload == "attn_fwd" else args.workload
             line["cpu_baseline"] = cpu_baseline(base if base in ("attn_fwd", "attn_gqa", "quant") else "gemm_bf16")
+            if args.workload.startswith("gemm_mx"):
+                line["cpu_baseline"]["sample"] += " (fp32 matmul of dequantised operands has the same cost)"
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
