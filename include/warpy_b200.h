@@ -31,6 +31,10 @@ extern "C" {
 #define WK_E_ARG (-1)       /* a size, stride, alignment or pointer was rejected */
 #define WK_E_CUDA (-2)      /* the CUDA runtime or driver returned an error */
 #define WK_E_UNSUPPORTED (-3) /* the device is not compute capability 10.x */
+#define WK_E_TOO_LARGE (-4) /* the problem does not fit the fixed scratch of a no-allocation entry point */
+
+/* Size of the scratch array built into the library for wk_gemm_mxfp8_noalloc. */
+#define WK_NOALLOC_SCRATCH_BYTES (8ll << 20)
 
 /* dtype codes */
 #define WK_BF16 0
@@ -98,6 +102,37 @@ typedef struct {
 
 int64_t wk_gemm_mxfp8_workspace_bytes(int m, int n, int k);
 int wk_gemm_mxfp8(const wk_gemm_mx_args* args, void* stream);
+
+/* MXFP8 GEMM for callers that cannot allocate device memory.  No counterpart in the
+ * reference (its host API allocates its workspaces with torch on every make_gemm).
+ *
+ * Who needs it: code that runs inside a process whose GPU memory has already been
+ * handed out in full -- an inference server that reserves the whole card for its own
+ * pool at start-up, a plugin that is only given pre-made buffers -- or on a latency
+ * path where a cudaMalloc (which may synchronise the device, and may simply fail) is
+ * not acceptable.  Such a caller still passes a, b, the scale tensors and the outputs,
+ * but no workspace: `workspace` and `workspace_bytes` of the argument block are
+ * ignored, and the re-tiled scale factors go into an array of WK_NOALLOC_SCRATCH_BYTES
+ * bytes that is part of the library image on every GPU that loads it.  This entry
+ * point calls no cudaMalloc, cudaFree or other allocating routine, not even for the
+ * status word: wk_gemm_mxfp8_noalloc_status() reads its own.
+ *
+ * Limits and rules
+ *  - (M + N) * K / 32 + 32 must not exceed WK_NOALLOC_SCRATCH_BYTES (see
+ *    wk_gemm_mxfp8_noalloc_max_bytes()); larger problems return WK_E_TOO_LARGE and
+ *    launch nothing.
+ *  - The first call on a device looks up the array's device address; make that first
+ *    call on each device before starting any stream capture.
+ *  - All calls on a device share the one array.  Each call rewrites every byte it
+ *    later reads, so earlier contents never leak into a result, but two calls that
+ *    can run at the same time on the GPU (different streams) race on it: keep calls
+ *    to this entry point on one stream, or order them with events.
+ * Otherwise identical to wk_gemm_mxfp8 (same kernels, bit-identical results). */
+int wk_gemm_mxfp8_noalloc(const wk_gemm_mx_args* args, void* stream);
+int64_t wk_gemm_mxfp8_noalloc_max_bytes(void);
+/* wk_status() for the no-allocation entry point: synchronises, returns and clears the
+ * status word its kernels report to. */
+int wk_gemm_mxfp8_noalloc_status(void);
 
 /* FP8 attention forward.  Replaces the launch built in
  * warpy_kernels/attn/fwd_api.py:344-390 (kernel: warpy_kernels/attn/fwd_base.py:670-758 with the

@@ -27,6 +27,9 @@ SIGNATURES = {
     "wk_attn_fwd_fp8": (_i32, [_ptr, _ptr]),
     "wk_gemm_mxfp8_workspace_bytes": (_i64, [_i32, _i32, _i32]),
     "wk_gemm_mxfp8": (_i32, [_ptr, _ptr]),
+    "wk_gemm_mxfp8_noalloc": (_i32, [_ptr, _ptr]),
+    "wk_gemm_mxfp8_noalloc_max_bytes": (_i64, []),
+    "wk_gemm_mxfp8_noalloc_status": (_i32, []),
 }
 
 _lib = None

@@ -361,3 +361,126 @@ extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
   gemm_mxfp8_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(ta, tb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
 }
+
+// ---------------------------------------------------------------------------
+// Variant for callers that must not allocate device memory.
+// ---------------------------------------------------------------------------
+// The re-tiled scale factors live in a fixed array that is part of the loaded
+// module instead of a caller-provided workspace, and the status word is a module
+// variable too, so this entry point never calls cudaMalloc / cudaFree or any
+// allocating library routine.  Every GPU that loads the library carries the array
+// (WK_NOALLOC_SCRATCH_BYTES) until the process exits.
+//
+// In host code the names below are only handles for the runtime, not device
+// addresses; the real addresses are looked up once per device with
+// cudaGetSymbolAddress while that device is current, and those pointers are what
+// the kernels receive.
+namespace wk {
+namespace {
+
+constexpr int64_t kNoAllocScratchBytes = WK_NOALLOC_SCRATCH_BYTES;
+static __device__ __align__(256) uint8_t g_noalloc_scratch[kNoAllocScratchBytes];
+static __device__ int g_noalloc_status;
+
+constexpr int kNoAllocMaxDevices = 64;
+uint8_t* g_noalloc_scratch_ptr[kNoAllocMaxDevices] = {};
+int* g_noalloc_status_ptr[kNoAllocMaxDevices] = {};
+
+// Looks the two device addresses up on the first call made on a device.
+int noalloc_setup(int dev) {
+  if (g_noalloc_scratch_ptr[dev] && g_noalloc_status_ptr[dev]) return 0;
+  void* scratch = nullptr;
+  void* status = nullptr;
+  if (cudaGetSymbolAddress(&scratch, g_noalloc_scratch) != cudaSuccess || !scratch) return WK_E_CUDA;
+  if (cudaGetSymbolAddress(&status, g_noalloc_status) != cudaSuccess || !status) return WK_E_CUDA;
+  g_noalloc_scratch_ptr[dev] = static_cast<uint8_t*>(scratch);
+  g_noalloc_status_ptr[dev] = static_cast<int*>(status);
+  return 0;
+}
+
+}  // namespace
+}  // namespace wk
+
+extern "C" int64_t wk_gemm_mxfp8_noalloc_max_bytes(void) { return wk::kNoAllocScratchBytes; }
+
+extern "C" int wk_gemm_mxfp8_noalloc(const wk_gemm_mx_args* a, void* stream) {
+  using namespace wk;
+  if (!a) return WK_E_ARG;
+  const int m = a->m, n = a->n, k = a->k;
+  if (m < 0 || n < 0 || k < 0 || m % BM || n % 128 || k % BK) return WK_E_ARG;
+  if (m == 0 || n == 0) return 0;
+  if (k == 0) return WK_E_ARG;
+  if (!a->a || !a->b || !a->out) return WK_E_ARG;
+  if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->out)) return WK_E_ARG;
+  if (a->a_scale_mx && (reinterpret_cast<uintptr_t>(a->a_scale_mx) & 3)) return WK_E_ARG;
+  if (a->b_scale_mx && (reinterpret_cast<uintptr_t>(a->b_scale_mx) & 3)) return WK_E_ARG;
+  if ((a->q_mx == nullptr) != (a->s_mx == nullptr)) return WK_E_ARG;
+  if (a->q_mx && !aligned16(a->q_mx)) return WK_E_ARG;
+  // the fixed array bounds the problem size: (M + N) * K / 32 scale bytes must fit
+  if (wk_gemm_mxfp8_workspace_bytes(m, n, k) > kNoAllocScratchBytes) return WK_E_TOO_LARGE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return WK_E_CUDA;
+  int r = noalloc_setup(dev);
+  if (r) return r;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  uint8_t* sfa = g_noalloc_scratch_ptr[dev];
+  uint8_t* sfb = sfa + ((static_cast<int64_t>(m) * (k / 32) + 15) / 16) * 16;
+  // every atom the GEMM will read is rewritten here, so nothing of the previous call survives into this one
+  r = swizzle(a->a_scale_mx, sfa, m, k, st);
+  if (r) return r;
+  r = swizzle(a->b_scale_mx, sfb, n, k, st);
+  if (r) return r;
+
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k)};
+    const uint32_t box[2] = {BK, BM};
+    r = encode_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r) return r;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k)};
+    const uint32_t box[2] = {BK, BN};
+    r = encode_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r) return r;
+  }
+  GemmParams p;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.q_mx = static_cast<uint8_t*>(a->q_mx);
+  p.s_mx = static_cast<uint8_t*>(a->s_mx);
+  p.sfa = sfa;
+  p.sfb = sfb;
+  p.scale_a = a->scale_a;
+  p.scale_b = a->scale_b;
+  p.M = m;
+  p.N = n;
+  p.K = k;
+  p.group_m = 8;
+  p.status = g_noalloc_status_ptr[dev];
+  if (cudaFuncSetAttribute(reinterpret_cast<const void*>(gemm_mxfp8_kernel),
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    return WK_E_CUDA;
+  const int num_tiles = (m / BM) * ((n + BN - 1) / BN);
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    return WK_E_CUDA;
+  const int grid = num_tiles < sms ? num_tiles : sms;
+  gemm_mxfp8_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
+}
+
+extern "C" int wk_gemm_mxfp8_noalloc_status(void) {
+  using namespace wk;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return WK_E_CUDA;
+  if (noalloc_setup(dev)) return WK_E_CUDA;
+  if (cudaDeviceSynchronize() != cudaSuccess) return WK_E_CUDA;
+  int v = 0;
+  if (cudaMemcpy(&v, g_noalloc_status_ptr[dev], sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return WK_E_CUDA;
+  if (v != 0 && cudaMemset(g_noalloc_status_ptr[dev], 0, sizeof(int)) != cudaSuccess) return WK_E_CUDA;
+  return v;
+}

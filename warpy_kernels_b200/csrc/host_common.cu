@@ -137,6 +137,7 @@ const char* wk_error_string(int code) {
     case WK_E_ARG: return "argument rejected (size, stride, alignment or null pointer)";
     case WK_E_CUDA: return "CUDA runtime or driver error";
     case WK_E_UNSUPPORTED: return "device is not compute capability 10.x";
+    case WK_E_TOO_LARGE: return "problem too large for the library's fixed scratch array";
     case wk::WK_ERR_TIMEOUT_LOAD: return "kernel gave up waiting for a TMA load";
     case wk::WK_ERR_TIMEOUT_EMPTY: return "kernel gave up waiting for a free pipeline stage";
     case wk::WK_ERR_TIMEOUT_MMA: return "kernel gave up waiting for the tensor core";
