@@ -202,6 +202,8 @@ def make_quant(dev, m, k, seed):
 WORKLOADS = {
     "attn_fwd": dict(desc="FP8 causal attention forward B4 H32 N4096 d128", unit="TFLOP/s",
                      make=lambda dev: make_attn(dev, 4, 32, 32, 4096, 128, True, 0)),
+    "attn_fwd_small": dict(desc="FP8 causal attention forward B2 H32 N4096 d128 (profiling size)", unit="TFLOP/s",
+                           make=lambda dev: make_attn(dev, 2, 32, 32, 4096, 128, True, 0)),
     "attn_gqa": dict(desc="FP8 GQA causal attention forward B1 Hq64 Hkv8 N32768 d128", unit="TFLOP/s",
                      make=lambda dev: make_attn(dev, 1, 64, 8, 32768, 128, True, 0)),
     "gemm_bf16": dict(desc="BF16 GEMM M=N=K=2048", unit="TFLOP/s",
@@ -419,7 +421,7 @@ def main():
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
-            base = "attn_fwd" if args.workload == "attn_fwd" else args.workload
+            base = "attn_fwd" if args.workload.startswith("attn_fwd") else args.workload
             line["cpu_baseline"] = cpu_baseline(base if base in ("attn_fwd", "attn_gqa", "quant") else "gemm_bf16")
             if args.workload.startswith("gemm_mx"):
                 line["cpu_baseline"]["sample"] += " (fp32 matmul of dequantised operands has the same cost)"

@@ -7,19 +7,25 @@
 //   warp 1      allocates 256 TMEM columns (S: 0..127, O: 128..255) and issues
 //               tcgen05.mma kind::f8f6f4:  S = Q.K^T (both K-major from shared memory),
 //               O += P.V (P read from TMEM, V MN-major from shared memory)
-//   warps 2-5   softmax, one thread per query row: read S from TMEM, running maximum
-//               with a lazily refreshed reference (O and the row sum are rescaled
-//               only when the maximum grew by more than 2^4), P = 2^(S.beta - m_ref + 4)
-//               rounded to e4m3 and written back over the S columns, fp32 row sums;
+//   warps 2-5   softmax, one thread per query row: read S from TMEM, P as MXFP8 (e4m3
+//               codes written back over the S columns plus one power-of-two scale per
+//               row and 32 keys, staged through shared memory), fp32 row sums;
 //               finally O . v_descale / l -> bf16, lse (base 2) and pmax
 //
 // Numerics follow the reference's forward (warpy_kernels/attn/fwd_base.py:297-360,
 // 939-988; fwd_sm120.py:93-136): logits in base 2 with beta = softmax_scale .
-// q_descale . k_descale . log2(e), bottom-right aligned causal mask, P stored with a
-// power-of-two offset so that small probabilities stay above e4m3 subnormals, lse =
-// m_ref + log2(l) - offset, pmax = 2^(m_true - lse), empty rows give out = 0,
-// lse = +inf, pmax = 0.  The offset here is 2^4 instead of the reference's 2^8: the
-// stale reference maximum may trail the true one by 2^4, and 2^(4+4) <= 448.
+// q_descale . k_descale . log2(e), bottom-right aligned causal mask, lse =
+// m_ref + log2(l), pmax = 2^(m_true - lse), empty rows give out = 0, lse = +inf,
+// pmax = 0.  Where the reference quantises P against each 128-key tile's own maximum
+// ("tile_local") and rescales O by the ratio of consecutive references, this kernel
+// quantises every block of 32 keys against its own exponent e_blk = m_ref + k, k the
+// smallest integer with e_blk >= block maximum,
+//   P8 = e4m3(2^(s.beta - e_blk + 8)),   scale = 2^(k - 8),
+// and lets the block-scaled MMA (kind::mxf8f6f4) apply the scale, so O accumulates in
+// the units of one reference m_ref per row.  m_ref is the row's running maximum at its
+// last refresh: the largest probability of the row is then stored exactly (2^8), as in
+// the reference.  It is refreshed (with a rescale of O and l) only when the running
+// maximum has grown by more than a factor of two.
 //
 // Tensor-core bound: 4 . B . Hq . Nq . Nk . d flops (half of that when causal).
 #include <math.h>
@@ -39,9 +45,15 @@ constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 256;
 constexpr int S_COL = 0;
 constexpr int O_COL = 128;
-constexpr float P_OFFSET = 4.0f;   // log2 of the factor P is stored with
-constexpr float RESCALE_TAU = 4.0f;  // refresh the reference maximum when it trails by more than this
-constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 1024 + 256;
+constexpr int P_OFFSET = 8;          // a block's largest P is stored in (2^7, 2^8]
+constexpr float RESCALE_TAU = 1.0f;   // refresh the row reference when the maximum outgrew it by more than this (log2)
+constexpr int SF_BYTES = 512;        // one scale-factor atom: 128 rows x 4 blocks of 32 keys
+constexpr int SFA_COL = 64;          // TMEM columns (inside the consumed part of S) the scales are copied to
+constexpr int SFB_COL = 68;
+constexpr int SFA_LO_COL = 72;       // scales of the residual term
+constexpr int PLO_COL = 32;          // residual P codes (S columns 32..63)
+constexpr int RESID_MAX_TILES = 4;   // query blocks that see at most this many key tiles carry the residual term
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 3 * SF_BYTES + 1024 + 256;
 
 struct FwdParams {
   __nv_bfloat16* out;
@@ -61,6 +73,10 @@ struct FwdParams {
   int* status;
 };
 
+// RESID: this instantiation handles the query blocks that see at most RESID_MAX_TILES key tiles and carries P
+// as two e4m3 terms; the other instantiation handles all other blocks.  Both are launched on the full grid and
+// a CTA leaves at once when the block is not of its kind.
+template <bool RESID>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FwdParams p) {
@@ -69,7 +85,10 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t q_smem = smem_base;
   const uint32_t k_smem = smem_base + TILE_BYTES;
   const uint32_t v_smem = k_smem + KV_STAGES * TILE_BYTES;
-  const uint32_t bar_base = v_smem + KV_STAGES * TILE_BYTES;
+  const uint32_t sfa_smem = v_smem + KV_STAGES * TILE_BYTES;  // P scales of the current tile
+  const uint32_t sfb_smem = sfa_smem + SF_BYTES;              // unit scales for V
+  const uint32_t sfa_lo_smem = sfb_smem + SF_BYTES;           // P residual scales
+  const uint32_t bar_base = sfa_lo_smem + SF_BYTES;
   const uint32_t q_full = bar_base;
   auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto k_empty = [&](int s) { return bar_base + 8u * (1 + KV_STAGES + s); };
@@ -98,6 +117,10 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const int last_key = last_row + shift;  // may be negative
     n_tiles = last_key < 0 ? 0 : min(n_tiles, last_key / BN + 1);
   }
+  // With few keys the e4m3 rounding of P does not average out; such blocks carry P as two e4m3 terms
+  // (value + 2^-4 . residual) at the price of a second P.V product.
+  if ((n_tiles <= RESID_MAX_TILES) != RESID) return;
+  constexpr bool resid = RESID;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -119,6 +142,10 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
+  if (threadIdx.x < SF_BYTES / 4) {
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfb_smem + 4u * threadIdx.x), "r"(0x7f7f7f7fu) : "memory");
+  }
+  fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -144,7 +171,6 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_qk = make_idesc(0, 0, 0, 0, BM, BN);
-      constexpr uint32_t idesc_pv = make_idesc(0, 0, 0, 1, BM, D);
       const uint32_t s_tmem = tmem_base + S_COL;
       const uint32_t o_tmem = tmem_base + O_COL;
       bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
@@ -168,10 +194,21 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // V tile: 128 keys (the MMA's K) x 128 bytes of head dim (the MMA's N): MN-major,
         // one 128-byte span wide, 8-key groups 1024 bytes apart, 32 keys per MMA = 4096 bytes
         const uint64_t v_desc = smem_desc_sw128(v_smem + s * TILE_BYTES, 16, 1024);
+        tmem_cp_32x128b_warpx4(s_tmem + SFA_COL, smem_desc_plain(sfa_smem, 16, 128));
+        tmem_cp_32x128b_warpx4(s_tmem + SFB_COL, smem_desc_plain(sfb_smem, 16, 128));
 #pragma unroll
         for (int k = 0; k < BN / 32; ++k) {
-          // P: 32 e4m3 per K step = 8 TMEM columns
-          mma_f8_ts(o_tmem, s_tmem + 8 * k, v_desc + 256 * k, idesc_pv, (j | k) != 0);
+          // P: 32 e4m3 per K step = 8 TMEM columns; scale byte k of the row's scale word
+          mma_mxf8_ts(o_tmem, s_tmem + 8 * k, v_desc + 256 * k, make_idesc_mx_major(BM, D, k, 0, 0, 1),
+                      s_tmem + SFA_COL, s_tmem + SFB_COL, (j | k) != 0);
+        }
+        if (resid) {
+          tmem_cp_32x128b_warpx4(s_tmem + SFA_LO_COL, smem_desc_plain(sfa_lo_smem, 16, 128));
+#pragma unroll
+          for (int k = 0; k < BN / 32; ++k) {
+            mma_mxf8_ts(o_tmem, s_tmem + PLO_COL + 8 * k, v_desc + 256 * k,
+                        make_idesc_mx_major(BM, D, k, 0, 0, 1), s_tmem + SFA_LO_COL, s_tmem + SFB_COL, 1);
+          }
         }
         tc_commit(v_empty(s));
         if (j == n_tiles - 1) tc_commit(o_full);
@@ -189,7 +226,9 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const float beta = p.softmax_scale * p.q_descale[sc] * p.k_descale[sc] * 1.4426950408889634f;
     const float sv = p.v_descale[sc];
     const int row_limit = p.causal ? row + shift : nk - 1;  // last visible key of this row
-    float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
+    // m_ref: reference exponent of this row (O and l are in units of 2^-m_ref)
+    // l: exact row sum (for lse and pmax); lq: sum of the rounded P the MMA multiplies V with (normaliser of O)
+    float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f, lq = 0.f;
     bool ok = true;
 
     for (int j = 0; j < n_tiles; ++j) {
@@ -202,30 +241,45 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const bool tile_masked = (key0 + BN > nk) || (p.causal && key0 + BN - 1 > m0 + shift);
       const int limit = min(row_limit, nk - 1) - key0;  // columns > limit are masked
 
-      // pass 1: row maximum of the raw scores
-      float tmax = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(s_tmem + c * 32, v);
-        tc_wait_ld();
-        if (tile_masked) {
+      // the whole row of S: 128 raw scores
+      uint32_t sraw[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, sraw[c]);
+      tc_wait_ld();
+      if (tile_masked) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i <= limit) tmax = fmaxf(tmax, __uint_as_float(v[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) tmax = fmaxf(tmax, __uint_as_float(v[i]));
-        }
+            if (c * 32 + i > limit) sraw[c][i] = 0xff800000u;  // -inf
       }
-      const float t = beta >= 0.f ? tmax * beta : -INFINITY;  // beta < 0 is rejected on the host
+      // maxima per block of 32 keys
+      float cm[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float a0 = fmaxf(__uint_as_float(sraw[c][0]), __uint_as_float(sraw[c][1]));
+        float a1 = fmaxf(__uint_as_float(sraw[c][2]), __uint_as_float(sraw[c][3]));
+        float a2 = fmaxf(__uint_as_float(sraw[c][4]), __uint_as_float(sraw[c][5]));
+        float a3 = fmaxf(__uint_as_float(sraw[c][6]), __uint_as_float(sraw[c][7]));
+#pragma unroll
+        for (int i = 8; i < 32; i += 8) {
+          a0 = max3(a0, __uint_as_float(sraw[c][i + 0]), __uint_as_float(sraw[c][i + 1]));
+          a1 = max3(a1, __uint_as_float(sraw[c][i + 2]), __uint_as_float(sraw[c][i + 3]));
+          a2 = max3(a2, __uint_as_float(sraw[c][i + 4]), __uint_as_float(sraw[c][i + 5]));
+          a3 = max3(a3, __uint_as_float(sraw[c][i + 6]), __uint_as_float(sraw[c][i + 7]));
+        }
+        cm[c] = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * beta;  // beta > 0 (checked on the host)
+      }
+      const float t = fmaxf(fmaxf(cm[0], cm[1]), fmaxf(cm[2], cm[3]));
       m_true = fmaxf(m_true, t);
-      const bool need = t > m_ref + RESCALE_TAU || (m_ref == -INFINITY && t > -INFINITY);
+      const bool need = t > -INFINITY && (m_ref == -INFINITY || t > m_ref + RESCALE_TAU);
       float corr = 1.f;
       if (need) {
-        corr = m_ref == -INFINITY ? 0.f : ex2_approx(m_ref - t);
+        const float m_new = t;
+        corr = m_ref == -INFINITY ? 0.f : exp2f(m_ref - m_new);
         l *= corr;
-        m_ref = t;
+        lq *= corr;
+        m_ref = m_new;
       }
       if (j > 0 && __any_sync(0xffffffffu, need)) {
         // the previous P.V has completed (s_full tracks every earlier MMA), so O is quiescent
@@ -241,26 +295,71 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         tc_wait_st();
       }
 
-      // pass 2: P = 2^(s.beta - m_ref + offset) -> e4m3, written over the S columns already consumed
-      const float bias = (m_ref == -INFINITY ? 0.f : -m_ref) + P_OFFSET;
-#pragma unroll 1
+      // P as MXFP8: per block of 32 keys an integer exponent e_blk >= block maximum
+      uint32_t sf_word = 0, sf_word_lo = 0;
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(s_tmem + c * 32, v);
-        tc_wait_ld();
-        float pr[32];
+        const bool live = cm[c] > -INFINITY;
+        const float kf = live ? ceilf(cm[c] - m_ref) : 0.f;  // block exponent relative to the row reference
+        const float bias = live ? (static_cast<float>(P_OFFSET) - kf) - m_ref : 0.f;
+        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+        uint32_t hsum0 = 0, hsum1 = 0;  // f16x2 partial sums of the rounded codes
+        uint32_t w[8], wl[8];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = ex2_approx(fmaf(__uint_as_float(v[i]), beta, bias));
-          if (tile_masked && c * 32 + i > limit) e = 0.f;
-          pr[i] = e;
-          l += e;
+        for (int i = 0; i < 8; ++i) {
+          float p0 = fmaf(__uint_as_float(sraw[c][4 * i + 0]), beta, bias);
+          float p1 = fmaf(__uint_as_float(sraw[c][4 * i + 1]), beta, bias);
+          float p2 = fmaf(__uint_as_float(sraw[c][4 * i + 2]), beta, bias);
+          float p3 = fmaf(__uint_as_float(sraw[c][4 * i + 3]), beta, bias);
+          p0 = ex2_approx(p0);
+          p1 = ex2_approx(p1);
+          p2 = ex2_approx(p2);
+          p3 = ex2_approx(p3);
+          const uint16_t h01 = cvt_e4m3x2(p0, p1), h23 = cvt_e4m3x2(p2, p3);
+          w[i] = static_cast<uint32_t>(h01) | (static_cast<uint32_t>(h23) << 16);
+          acc0 += p0;
+          acc1 += p1;
+          acc2 += p2;
+          acc3 += p3;
+          if (!resid) {
+            // the normaliser of O sums what the MMA will see: the rounded codes, exact in f16
+            hsum0 = hadd2(hsum0, e4m3x2_to_f16x2(h01));
+            hsum1 = hadd2(hsum1, e4m3x2_to_f16x2(h23));
+          } else {
+            // second e4m3 term: what the first rounding lost, times 2^4
+            float q0, q1, q2, q3;
+            unpack_e4m3x2(h01, q0, q1);
+            unpack_e4m3x2(h23, q2, q3);
+            wl[i] = pack_e4m3x4((p0 - q0) * 16.f, (p1 - q1) * 16.f, (p2 - q2) * 16.f, (p3 - q3) * 16.f);
+          }
         }
-        uint32_t w[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) w[i] = pack_e4m3x4(pr[4 * i], pr[4 * i + 1], pr[4 * i + 2], pr[4 * i + 3]);
         tmem_st8(s_tmem + c * 8, w);
+        if (resid) tmem_st8(s_tmem + PLO_COL + c * 8, wl);
+        // scale of this block relative to the row reference: 2^(e_blk - offset - m_ref)
+        int sf = live ? 127 + static_cast<int>(kf) - P_OFFSET : 0;
+        sf = min(max(sf, 0), 254);
+        const float blk_scale = __uint_as_float(static_cast<uint32_t>(sf) << 23);
+        const float blk_sum = (acc0 + acc1) + (acc2 + acc3);
+        if (live) l = fmaf(blk_sum, blk_scale, l);
+        if (!resid) {
+          float s0, s1, s2, s3;
+          f16x2_to_float2(hsum0, s0, s1);
+          f16x2_to_float2(hsum1, s2, s3);
+          if (live) lq = fmaf((s0 + s1) + (s2 + s3), blk_scale, lq);
+        } else {
+          if (live) lq = fmaf(blk_sum, blk_scale, lq);
+        }
+        sf_word |= static_cast<uint32_t>(sf) << (8 * c);
+        sf_word_lo |= static_cast<uint32_t>(max(sf - 4, 0)) << (8 * c);
       }
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfa_smem + (r % 32) * 16 + (r / 32) * 4), "r"(sf_word)
+                   : "memory");
+      if (resid) {
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfa_lo_smem + (r % 32) * 16 + (r / 32) * 4),
+                     "r"(sf_word_lo)
+                     : "memory");
+      }
+      fence_proxy_async_smem();
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(p_full);
@@ -271,7 +370,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     if (ok) {
       tc_fence_after();
       const bool empty = !(l > 0.f);
-      const float inv = empty ? 0.f : sv / l;
+      const float inv = empty ? 0.f : sv / lq;
       __nv_bfloat16* out_row =
           p.out + b * p.out_stride_b + hq * p.out_stride_h + static_cast<int64_t>(row) * p.out_stride_n;
 #pragma unroll 1
@@ -299,7 +398,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
       if (p.write_lse && row < p.Nq) {
         const int64_t off = b * p.lse_stride_b + hq * p.lse_stride_h + row;
-        const float lse = empty ? INFINITY : m_ref + log2f(l) - P_OFFSET;
+        const float lse = empty ? INFINITY : m_ref + log2f(l);
         p.lse[off] = p.lse_natural ? lse * 0.6931471805599453f : lse;
         p.pmax[off] = empty ? 0.f : exp2f(m_true - lse);
       }
@@ -383,8 +482,14 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
   p.softmax_scale = a->softmax_scale;
   p.status = status;
 
-  if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel), SMEM_BYTES)) return WK_E_CUDA;
+  if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<false>), SMEM_BYTES)) return WK_E_CUDA;
+  if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<true>), SMEM_BYTES)) return WK_E_CUDA;
   dim3 grid((a->Nq + BM - 1) / BM, a->Hq, a->B);
-  attn_fwd_fp8_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // long blocks first, then the few short ones that need the two-term P
+  attn_fwd_fp8_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
+  if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+  attn_fwd_fp8_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
 }
+

@@ -75,10 +75,36 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
 // Wait for the phase with the given parity to complete.  Gives up after
 // WK_WAIT_LIMIT_NS, records `code` in *status and returns false; the caller must
 // then leave its loop and fall through to the kernel's common teardown.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code,
+                                          bool poll = false) {
+  if (poll) {
+    const unsigned long long t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+      for (int i = 0; i < 1024; ++i) {
+        if (mbar_test_wait(bar, parity)) return true;
+      }
+      if (globaltimer_ns() - t0 > WK_WAIT_LIMIT_NS) {
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   for (;;) {
@@ -95,8 +121,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
 
 // Same, for a whole converged warp: every lane gets the same answer, so warp-wide
 // (.sync.aligned) instructions after it stay legal.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int* status, int code) {
-  const bool ok = mbar_wait(bar, parity, status, code);
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int* status, int code,
+                                               bool poll = false) {
+  const bool ok = mbar_wait(bar, parity, status, code, poll);
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -249,6 +276,13 @@ __device__ __forceinline__ uint32_t make_idesc_mx(uint32_t m, uint32_t n, uint32
          ((m >> 4) << 24) | (a_sf_id << 29);
 }
 
+// Same with explicit operand majors (0 = K-major, 1 = MN-major).
+__device__ __forceinline__ uint32_t make_idesc_mx_major(uint32_t m, uint32_t n, uint32_t a_sf_id,
+                                                        uint32_t b_sf_id, uint32_t a_major,
+                                                        uint32_t b_major) {
+  return make_idesc_mx(m, n, a_sf_id, b_sf_id) | (a_major << 15) | (b_major << 16);
+}
+
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                            uint32_t idesc, uint32_t accumulate) {
@@ -289,6 +323,18 @@ __device__ __forceinline__ void mma_mxf8_ss(uint32_t d_tmem, uint64_t a_desc, ui
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
       : "memory");
 }
+// Block-scaled, A operand from TMEM.
+__device__ __forceinline__ void mma_mxf8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], [%1], %2, %3, [%4], "
+      "[%5], p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
 // Copy 32 rows x 16 bytes from shared memory into 4 TMEM columns of every 32-lane
 // quarter (the layout block-scale factors are read from).
 __device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
@@ -309,10 +355,38 @@ __device__ __forceinline__ uint16_t cvt_e4m3x2(float lo, float hi) {
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
   return static_cast<uint32_t>(cvt_e4m3x2(a, b)) | (static_cast<uint32_t>(cvt_e4m3x2(c, d)) << 16);
 }
+// Two e4m3 codes (low byte first) -> two fp32 values (exact).
+__device__ __forceinline__ void unpack_e4m3x2(uint16_t codes, float& lo, float& hi) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(codes));
+  asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.f32.f16 %0, a;\n\tcvt.f32.f16 %1, b;\n\t}"
+      : "=f"(lo), "=f"(hi)
+      : "r"(h2));
+}
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t codes) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(codes));
+  return h2;
+}
+__device__ __forceinline__ uint32_t hadd2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ void f16x2_to_float2(uint32_t h2, float& lo, float& hi) {
+  asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.f32.f16 %0, a;\n\tcvt.f32.f16 %1, b;\n\t}"
+      : "=f"(lo), "=f"(hi)
+      : "r"(h2));
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
