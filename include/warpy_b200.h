@@ -175,6 +175,48 @@ typedef struct {
 
 int wk_attn_fwd_fp8(const wk_attn_fwd_args* args, void* stream);
 
+/* FP8 attention backward.  Replaces the launches of warpy_kernels/attn/bwd_api.py:381-398
+ * (BwdPrep warpy_kernels/attn/bwd_common.py:23-266, AttnBwdSm120 warpy_kernels/attn/bwd_sm120.py:38-1202,
+ * BwdDqPost warpy_kernels/attn/bwd_common.py:307-403).
+ *   q [B,Hq,Nq,d], k,v [B,Hkv,Nk,d]  e4m3, strides as in wk_attn_fwd_args
+ *   out, dout [B,Hq,Nq,d] bf16, element strides of (B, H, N) multiples of 4, last dim contiguous,
+ *       base 8-byte aligned
+ *   lse   fp32 base-2 log-sum-exp of the forward (+inf for rows without a visible key),
+ *       element strides lse_strides = (B, H)
+ *   dq [B,Hq,Nq,d], dk, dv [B,Hkv,Nk,d]  bf16 contiguous, 16-byte aligned: gradients with
+ *       respect to the dequantised q, k, v
+ *   workspace: scratch of wk_attn_bwd_fp8_workspace_bytes(B, Hq, Nq) bytes, 16-byte aligned
+ *       (the e4m3 copy of dout and one 16-byte record per query row)
+ * d == 128, Hq % Hkv == 0, softmax_scale > 0. */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* out;
+  const void* dout;
+  const float* lse;
+  const float* q_descale;
+  const float* k_descale;
+  const float* v_descale;
+  void* dq;
+  void* dk;
+  void* dv;
+  void* workspace;
+  int64_t workspace_bytes;
+  int64_t q_strides[3];
+  int64_t k_strides[3];
+  int64_t v_strides[3];
+  int64_t out_strides[3];
+  int64_t dout_strides[3];
+  int64_t lse_strides[2];
+  int32_t B, Hq, Hkv, Nq, Nk, d;
+  int32_t causal;
+  float softmax_scale;
+} wk_attn_bwd_args;
+
+int64_t wk_attn_bwd_fp8_workspace_bytes(int B, int Hq, int Nq);
+int wk_attn_bwd_fp8(const wk_attn_bwd_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,132 @@
+"""GPU: FP8 attention backward against the fp32 oracle (autograd through the reference's attention).
+
+Tolerances: north star (cosine >= 0.995 for dq, dk, dv) and the reference's gate (rel-L2 <= 8e-2,
+``tests/attn/test_grad.py:19``).
+"""
+
+import os
+
+import pytest
+import torch
+
+from oracle import reference_math as R
+from tests.helpers import hard_inputs, load_golden, randn_qkv
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = ["attn_mha_causal", "attn_gqa_ragged_causal", "attn_gqa_noncausal", "attn_short_q_causal"]
+# d = 128 shapes of the reference's gradient test (tests/attn/test_grad.py) plus ragged / GQA / Nq != Nk cases
+SHAPES = [
+    (1, 1, 1, 128, 128, 128),
+    (2, 4, 2, 1000, 1000, 128),
+    (1, 2, 2, 512, 1024, 128),
+    (1, 2, 1, 512, 128, 128),
+    (1, 8, 2, 384, 640, 128),
+]
+
+
+def check_grads(got, want):
+    for name, g, w in zip(("dq", "dk", "dv"), got, want):
+        g, w = g.float().cpu(), w.float().cpu()
+        assert not torch.isnan(g).any().item(), f"{name} contains NaN"
+        assert R.cosine(g, w) >= 0.995, (name, R.cosine(g, w))
+        assert R.rel_l2(g, w) <= 8e-2, (name, R.rel_l2(g, w))
+
+
+@pytest.mark.parametrize("name", GOLDEN)
+def test_against_reference_fixture(cuda, golden_dir, name):
+    from warpy_kernels import attn_bwd, attn_fwd
+
+    t = load_golden(os.path.join(golden_dir, f"{name}.npz"), cuda)
+    args = (t["q8"], t["k8"], t["v8"])
+    scales = (t["sq"], t["sk"], t["sv"])
+    out, lse, pmax = attn_fwd(*args, *scales, causal=t["causal"])
+    dq, dk, dv = attn_bwd(*args, out, lse, pmax, t["dout"], *scales, causal=t["causal"])
+    assert dq.shape == t["q8"].shape and dk.shape == t["k8"].shape and dv.dtype == torch.bfloat16
+    check_grads((dq, dk, dv), (t["dq"], t["dk"], t["dv"]))
+
+
+def _oracle_grads(q8, k8, v8, sq, sk, sv, dout, causal):
+    qd, kd, vd = [x.requires_grad_() for x in R.dequantize_qkv(q8, k8, v8, sq, sk, sv)]
+    out, _ = R.attention_reference(qd, kd, vd, causal)
+    out.backward(dout.float())
+    return qd.grad, kd.grad, vd.grad
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_reference_shapes(cuda, shape, causal):
+    from warpy_kernels import attn_bwd, attn_fwd
+
+    q, k, v = randn_qkv(*shape, device=cuda)
+    q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+    dout = torch.randn(q.shape, device=cuda, generator=torch.Generator(device=cuda).manual_seed(7)).bfloat16()
+    out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=causal)
+    got = attn_bwd(q8, k8, v8, out, lse, pmax, dout, sq, sk, sv, causal=causal)
+    check_grads(got, _oracle_grads(q8, k8, v8, sq, sk, sv, dout, causal))
+
+
+def test_repeat_is_bit_identical(cuda):
+    """Four runs: dK and dV bit-identical ("else a race", ``tests/attn/test_grad.py:108-135``); dQ too, since this
+    backward has no atomics."""
+    from warpy_kernels import attn_bwd, attn_fwd
+
+    q, k, v = randn_qkv(1, 4, 2, 640, 640, 128, seed=3, device=cuda)
+    q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+    dout = torch.randn(q.shape, device=cuda).bfloat16()
+    out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
+    first = attn_bwd(q8, k8, v8, out, lse, pmax, dout, sq, sk, sv, causal=True)
+    for _ in range(3):
+        again = attn_bwd(q8, k8, v8, out, lse, pmax, dout, sq, sk, sv, causal=True, deterministic=True)
+        for a, b in zip(first, again):
+            assert torch.equal(a, b)
+
+
+def test_hard_inputs_mean_over_seeds(cuda):
+    """Peaky softmax, log-normal dO row norms (``grad_hard``, ``tests/attn/test_grad.py``): mean error over 3 seeds."""
+    from warpy_kernels import attn_bwd, attn_fwd
+
+    errs = {"dq": 0.0, "dk": 0.0, "dv": 0.0}
+    for seed in range(3):
+        q, k, v, dout = hard_inputs(1, 4, 2, 512, 512, 128, seed=seed, device=cuda)
+        dout = dout.bfloat16()
+        q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+        out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
+        got = attn_bwd(q8, k8, v8, out, lse, pmax, dout, sq, sk, sv, causal=True)
+        want = _oracle_grads(q8, k8, v8, sq, sk, sv, dout, True)
+        for name, g, w in zip(errs, got, want):
+            errs[name] += R.rel_l2(g, w) / 3
+    assert max(errs.values()) <= 8e-2, errs
+
+
+def test_strided_inputs_and_float_dout(cuda):
+    from warpy_kernels import attn_bwd, attn_fwd
+
+    B, H, N, d = 2, 4, 300, 128
+    q, k, v = randn_qkv(B, H, H, N, N, d, seed=5, device=cuda)
+    q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+    dout = torch.randn(q.shape, device=cuda)
+    out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
+    base = attn_bwd(q8, k8, v8, out, lse, pmax, dout.bfloat16(), sq, sk, sv, causal=True)
+    tq, tk, tv = [x.transpose(1, 2).contiguous().transpose(1, 2) for x in (q8, k8, v8)]
+    tout = out.transpose(1, 2).contiguous().transpose(1, 2)
+    got = attn_bwd(tq, tk, tv, tout, lse, pmax, dout, sq, sk, sv, causal=True)  # float32 dout is converted
+    for a, b in zip(base, got):
+        assert torch.equal(a, b)
+
+
+def test_validation_errors(cuda):
+    from warpy_kernels import attn_bwd
+
+    q = torch.zeros(1, 2, 128, 128, device=cuda).to(torch.float8_e4m3fn)
+    kv = torch.zeros(1, 1, 128, 128, device=cuda).to(torch.float8_e4m3fn)
+    o = torch.zeros(1, 2, 128, 128, device=cuda, dtype=torch.bfloat16)
+    l = torch.zeros(1, 2, 128, device=cuda)
+    with pytest.raises(NotImplementedError):
+        attn_bwd(q, kv, kv, o, l, l, o, seqused_k=torch.ones(1, device=cuda, dtype=torch.int32))
+    with pytest.raises(ValueError):
+        attn_bwd(q, kv, kv, o[:, :1], l, l, o)
+    with pytest.raises(ValueError):
+        attn_bwd(q, kv, kv, o, l[:, :, :64], l, o)
+    with pytest.raises(ValueError):
+        attn_bwd(q, kv.bfloat16(), kv, o, l, l, o)

@@ -25,6 +25,8 @@ SIGNATURES = {
     "wk_quantize_mx": (_i32, [_ptr, _i32, _i64, _i64, _i64, _ptr, _ptr, _ptr]),
     "wk_gemm_bf16": (_i32, [_ptr, _ptr, _ptr, _i32, _i32, _i32, _ptr]),
     "wk_attn_fwd_fp8": (_i32, [_ptr, _ptr]),
+    "wk_attn_bwd_fp8_workspace_bytes": (_i64, [_i32, _i32, _i32]),
+    "wk_attn_bwd_fp8": (_i32, [_ptr, _ptr]),
     "wk_gemm_mxfp8_workspace_bytes": (_i64, [_i32, _i32, _i32]),
     "wk_gemm_mxfp8": (_i32, [_ptr, _ptr]),
     "wk_gemm_mxfp8_noalloc": (_i32, [_ptr, _ptr]),

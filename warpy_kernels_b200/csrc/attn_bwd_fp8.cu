@@ -1,0 +1,722 @@
+// FP8 (e4m3) flash-attention backward for sm_100a, head dimension 128.
+//
+// Gradients with respect to the dequantised q, k, v (q = q_descale . q8 and so on):
+//   S = alpha . q k^T,  P = softmax(S) = 2^(S . log2e - L)   (L: the forward's base-2 lse)
+//   dV = P^T dO,  dP = dO v^T,  D = rowsum(dO * O),  dS = P * (dP - D),
+//   dQ = alpha . dS k,  dK = alpha . dS^T q
+// as in the reference's backward (warpy_kernels/attn/bwd_common.py:88-304, bwd_sm120.py:253-512):
+// every product runs on the tensor core in e4m3.  Three kernels:
+//
+//  1. attn_bwd_prep_kernel (HBM-bound): per query row, dO -> e4m3 with a power-of-two row
+//     scale g (as the MXFP8 quantiser picks it), D = sum(dO8 . g . O), and the row record
+//     (L, g, g . v_descale, D) the main kernels read.  The reference scales dO per
+//     (batch, kv head) and carries a second residual term (bwd_common.py:133-266); a scale per
+//     row keeps small rows precise without it.
+//  2. attn_bwd_dkdv_kernel: CTA = 128 keys of one (batch, kv head), K and V resident in shared
+//     memory, loop over the group's query heads and query tiles.  Per tile:
+//       S^T = K Q^T and dP^T = V dO8^T            (tcgen05.mma kind::f8f6f4, into TMEM)
+//       threads (one per key): P^T . g and dS^T as MXFP8 (e4m3 codes back into TMEM, one
+//                              power-of-two scale per key and 32 queries through smem)
+//       dV += (P g)^T dO8 and dK += dS^T Q8       (kind::mxf8f6f4, A from TMEM, B = the same
+//                                                  Q / dO8 tiles read MN-major)
+//     dV and dK stay in TMEM for the whole CTA (4 x 128 columns in use).
+//  3. attn_bwd_dq_kernel: CTA = 128 queries of one (batch, query head), loop over key tiles,
+//     recomputes S and dP, dQ += dS K in TMEM.  Recomputing instead of reducing dQ across
+//     key blocks costs two more products but needs no atomics, no fp32 dQ buffer, no
+//     post-pass, and is deterministic (the reference: bwd_sm120.py:742-756 red.global.add /
+//     bwd_common.py:307-403 post kernel).
+//
+// Tensor-core bound: 10 . B . Hq . Nq . Nk . d flops of algorithmic work (half when causal).
+#include <math.h>
+
+#include "common.cuh"
+#include "host_common.h"
+
+namespace wk {
+namespace {
+
+constexpr int BM = 128;  // queries per tile
+constexpr int BN = 128;  // keys per tile
+constexpr int D = 128;
+constexpr int TILE_BYTES = 128 * 128;
+constexpr int SF_BYTES = 512;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr float LOG2E = 1.4426950408889634f;
+
+// ---------------------------------------------------------------------------
+// 1. prep
+// ---------------------------------------------------------------------------
+struct PrepParams {
+  const __nv_bfloat16* dout;  // [B,Hq,Nq,D] with element strides
+  const __nv_bfloat16* out;
+  const float* lse;           // [B,Hq,*] base 2
+  const float* v_descale;     // [B,Hkv]
+  uint8_t* do8;               // [B,Hq,Nq,D] contiguous
+  float4* qstat;              // [B,Hq,Nq_pad]: (L, g, g*sv, D)
+  int64_t do_sb, do_sh, do_sn;
+  int64_t o_sb, o_sh, o_sn;
+  int64_t lse_sb, lse_sh;
+  int B, Hq, Hkv, Nq, nq_pad;
+};
+
+// one warp per query row, 4 consecutive elements per lane
+__global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const PrepParams p) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
+  const int64_t rows = static_cast<int64_t>(p.B) * p.Hq * p.nq_pad;
+  if (warp >= rows) return;
+  const int i = warp % p.nq_pad;
+  const int h = (warp / p.nq_pad) % p.Hq;
+  const int b = warp / (p.nq_pad * p.Hq);
+  float4* stat = p.qstat + (static_cast<int64_t>(b) * p.Hq + h) * p.nq_pad + i;
+  if (i >= p.Nq) {
+    // padding rows: lse = +inf makes every probability zero
+    if (lane == 0) *stat = make_float4(INFINITY, 0.f, 0.f, 0.f);
+    return;
+  }
+  const __nv_bfloat16* dsrc = p.dout + b * p.do_sb + h * p.do_sh + static_cast<int64_t>(i) * p.do_sn + lane * 4;
+  const __nv_bfloat16* osrc = p.out + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(i) * p.o_sn + lane * 4;
+  const uint2 draw = *reinterpret_cast<const uint2*>(dsrc);
+  const uint2 oraw = *reinterpret_cast<const uint2*>(osrc);
+  float dv[4], ov[4];
+  dv[0] = __uint_as_float(draw.x << 16);
+  dv[1] = __uint_as_float(draw.x & 0xffff0000u);
+  dv[2] = __uint_as_float(draw.y << 16);
+  dv[3] = __uint_as_float(draw.y & 0xffff0000u);
+  ov[0] = __uint_as_float(oraw.x << 16);
+  ov[1] = __uint_as_float(oraw.x & 0xffff0000u);
+  ov[2] = __uint_as_float(oraw.y << 16);
+  ov[3] = __uint_as_float(oraw.y & 0xffff0000u);
+  uint32_t amax = 0;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) amax = max(amax, __float_as_uint(dv[c]) & 0x7fffffffu);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  // the MXFP8 quantiser's scale: the row peak lands in (224, 448]
+  int e = static_cast<int>((amax + 0x1fffffu) >> 23) - 8;
+  e = min(max(e, 0), 254);
+  const float inv = __uint_as_float(static_cast<uint32_t>(max(254 - e, 1)) << 23);
+  const float g = __uint_as_float(static_cast<uint32_t>(max(e, 1)) << 23) * (e == 0 ? 0.5f : 1.f);
+  const uint16_t c01 = cvt_e4m3x2(dv[0] * inv, dv[1] * inv);
+  const uint16_t c23 = cvt_e4m3x2(dv[2] * inv, dv[3] * inv);
+  float q0, q1, q2, q3;
+  unpack_e4m3x2(c01, q0, q1);
+  unpack_e4m3x2(c23, q2, q3);
+  float dsum = (q0 * ov[0] + q1 * ov[1]) + (q2 * ov[2] + q3 * ov[3]);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
+  uint8_t* dst = p.do8 + ((static_cast<int64_t>(b) * p.Hq + h) * p.Nq + i) * D + lane * 4;
+  *reinterpret_cast<uint32_t*>(dst) = static_cast<uint32_t>(c01) | (static_cast<uint32_t>(c23) << 16);
+  if (lane == 0) {
+    const float sv = p.v_descale[b * p.Hkv + h / (p.Hq / p.Hkv)];
+    const float L = p.lse[b * p.lse_sb + h * p.lse_sh + i];
+    *stat = make_float4(L, g, g * sv, dsum * g);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// helpers shared by the two main kernels
+// ---------------------------------------------------------------------------
+// Power-of-two scale for a block whose largest magnitude has the fp32 bit pattern `amax_bits`:
+// the scaled peak lands in [128, 256).  Returns the ue8m0 byte; `inv` is the multiplier.
+__device__ __forceinline__ uint32_t block_scale(uint32_t amax_bits, float& inv) {
+  const int eb = static_cast<int>(amax_bits >> 23);
+  const int sf = max(eb - 7, 0);
+  inv = __uint_as_float(static_cast<uint32_t>(254 - sf) << 23);
+  return static_cast<uint32_t>(sf);
+}
+
+__device__ __forceinline__ void quantize_block_to_tmem(const float (&x)[32], uint32_t taddr, float inv) {
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    w[i] = pack_e4m3x4(x[4 * i] * inv, x[4 * i + 1] * inv, x[4 * i + 2] * inv, x[4 * i + 3] * inv);
+  tmem_st8(taddr, w);
+}
+
+struct BwdParams {
+  const float4* qstat;   // [B,Hq,nq_pad]
+  const float* q_descale;
+  const float* k_descale;
+  __nv_bfloat16* dq;     // [B,Hq,Nq,D] contiguous
+  __nv_bfloat16* dk;     // [B,Hkv,Nk,D] contiguous
+  __nv_bfloat16* dv;
+  int B, Hq, Hkv, Nq, Nk, nq_pad;
+  int causal;
+  float softmax_scale;
+  int* status;
+};
+
+// ---------------------------------------------------------------------------
+// 2. dK / dV
+// ---------------------------------------------------------------------------
+constexpr int A_STAGES = 2;
+constexpr int A_STAT_BYTES = BM * 16;
+constexpr int A_STAGE_BYTES = 2 * TILE_BYTES + A_STAT_BYTES;
+constexpr int A_SMEM_BYTES = 2 * TILE_BYTES + A_STAGES * A_STAGE_BYTES + 3 * SF_BYTES + 1024 + 256;
+constexpr int A_ST_COL = 0, A_DPT_COL = 128, A_DV_COL = 256, A_DK_COL = 384;
+constexpr int A_SF_P = 64, A_SF_UNIT = 68, A_SF_DS = 72;  // inside the consumed S^T columns
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                     const __grid_constant__ BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t k_smem = smem_base;
+  const uint32_t v_smem = k_smem + TILE_BYTES;
+  const uint32_t stage_smem = v_smem + TILE_BYTES;  // per stage: Q tile, dO tile, row records
+  const uint32_t sfp_smem = stage_smem + A_STAGES * A_STAGE_BYTES;
+  const uint32_t sfu_smem = sfp_smem + SF_BYTES;
+  const uint32_t sfd_smem = sfu_smem + SF_BYTES;
+  const uint32_t bar_base = sfd_smem + SF_BYTES;
+  const uint32_t kv_full = bar_base;
+  auto q_full = [&](int s) { return bar_base + 8u * (1 + s); };
+  auto q_empty = [&](int s) { return bar_base + 8u * (1 + A_STAGES + s); };
+  const uint32_t s_full = bar_base + 8u * (1 + 2 * A_STAGES);
+  const uint32_t p_full = s_full + 8;
+  const uint32_t acc_full = s_full + 16;
+  const uint32_t tmem_slot = s_full + 24;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));  // generic pointer to the aligned base
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const int n_blk = blockIdx.x;
+  const int hkv = blockIdx.y;
+  const int b = blockIdx.z;
+  const int n0 = n_blk * BN;
+  const int group = p.Hq / p.Hkv;
+  const int shift = p.Nk - p.Nq;
+  const int num_m = (p.Nq + BM - 1) / BM;
+  // first query tile that sees a key of this block (bottom-right aligned causal mask)
+  const int m_first = p.causal ? min(num_m, max(0, n0 - shift) / BM) : 0;
+  const int tiles_per_head = num_m - m_first;
+  const int n_iter = group * tiles_per_head;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < A_STAGES; ++s) {
+      mbar_init(q_full(s), 1);
+      mbar_init(q_empty(s), 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(acc_full, 1);
+    mbar_fence_init();
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+    prefetch_tmap(&tmap_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (threadIdx.x < SF_BYTES / 4) {
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfu_smem + 4u * threadIdx.x), "r"(0x7f7f7f7fu) : "memory");
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == 0) {
+    if (lane == 0 && n_iter > 0) {
+      mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+      tma_load_4d(k_smem, &tmap_k, kv_full, 0, n0, hkv, b);
+      tma_load_4d(v_smem, &tmap_v, kv_full, 0, n0, hkv, b);
+      for (int it = 0; it < n_iter; ++it) {
+        const int s = it % A_STAGES;
+        const uint32_t ph = (it / A_STAGES) & 1;
+        const int hq = hkv * group + it / tiles_per_head;
+        const int m0 = (m_first + it % tiles_per_head) * BM;
+        if (!mbar_wait(q_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
+        const uint32_t base = stage_smem + s * A_STAGE_BYTES;
+        mbar_expect_tx(q_full(s), A_STAGE_BYTES);
+        tma_load_4d(base, &tmap_q, q_full(s), 0, m0, hq, b);
+        tma_load_4d(base + TILE_BYTES, &tmap_do, q_full(s), 0, m0, hq, b);
+        bulk_load(base + 2 * TILE_BYTES, p.qstat + (static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0,
+                  A_STAT_BYTES, q_full(s));
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && n_iter > 0) {
+      constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BN, BM);
+      const uint32_t st_tmem = tmem_base + A_ST_COL;
+      const uint32_t dpt_tmem = tmem_base + A_DPT_COL;
+      bool ok = mbar_wait(kv_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
+      const uint64_t k_desc = smem_desc_sw128(k_smem, 16, 1024);
+      const uint64_t v_desc = smem_desc_sw128(v_smem, 16, 1024);
+      for (int it = 0; ok && it < n_iter; ++it) {
+        const int s = it % A_STAGES;
+        const uint32_t ph = (it / A_STAGES) & 1;
+        if (!mbar_wait(q_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        tc_fence_after();
+        const uint32_t base = stage_smem + s * A_STAGE_BYTES;
+        const uint64_t q_desc = smem_desc_sw128(base, 16, 1024);
+        const uint64_t do_desc = smem_desc_sw128(base + TILE_BYTES, 16, 1024);
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) mma_f8_ss(st_tmem, k_desc + 2 * k, q_desc + 2 * k, idesc_ss, k != 0);
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) mma_f8_ss(dpt_tmem, v_desc + 2 * k, do_desc + 2 * k, idesc_ss, k != 0);
+        tc_commit(s_full);
+        if (!mbar_wait(p_full, it & 1, p.status, WK_ERR_TIMEOUT_P)) break;
+        tc_fence_after();
+        tmem_cp_32x128b_warpx4(st_tmem + A_SF_P, smem_desc_plain(sfp_smem, 16, 128));
+        tmem_cp_32x128b_warpx4(st_tmem + A_SF_UNIT, smem_desc_plain(sfu_smem, 16, 128));
+        tmem_cp_32x128b_warpx4(st_tmem + A_SF_DS, smem_desc_plain(sfd_smem, 16, 128));
+        // B operands: the dO8 / Q8 tiles again, now read MN-major (K = queries, N = head dim)
+#pragma unroll
+        for (int k = 0; k < BM / 32; ++k) {
+          mma_mxf8_ts(tmem_base + A_DV_COL, st_tmem + 8 * k, do_desc + 256 * k,
+                      make_idesc_mx_major(BN, D, k, 0, 0, 1), st_tmem + A_SF_P, st_tmem + A_SF_UNIT,
+                      (it | k) != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < BM / 32; ++k) {
+          mma_mxf8_ts(tmem_base + A_DK_COL, dpt_tmem + 8 * k, q_desc + 256 * k,
+                      make_idesc_mx_major(BN, D, k, 0, 0, 1), st_tmem + A_SF_DS, st_tmem + A_SF_UNIT,
+                      (it | k) != 0);
+        }
+        tc_commit(q_empty(s));
+        if (it == n_iter - 1) tc_commit(acc_full);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;  // key row of the tile == TMEM lane
+    const int key = n0 + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t st_tmem = tmem_base + lane_addr + A_ST_COL;
+    const uint32_t dpt_tmem = tmem_base + lane_addr + A_DPT_COL;
+    const int sc = b * p.Hkv + hkv;
+    const float sq = p.q_descale[sc], sk = p.k_descale[sc];
+    const float beta = p.softmax_scale * sq * sk * LOG2E;
+    bool ok = true;
+
+    for (int it = 0; it < n_iter; ++it) {
+      const int s = it % A_STAGES;
+      const int m0 = (m_first + it % tiles_per_head) * BM;
+      if (!mbar_wait_warp(s_full, it & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const float4* stat = reinterpret_cast<const float4*>(smem_gen + (stage_smem - smem_base) + s * A_STAGE_BYTES +
+                                                           2 * TILE_BYTES);
+      // query column c is visible to this key iff key < Nk and (not causal or key <= m0 + c + shift)
+      const int first_col = key >= p.Nk ? BM : (p.causal ? max(0, key - shift - m0) : 0);
+      uint32_t sf_p = 0, sf_d = 0;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sraw[32], draw[32];
+        tmem_ld32(st_tmem + c * 32, sraw);
+        tmem_ld32(dpt_tmem + c * 32, draw);
+        tc_wait_ld();
+        float pt[32], ds[32];
+        uint32_t pmax_bits = 0, dmax_bits = 0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float4 st = stat[c * 32 + i];  // (L, g, g*sv, D): same address for every thread
+          float pr = ex2_approx(fmaf(__uint_as_float(sraw[i]), beta, -st.x));
+          if (c * 32 + i < first_col) pr = 0.f;
+          pt[i] = pr * st.y;
+          ds[i] = pr * fmaf(__uint_as_float(draw[i]), st.z, -st.w);
+          pmax_bits = max(pmax_bits, __float_as_uint(pt[i]) & 0x7fffffffu);
+          dmax_bits = max(dmax_bits, __float_as_uint(ds[i]) & 0x7fffffffu);
+        }
+        float inv_p, inv_d;
+        const uint32_t bp = block_scale(pmax_bits, inv_p);
+        const uint32_t bd = block_scale(dmax_bits, inv_d);
+        quantize_block_to_tmem(pt, st_tmem + c * 8, inv_p);
+        quantize_block_to_tmem(ds, dpt_tmem + c * 8, inv_d);
+        sf_p |= bp << (8 * c);
+        sf_d |= bd << (8 * c);
+      }
+      const uint32_t sf_off = (r % 32) * 16 + (r / 32) * 4;
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfp_smem + sf_off), "r"(sf_p) : "memory");
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfd_smem + sf_off), "r"(sf_d) : "memory");
+      fence_proxy_async_smem();
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+
+    if (n_iter > 0 && ok) ok = mbar_wait_warp(acc_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
+    if (ok) {
+      tc_fence_after();
+      const float dk_scale = p.softmax_scale * sq;
+      const int64_t row_off = ((static_cast<int64_t>(b) * p.Hkv + hkv) * p.Nk + key) * D;
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        const uint32_t src = tmem_base + lane_addr + (half == 0 ? A_DV_COL : A_DK_COL);
+        __nv_bfloat16* dst_row = (half == 0 ? p.dv : p.dk) + row_off;
+        const float scale = half == 0 ? 1.f : dk_scale;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          if (n_iter > 0) {  // uniform: TMEM loads are warp-wide
+            tmem_ld32(src + c * 32, v);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0;
+          }
+          if (key < p.Nk) {
+            uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(v[8 * i + 0]) * scale, __uint_as_float(v[8 * i + 1]) * scale);
+              w.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]) * scale, __uint_as_float(v[8 * i + 3]) * scale);
+              w.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]) * scale, __uint_as_float(v[8 * i + 5]) * scale);
+              w.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]) * scale, __uint_as_float(v[8 * i + 7]) * scale);
+              dst[i] = w;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 3. dQ
+// ---------------------------------------------------------------------------
+constexpr int B_STAGES = 2;
+constexpr int B_STAGE_BYTES = 2 * TILE_BYTES;  // K tile, V tile
+constexpr int B_SMEM_BYTES = 2 * TILE_BYTES + B_STAGES * B_STAGE_BYTES + 2 * SF_BYTES + 1024 + 256;
+constexpr int B_S_COL = 0, B_DP_COL = 128, B_DQ_COL = 256;
+constexpr int B_SF_DS = 64, B_SF_UNIT = 68;
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                   const __grid_constant__ BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_smem = smem_base;
+  const uint32_t do_smem = q_smem + TILE_BYTES;
+  const uint32_t stage_smem = do_smem + TILE_BYTES;
+  const uint32_t sfd_smem = stage_smem + B_STAGES * B_STAGE_BYTES;
+  const uint32_t sfu_smem = sfd_smem + SF_BYTES;
+  const uint32_t bar_base = sfu_smem + SF_BYTES;
+  const uint32_t q_full = bar_base;
+  auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
+  auto kv_empty = [&](int s) { return bar_base + 8u * (1 + B_STAGES + s); };
+  const uint32_t s_full = bar_base + 8u * (1 + 2 * B_STAGES);
+  const uint32_t p_full = s_full + 8;
+  const uint32_t acc_full = s_full + 16;
+  const uint32_t tmem_slot = s_full + 24;
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const int m_blk = gridDim.x - 1 - blockIdx.x;
+  const int hq = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hkv = hq / (p.Hq / p.Hkv);
+  const int m0 = m_blk * BM;
+  const int shift = p.Nk - p.Nq;
+  int n_tiles = (p.Nk + BN - 1) / BN;
+  if (p.causal) {
+    const int last_key = min(m0 + BM, p.Nq) - 1 + shift;
+    n_tiles = last_key < 0 ? 0 : min(n_tiles, last_key / BN + 1);
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < B_STAGES; ++s) {
+      mbar_init(kv_full(s), 1);
+      mbar_init(kv_empty(s), 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(acc_full, 1);
+    mbar_fence_init();
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+    prefetch_tmap(&tmap_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (threadIdx.x < SF_BYTES / 4) {
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfu_smem + 4u * threadIdx.x), "r"(0x7f7f7f7fu) : "memory");
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == 0) {
+    if (lane == 0 && n_tiles > 0) {
+      mbar_expect_tx(q_full, 2 * TILE_BYTES);
+      tma_load_4d(q_smem, &tmap_q, q_full, 0, m0, hq, b);
+      tma_load_4d(do_smem, &tmap_do, q_full, 0, m0, hq, b);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % B_STAGES;
+        const uint32_t ph = (j / B_STAGES) & 1;
+        if (!mbar_wait(kv_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
+        const uint32_t base = stage_smem + s * B_STAGE_BYTES;
+        mbar_expect_tx(kv_full(s), B_STAGE_BYTES);
+        tma_load_4d(base, &tmap_k, kv_full(s), 0, j * BN, hkv, b);
+        tma_load_4d(base + TILE_BYTES, &tmap_v, kv_full(s), 0, j * BN, hkv, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BM, BN);
+      const uint32_t s_tmem = tmem_base + B_S_COL;
+      const uint32_t dp_tmem = tmem_base + B_DP_COL;
+      bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
+      const uint64_t q_desc = smem_desc_sw128(q_smem, 16, 1024);
+      const uint64_t do_desc = smem_desc_sw128(do_smem, 16, 1024);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const int s = j % B_STAGES;
+        const uint32_t ph = (j / B_STAGES) & 1;
+        if (!mbar_wait(kv_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        tc_fence_after();
+        const uint32_t base = stage_smem + s * B_STAGE_BYTES;
+        const uint64_t k_desc = smem_desc_sw128(base, 16, 1024);
+        const uint64_t v_desc = smem_desc_sw128(base + TILE_BYTES, 16, 1024);
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_ss, k != 0);
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) mma_f8_ss(dp_tmem, do_desc + 2 * k, v_desc + 2 * k, idesc_ss, k != 0);
+        tc_commit(s_full);
+        if (!mbar_wait(p_full, j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
+        tc_fence_after();
+        tmem_cp_32x128b_warpx4(s_tmem + B_SF_DS, smem_desc_plain(sfd_smem, 16, 128));
+        tmem_cp_32x128b_warpx4(s_tmem + B_SF_UNIT, smem_desc_plain(sfu_smem, 16, 128));
+        // dQ += dS K: A = dS codes in the dP columns, B = the K tile read MN-major
+#pragma unroll
+        for (int k = 0; k < BN / 32; ++k) {
+          mma_mxf8_ts(tmem_base + B_DQ_COL, dp_tmem + 8 * k, k_desc + 256 * k,
+                      make_idesc_mx_major(BM, D, k, 0, 0, 1), s_tmem + B_SF_DS, s_tmem + B_SF_UNIT,
+                      (j | k) != 0);
+        }
+        tc_commit(kv_empty(s));
+        if (j == n_tiles - 1) tc_commit(acc_full);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int row = m0 + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_addr + B_S_COL;
+    const uint32_t dp_tmem = tmem_base + lane_addr + B_DP_COL;
+    const int sc = b * p.Hkv + hkv;
+    const float sq = p.q_descale[sc], sk = p.k_descale[sc];
+    const float beta = p.softmax_scale * sq * sk * LOG2E;
+    const float4 st = p.qstat[(static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + row];  // (L, g, g*sv, D)
+    const int row_limit = min(p.causal ? row + shift : p.Nk - 1, p.Nk - 1);
+    bool ok = true;
+
+    for (int j = 0; j < n_tiles; ++j) {
+      if (!mbar_wait_warp(s_full, j & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int limit = row_limit - j * BN;  // columns > limit are masked
+      uint32_t sf_d = 0;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sraw[32], draw[32];
+        tmem_ld32(s_tmem + c * 32, sraw);
+        tmem_ld32(dp_tmem + c * 32, draw);
+        tc_wait_ld();
+        float ds[32];
+        uint32_t dmax_bits = 0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float pr = ex2_approx(fmaf(__uint_as_float(sraw[i]), beta, -st.x));
+          if (c * 32 + i > limit) pr = 0.f;
+          ds[i] = pr * fmaf(__uint_as_float(draw[i]), st.z, -st.w);
+          dmax_bits = max(dmax_bits, __float_as_uint(ds[i]) & 0x7fffffffu);
+        }
+        float inv_d;
+        const uint32_t bd = block_scale(dmax_bits, inv_d);
+        quantize_block_to_tmem(ds, dp_tmem + c * 8, inv_d);
+        sf_d |= bd << (8 * c);
+      }
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfd_smem + (r % 32) * 16 + (r / 32) * 4), "r"(sf_d)
+                   : "memory");
+      fence_proxy_async_smem();
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+
+    if (n_tiles > 0 && ok) ok = mbar_wait_warp(acc_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
+    if (ok) {
+      tc_fence_after();
+      const float scale = p.softmax_scale * sk;
+      __nv_bfloat16* dst_row = p.dq + ((static_cast<int64_t>(b) * p.Hq + hq) * p.Nq + row) * D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tmem_base + lane_addr + B_DQ_COL + c * 32, v);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0;
+        }
+        if (row < p.Nq) {
+          uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(v[8 * i + 0]) * scale, __uint_as_float(v[8 * i + 1]) * scale);
+            w.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]) * scale, __uint_as_float(v[8 * i + 3]) * scale);
+            w.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]) * scale, __uint_as_float(v[8 * i + 5]) * scale);
+            w.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]) * scale, __uint_as_float(v[8 * i + 7]) * scale);
+            dst[i] = w;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+int make_map4(CUtensorMap* m, const void* base, int n, int h, int b, const int64_t* strides) {
+  const uint64_t dims[4] = {D, static_cast<uint64_t>(n), static_cast<uint64_t>(h), static_cast<uint64_t>(b)};
+  const uint64_t str[3] = {static_cast<uint64_t>(strides[2]), static_cast<uint64_t>(strides[1]),
+                           static_cast<uint64_t>(strides[0])};
+  const uint32_t box[4] = {D, 128, 1, 1};
+  return encode_tmap(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, base, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace
+}  // namespace wk
+
+extern "C" int64_t wk_attn_bwd_fp8_workspace_bytes(int B, int Hq, int Nq) {
+  if (B < 0 || Hq < 0 || Nq < 0) return WK_E_ARG;
+  const int64_t nq_pad = (static_cast<int64_t>(Nq) + 127) / 128 * 128;
+  return static_cast<int64_t>(B) * Hq * (static_cast<int64_t>(Nq) * 128 + nq_pad * 16) + 256;
+}
+
+extern "C" int wk_attn_bwd_fp8(const wk_attn_bwd_args* a, void* stream) {
+  using namespace wk;
+  if (!a) return WK_E_ARG;
+  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Nq <= 0 || a->Nk <= 0 || a->d != D) return WK_E_ARG;
+  if (a->Hq % a->Hkv || a->B > 65535 || a->Hq > 65535) return WK_E_ARG;
+  if (!a->q || !a->k || !a->v || !a->out || !a->dout || !a->lse || !a->dq || !a->dk || !a->dv) return WK_E_ARG;
+  if (!a->q_descale || !a->k_descale || !a->v_descale || !a->workspace) return WK_E_ARG;
+  if (!(a->softmax_scale > 0.f)) return WK_E_ARG;
+  const void* ptrs[] = {a->q, a->k, a->v, a->dq, a->dk, a->dv, a->workspace};
+  for (const void* ptr : ptrs)
+    if (!aligned16(ptr)) return WK_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(a->out) & 7) || (reinterpret_cast<uintptr_t>(a->dout) & 7)) return WK_E_ARG;
+  for (int i = 0; i < 3; ++i) {
+    if (a->q_strides[i] % 16 || a->k_strides[i] % 16 || a->v_strides[i] % 16) return WK_E_ARG;
+    if (a->q_strides[i] <= 0 || a->k_strides[i] <= 0 || a->v_strides[i] <= 0) return WK_E_ARG;
+    if (a->out_strides[i] % 4 || a->dout_strides[i] % 4 || a->out_strides[i] <= 0 || a->dout_strides[i] <= 0)
+      return WK_E_ARG;
+  }
+  if (a->workspace_bytes < wk_attn_bwd_fp8_workspace_bytes(a->B, a->Hq, a->Nq)) return WK_E_ARG;
+  int* status = status_word();
+  if (!status) return WK_E_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  const int nq_pad = (a->Nq + 127) / 128 * 128;
+  uint8_t* do8 = static_cast<uint8_t*>(a->workspace);
+  const int64_t do8_bytes = (static_cast<int64_t>(a->B) * a->Hq * a->Nq * D + 255) / 256 * 256;
+  float4* qstat = reinterpret_cast<float4*>(do8 + do8_bytes);
+
+  PrepParams pp;
+  pp.dout = static_cast<const __nv_bfloat16*>(a->dout);
+  pp.out = static_cast<const __nv_bfloat16*>(a->out);
+  pp.lse = a->lse;
+  pp.v_descale = a->v_descale;
+  pp.do8 = do8;
+  pp.qstat = qstat;
+  pp.do_sb = a->dout_strides[0];
+  pp.do_sh = a->dout_strides[1];
+  pp.do_sn = a->dout_strides[2];
+  pp.o_sb = a->out_strides[0];
+  pp.o_sh = a->out_strides[1];
+  pp.o_sn = a->out_strides[2];
+  pp.lse_sb = a->lse_strides[0];
+  pp.lse_sh = a->lse_strides[1];
+  pp.B = a->B;
+  pp.Hq = a->Hq;
+  pp.Hkv = a->Hkv;
+  pp.Nq = a->Nq;
+  pp.nq_pad = nq_pad;
+  {
+    const int64_t rows = static_cast<int64_t>(a->B) * a->Hq * nq_pad;
+    const int64_t blocks = (rows + 7) / 8;
+    attn_bwd_prep_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(pp);
+    if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+  }
+
+  CUtensorMap tq, tk, tv, tdo;
+  int r = make_map4(&tq, a->q, a->Nq, a->Hq, a->B, a->q_strides);
+  if (r) return r;
+  r = make_map4(&tk, a->k, a->Nk, a->Hkv, a->B, a->k_strides);
+  if (r) return r;
+  r = make_map4(&tv, a->v, a->Nk, a->Hkv, a->B, a->v_strides);
+  if (r) return r;
+  const int64_t do_str[3] = {static_cast<int64_t>(a->Hq) * a->Nq * D, static_cast<int64_t>(a->Nq) * D, D};
+  r = make_map4(&tdo, do8, a->Nq, a->Hq, a->B, do_str);
+  if (r) return r;
+
+  BwdParams p;
+  p.qstat = qstat;
+  p.q_descale = a->q_descale;
+  p.k_descale = a->k_descale;
+  p.dq = static_cast<__nv_bfloat16*>(a->dq);
+  p.dk = static_cast<__nv_bfloat16*>(a->dk);
+  p.dv = static_cast<__nv_bfloat16*>(a->dv);
+  p.B = a->B;
+  p.Hq = a->Hq;
+  p.Hkv = a->Hkv;
+  p.Nq = a->Nq;
+  p.Nk = a->Nk;
+  p.nq_pad = nq_pad;
+  p.causal = a->causal;
+  p.softmax_scale = a->softmax_scale;
+  p.status = status;
+
+  if (allow_smem(reinterpret_cast<const void*>(attn_bwd_dkdv_kernel), A_SMEM_BYTES)) return WK_E_CUDA;
+  if (allow_smem(reinterpret_cast<const void*>(attn_bwd_dq_kernel), B_SMEM_BYTES)) return WK_E_CUDA;
+  {
+    dim3 grid((a->Nk + BN - 1) / BN, a->Hkv, a->B);
+    attn_bwd_dkdv_kernel<<<grid, THREADS, A_SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+  }
+  {
+    dim3 grid((a->Nq + BM - 1) / BM, a->Hq, a->B);
+    attn_bwd_dq_kernel<<<grid, THREADS, B_SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+  }
+  return 0;
+}
