@@ -134,6 +134,38 @@ def make_attn(dev, B, Hq, Hkv, N, d, causal, seed, backward=False):
                 check=lambda: None, tensors=(q8, k8, v8, dsq, dsk, dsv, out, lse))
 
 
+def make_attn_bwd(dev, B, Hq, Hkv, N, d, causal, seed):
+    import warpy_kernels as wk
+    from warpy_kernels.attn import make_attn_bwd as prepare
+
+    g = torch.Generator(device=dev).manual_seed(seed)
+    mk = lambda h: torch.randn(B, h, N, d, device=dev, generator=g).bfloat16().float()
+    q, k, v = mk(Hq), mk(Hkv), mk(Hkv)
+    q8, sq = quantize_per_tensor(q)
+    k8, sk = quantize_per_tensor(k)
+    v8, sv = quantize_per_tensor(v)
+    del q, k, v
+    full = lambda s: torch.full((B, Hkv), float(s), device=dev)
+    dsq, dsk, dsv = full(sq), full(sk), full(sv)
+    dout = torch.randn(B, Hq, N, d, device=dev, generator=torch.Generator(device=dev).manual_seed(7)).bfloat16()
+    out, lse, pmax = wk.attn_fwd(q8, k8, v8, dsq, dsk, dsv, causal=causal)
+    launch, finish = prepare(q8, k8, v8, out, lse, pmax, dout, dsq, dsk, dsv, causal=causal)
+    flops = 10.0 * B * Hq * N * N * d * (0.5 if causal else 1.0)
+    hdo = dout.cpu().pin_memory()
+    ddo = torch.empty_like(dout)
+    hg = [torch.empty(x.shape, dtype=torch.bfloat16).pin_memory() for x in (q8, k8, v8)]
+
+    def e2e_step():
+        # the forward's saved tensors stay on the device; dout arrives from the host, gradients go back
+        ddo.copy_(hdo, non_blocking=True)
+        grads = wk.attn_bwd(q8, k8, v8, out, lse, pmax, ddo, dsq, dsk, dsv, causal=causal)
+        for h_, g_ in zip(hg, grads):
+            h_.copy_(g_, non_blocking=True)
+
+    return dict(step=launch, e2e_step=e2e_step, work=flops, bound="tensor", dtype="fp8", launches=3,
+                h2d=hdo.numel() * 2, d2h=sum(h.numel() * 2 for h in hg), tensors=(q8, k8, v8, out, lse, dout))
+
+
 def make_gemm_bf16(dev, m, n, k, seed):
     import warpy_kernels as wk
 
@@ -204,6 +236,8 @@ WORKLOADS = {
                      make=lambda dev: make_attn(dev, 4, 32, 32, 4096, 128, True, 0)),
     "attn_fwd_small": dict(desc="FP8 causal attention forward B2 H32 N4096 d128 (profiling size)", unit="TFLOP/s",
                            make=lambda dev: make_attn(dev, 2, 32, 32, 4096, 128, True, 0)),
+    "attn_bwd": dict(desc="FP8 causal attention backward B4 H32 N4096 d128", unit="TFLOP/s",
+                     make=lambda dev: make_attn_bwd(dev, 4, 32, 32, 4096, 128, True, 0)),
     "attn_gqa": dict(desc="FP8 GQA causal attention forward B1 Hq64 Hkv8 N32768 d128", unit="TFLOP/s",
                      make=lambda dev: make_attn(dev, 1, 64, 8, 32768, 128, True, 0)),
     "gemm_bf16": dict(desc="BF16 GEMM M=N=K=2048", unit="TFLOP/s",
@@ -421,7 +455,7 @@ def main():
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
-            base = "attn_fwd" if args.workload.startswith("attn_fwd") else args.workload
+            base = "attn_fwd" if args.workload.startswith(("attn_fwd", "attn_bwd")) else args.workload
             line["cpu_baseline"] = cpu_baseline(base if base in ("attn_fwd", "attn_gqa", "quant") else "gemm_bf16")
             if args.workload.startswith("gemm_mx"):
                 line["cpu_baseline"]["sample"] += " (fp32 matmul of dequantised operands has the same cost)"
