@@ -1,31 +1,35 @@
 // FP8 (e4m3) flash-attention forward for sm_100a, head dimension 128.
 //
 // One CTA = 128 queries of one (batch, query head); two CTAs share an SM so that
-// one CTA's softmax overlaps the other's tensor-core work.
+// one CTA's softmax overlaps the other's tensor-core work.  320 threads:
 //   warp 0      TMA producer: Q tile once, then K and V tiles (128 keys x 128 bytes,
 //               128-byte swizzle) into two-stage rings
 //   warp 1      allocates 256 TMEM columns (S: 0..127, O: 128..255) and issues
-//               tcgen05.mma kind::f8f6f4:  S = Q.K^T (both K-major from shared memory),
-//               O += P.V (P read from TMEM, V MN-major from shared memory)
-//   warps 2-5   softmax, one thread per query row: read S from TMEM, P as MXFP8 (e4m3
-//               codes written back over the S columns plus one power-of-two scale per
-//               row and 32 keys, staged through shared memory), fp32 row sums;
-//               finally O . v_descale / l -> bf16, lse (base 2) and pmax
+//               tcgen05.mma:  S = Q.K^T (kind::f8f6f4, both operands K-major from shared
+//               memory), O += P.V (kind::mxf8f6f4.block_scale, P read from TMEM, V MN-major
+//               from shared memory)
+//   warps 2-9   softmax, two threads per query row (64 keys of the tile each): read S from
+//               TMEM, P as MXFP8 (e4m3 codes written back over the S columns plus one
+//               power-of-two scale per row and 32 keys, staged through shared memory), row
+//               sums; finally O . v_descale / l -> bf16, lse (base 2) and pmax
 //
 // Numerics follow the reference's forward (warpy_kernels/attn/fwd_base.py:297-360,
 // 939-988; fwd_sm120.py:93-136): logits in base 2 with beta = softmax_scale .
 // q_descale . k_descale . log2(e), bottom-right aligned causal mask, lse =
 // m_ref + log2(l), pmax = 2^(m_true - lse), empty rows give out = 0, lse = +inf,
-// pmax = 0.  Where the reference quantises P against each 128-key tile's own maximum
+// pmax = 0, and O is normalised by the sum of the *rounded* P (fwd_sm120.py:95-118).
+// Where the reference quantises P against each 128-key tile's own maximum
 // ("tile_local") and rescales O by the ratio of consecutive references, this kernel
 // quantises every block of 32 keys against its own exponent e_blk = m_ref + k, k the
 // smallest integer with e_blk >= block maximum,
 //   P8 = e4m3(2^(s.beta - e_blk + 8)),   scale = 2^(k - 8),
-// and lets the block-scaled MMA (kind::mxf8f6f4) apply the scale, so O accumulates in
-// the units of one reference m_ref per row.  m_ref is the row's running maximum at its
-// last refresh: the largest probability of the row is then stored exactly (2^8), as in
-// the reference.  It is refreshed (with a rescale of O and l) only when the running
-// maximum has grown by more than a factor of two.
+// and lets the block-scaled MMA apply the scale, so O accumulates in the units of one
+// reference m_ref per row.  m_ref is the row's running maximum at its last refresh: the
+// largest probability of the row is then stored exactly (2^8), as in the reference.  It
+// is refreshed (with a rescale of O and l) only when the running maximum has grown by
+// more than a factor of two.  Query blocks that see at most 512 keys carry P as two
+// e4m3 terms (value + 2^-4 . residual): with so few keys the rounding of P would not
+// average out.
 //
 // Tensor-core bound: 4 . B . Hq . Nq . Nk . d flops (half of that when causal).
 #include <math.h>
@@ -41,19 +45,21 @@ constexpr int BN = 128;       // keys per tile
 constexpr int D = 128;        // head dimension (bytes per row in e4m3)
 constexpr int KV_STAGES = 2;
 constexpr int TILE_BYTES = BN * D;  // 16 KiB
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;
+constexpr int SOFTMAX_THREADS = 256;
 constexpr int TMEM_COLS = 256;
 constexpr int S_COL = 0;
 constexpr int O_COL = 128;
 constexpr int P_OFFSET = 8;          // a block's largest P is stored in (2^7, 2^8]
-constexpr float RESCALE_TAU = 1.0f;   // refresh the row reference when the maximum outgrew it by more than this (log2)
+constexpr float RESCALE_TAU = 1.0f;  // refresh the row reference when the maximum outgrew it by more than this (log2)
 constexpr int SF_BYTES = 512;        // one scale-factor atom: 128 rows x 4 blocks of 32 keys
 constexpr int SFA_COL = 64;          // TMEM columns (inside the consumed part of S) the scales are copied to
 constexpr int SFB_COL = 68;
 constexpr int SFA_LO_COL = 72;       // scales of the residual term
 constexpr int PLO_COL = 32;          // residual P codes (S columns 32..63)
 constexpr int RESID_MAX_TILES = 4;   // query blocks that see at most this many key tiles carry the residual term
-constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 3 * SF_BYTES + 1024 + 256;
+constexpr int XCH_BYTES = 3 * 2 * BM * 4;  // pair exchange: maximum, row sum, rounded row sum
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 3 * SF_BYTES + XCH_BYTES + 1024 + 256;
 
 struct FwdParams {
   __nv_bfloat16* out;
@@ -73,6 +79,65 @@ struct FwdParams {
   int* status;
 };
 
+__device__ __forceinline__ void pair_sync(int id) {
+  asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
+}
+
+// One block of 32 keys of one row: P codes (and the residual codes), the exact and the rounded sum.
+template <bool RESID>
+__device__ __forceinline__ void softmax_block(const uint32_t (&sraw)[32], float beta, float bias, uint32_t (&w)[8],
+                                              uint32_t (&wl)[8], float& sum_exact, float& sum_rounded) {
+  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+  uint32_t hsum0 = 0, hsum1 = 0;  // f16x2 partial sums of the rounded codes (exact in f16)
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float p0 = ex2_approx(fmaf(__uint_as_float(sraw[4 * i + 0]), beta, bias));
+    const float p1 = ex2_approx(fmaf(__uint_as_float(sraw[4 * i + 1]), beta, bias));
+    const float p2 = ex2_approx(fmaf(__uint_as_float(sraw[4 * i + 2]), beta, bias));
+    const float p3 = ex2_approx(fmaf(__uint_as_float(sraw[4 * i + 3]), beta, bias));
+    acc0 += p0;
+    acc1 += p1;
+    acc2 += p2;
+    acc3 += p3;
+    const uint16_t h01 = cvt_e4m3x2(p0, p1), h23 = cvt_e4m3x2(p2, p3);
+    w[i] = static_cast<uint32_t>(h01) | (static_cast<uint32_t>(h23) << 16);
+    if (!RESID) {
+      hsum0 = hadd2(hsum0, e4m3x2_to_f16x2(h01));
+      hsum1 = hadd2(hsum1, e4m3x2_to_f16x2(h23));
+    } else {
+      // second e4m3 term: what the first rounding lost, times 2^4
+      float q0, q1, q2, q3;
+      unpack_e4m3x2(h01, q0, q1);
+      unpack_e4m3x2(h23, q2, q3);
+      wl[i] = pack_e4m3x4((p0 - q0) * 16.f, (p1 - q1) * 16.f, (p2 - q2) * 16.f, (p3 - q3) * 16.f);
+    }
+  }
+  sum_exact = (acc0 + acc1) + (acc2 + acc3);
+  if (!RESID) {
+    float s0, s1, s2, s3;
+    f16x2_to_float2(hsum0, s0, s1);
+    f16x2_to_float2(hsum1, s2, s3);
+    sum_rounded = (s0 + s1) + (s2 + s3);
+  } else {
+    sum_rounded = sum_exact;
+  }
+}
+
+__device__ __forceinline__ float block_max(const uint32_t (&s)[32]) {
+  float a0 = fmaxf(__uint_as_float(s[0]), __uint_as_float(s[1]));
+  float a1 = fmaxf(__uint_as_float(s[2]), __uint_as_float(s[3]));
+  float a2 = fmaxf(__uint_as_float(s[4]), __uint_as_float(s[5]));
+  float a3 = fmaxf(__uint_as_float(s[6]), __uint_as_float(s[7]));
+#pragma unroll
+  for (int i = 8; i < 32; i += 8) {
+    a0 = max3(a0, __uint_as_float(s[i + 0]), __uint_as_float(s[i + 1]));
+    a1 = max3(a1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+    a2 = max3(a2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+    a3 = max3(a3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+  }
+  return fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
+}
+
 // RESID: this instantiation handles the query blocks that see at most RESID_MAX_TILES key tiles and carries P
 // as two e4m3 terms; the other instantiation handles all other blocks.  Both are launched on the full grid and
 // a CTA leaves at once when the block is not of its kind.
@@ -88,7 +153,8 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t sfa_smem = v_smem + KV_STAGES * TILE_BYTES;  // P scales of the current tile
   const uint32_t sfb_smem = sfa_smem + SF_BYTES;              // unit scales for V
   const uint32_t sfa_lo_smem = sfb_smem + SF_BYTES;           // P residual scales
-  const uint32_t bar_base = sfa_lo_smem + SF_BYTES;
+  const uint32_t xch_smem = sfa_lo_smem + SF_BYTES;           // exchange between the two threads of a row
+  const uint32_t bar_base = xch_smem + XCH_BYTES;
   const uint32_t q_full = bar_base;
   auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto k_empty = [&](int s) { return bar_base + 8u * (1 + KV_STAGES + s); };
@@ -120,7 +186,6 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   // With few keys the e4m3 rounding of P does not average out; such blocks carry P as two e4m3 terms
   // (value + 2^-4 . residual) at the price of a second P.V product.
   if ((n_tiles <= RESID_MAX_TILES) != RESID) return;
-  constexpr bool resid = RESID;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -131,7 +196,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(v_empty(s), 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, SOFTMAX_THREADS);
     mbar_init(o_full, 1);
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
@@ -169,65 +234,80 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0 && n_tiles > 0) {
+    // The whole warp walks the loop (so addresses and descriptors stay warp-uniform); lane 0 issues.
+    if (n_tiles > 0) {
       constexpr uint32_t idesc_qk = make_idesc(0, 0, 0, 0, BM, BN);
+      const bool leader = lane == 0;
       const uint32_t s_tmem = tmem_base + S_COL;
       const uint32_t o_tmem = tmem_base + O_COL;
-      bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
+      bool ok = mbar_wait_warp(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
       const uint64_t q_desc = smem_desc_sw128(q_smem, 16, 1024);
+      const uint64_t sfa_desc = smem_desc_plain(sfa_smem, 16, 128);
+      const uint64_t sfb_desc = smem_desc_plain(sfb_smem, 16, 128);
+      const uint64_t sfa_lo_desc = smem_desc_plain(sfa_lo_smem, 16, 128);
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int s = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
-        if (!mbar_wait(k_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        if (!mbar_wait_warp(k_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) break;
         tc_fence_after();
-        const uint64_t k_desc = smem_desc_sw128(k_smem + s * TILE_BYTES, 16, 1024);
+        if (leader) {
+          const uint64_t k_desc = smem_desc_sw128(k_smem + s * TILE_BYTES, 16, 1024);
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k) {
-          // 32 e4m3 = 32 bytes along the head dimension inside the 128-byte swizzle span
-          mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k != 0);
+          for (int k = 0; k < D / 32; ++k) {
+            // 32 e4m3 = 32 bytes along the head dimension inside the 128-byte swizzle span
+            mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k != 0);
+          }
+          tc_commit(k_empty(s));
+          tc_commit(s_full);
         }
-        tc_commit(k_empty(s));
-        tc_commit(s_full);
-        if (!mbar_wait(p_full, j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
-        if (!mbar_wait(v_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        __syncwarp();
+        if (!mbar_wait_warp(p_full, j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
+        if (!mbar_wait_warp(v_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) break;
         tc_fence_after();
-        // V tile: 128 keys (the MMA's K) x 128 bytes of head dim (the MMA's N): MN-major,
-        // one 128-byte span wide, 8-key groups 1024 bytes apart, 32 keys per MMA = 4096 bytes
-        const uint64_t v_desc = smem_desc_sw128(v_smem + s * TILE_BYTES, 16, 1024);
-        tmem_cp_32x128b_warpx4(s_tmem + SFA_COL, smem_desc_plain(sfa_smem, 16, 128));
-        tmem_cp_32x128b_warpx4(s_tmem + SFB_COL, smem_desc_plain(sfb_smem, 16, 128));
-#pragma unroll
-        for (int k = 0; k < BN / 32; ++k) {
-          // P: 32 e4m3 per K step = 8 TMEM columns; scale byte k of the row's scale word
-          mma_mxf8_ts(o_tmem, s_tmem + 8 * k, v_desc + 256 * k, make_idesc_mx_major(BM, D, k, 0, 0, 1),
-                      s_tmem + SFA_COL, s_tmem + SFB_COL, (j | k) != 0);
-        }
-        if (resid) {
-          tmem_cp_32x128b_warpx4(s_tmem + SFA_LO_COL, smem_desc_plain(sfa_lo_smem, 16, 128));
+        if (leader) {
+          // V tile: 128 keys (the MMA's K) x 128 bytes of head dim (the MMA's N): MN-major,
+          // one 128-byte span wide, 8-key groups 1024 bytes apart, 32 keys per MMA = 4096 bytes
+          const uint64_t v_desc = smem_desc_sw128(v_smem + s * TILE_BYTES, 16, 1024);
+          tmem_cp_32x128b_warpx4(s_tmem + SFA_COL, sfa_desc);
+          tmem_cp_32x128b_warpx4(s_tmem + SFB_COL, sfb_desc);
 #pragma unroll
           for (int k = 0; k < BN / 32; ++k) {
-            mma_mxf8_ts(o_tmem, s_tmem + PLO_COL + 8 * k, v_desc + 256 * k,
-                        make_idesc_mx_major(BM, D, k, 0, 0, 1), s_tmem + SFA_LO_COL, s_tmem + SFB_COL, 1);
+            // P: 32 e4m3 per K step = 8 TMEM columns; scale byte k of the row's scale word
+            mma_mxf8_ts(o_tmem, s_tmem + 8 * k, v_desc + 256 * k, make_idesc_mx_major(BM, D, k, 0, 0, 1),
+                        s_tmem + SFA_COL, s_tmem + SFB_COL, (j | k) != 0);
           }
+          if (RESID) {
+            tmem_cp_32x128b_warpx4(s_tmem + SFA_LO_COL, sfa_lo_desc);
+#pragma unroll
+            for (int k = 0; k < BN / 32; ++k) {
+              mma_mxf8_ts(o_tmem, s_tmem + PLO_COL + 8 * k, v_desc + 256 * k,
+                          make_idesc_mx_major(BM, D, k, 0, 0, 1), s_tmem + SFA_LO_COL, s_tmem + SFB_COL, 1);
+            }
+          }
+          tc_commit(v_empty(s));
+          if (j == n_tiles - 1) tc_commit(o_full);
         }
-        tc_commit(v_empty(s));
-        if (j == n_tiles - 1) tc_commit(o_full);
+        __syncwarp();
       }
     }
-    __syncwarp();
   } else {
-    const int quad = warp & 3;
+    // two threads per row: `half` selects keys [64 half, 64 half + 64) of every tile
+    const int quad = warp & 3;  // TMEM lanes [32 quad, 32 quad + 32) are the ones this warp may touch
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;  // row of the tile == TMEM lane
     const int row = m0 + r;
+    const int col0 = 64 * half;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t s_tmem = tmem_base + lane_addr + S_COL;
     const uint32_t o_tmem = tmem_base + lane_addr + O_COL;
+    const uint32_t x_mine = xch_smem + (half * BM + r) * 4;
+    const uint32_t x_other = xch_smem + ((half ^ 1) * BM + r) * 4;
     const int sc = b * p.Hkv + hkv;
     const float beta = p.softmax_scale * p.q_descale[sc] * p.k_descale[sc] * 1.4426950408889634f;
     const float sv = p.v_descale[sc];
     const int row_limit = p.causal ? row + shift : nk - 1;  // last visible key of this row
-    // m_ref: reference exponent of this row (O and l are in units of 2^-m_ref)
-    // l: exact row sum (for lse and pmax); lq: sum of the rounded P the MMA multiplies V with (normaliser of O)
+    // m_ref: reference exponent of the row (O and the sums are in units of 2^-m_ref)
+    // l: exact sum of this thread's half (for lse and pmax); lq: sum of the rounded P (normaliser of O)
     float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f, lq = 0.f;
     bool ok = true;
 
@@ -239,124 +319,77 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       tc_fence_after();
       const int key0 = j * BN;
       const bool tile_masked = (key0 + BN > nk) || (p.causal && key0 + BN - 1 > m0 + shift);
-      const int limit = min(row_limit, nk - 1) - key0;  // columns > limit are masked
+      const int limit = min(row_limit, nk - 1) - key0 - col0;  // of this thread's 64 columns, those > limit are masked
 
-      // the whole row of S: 128 raw scores
-      uint32_t sraw[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, sraw[c]);
+      uint32_t sraw[2][32];
+      tmem_ld32(s_tmem + col0, sraw[0]);
+      tmem_ld32(s_tmem + col0 + 32, sraw[1]);
       tc_wait_ld();
       if (tile_masked) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i > limit) sraw[c][i] = 0xff800000u;  // -inf
       }
-      // maxima per block of 32 keys
-      float cm[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float a0 = fmaxf(__uint_as_float(sraw[c][0]), __uint_as_float(sraw[c][1]));
-        float a1 = fmaxf(__uint_as_float(sraw[c][2]), __uint_as_float(sraw[c][3]));
-        float a2 = fmaxf(__uint_as_float(sraw[c][4]), __uint_as_float(sraw[c][5]));
-        float a3 = fmaxf(__uint_as_float(sraw[c][6]), __uint_as_float(sraw[c][7]));
-#pragma unroll
-        for (int i = 8; i < 32; i += 8) {
-          a0 = max3(a0, __uint_as_float(sraw[c][i + 0]), __uint_as_float(sraw[c][i + 1]));
-          a1 = max3(a1, __uint_as_float(sraw[c][i + 2]), __uint_as_float(sraw[c][i + 3]));
-          a2 = max3(a2, __uint_as_float(sraw[c][i + 4]), __uint_as_float(sraw[c][i + 5]));
-          a3 = max3(a3, __uint_as_float(sraw[c][i + 6]), __uint_as_float(sraw[c][i + 7]));
-        }
-        cm[c] = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * beta;  // beta > 0 (checked on the host)
-      }
-      const float t = fmaxf(fmaxf(cm[0], cm[1]), fmaxf(cm[2], cm[3]));
+      float cm[2];
+      cm[0] = block_max(sraw[0]) * beta;  // beta > 0 (checked on the host)
+      cm[1] = block_max(sraw[1]) * beta;
+      const float own = fmaxf(cm[0], cm[1]);
+      asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine), "f"(own) : "memory");
+      pair_sync(1 + quad);
+      float other;
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(x_other) : "memory");
+      const float t = fmaxf(own, other);
       m_true = fmaxf(m_true, t);
       const bool need = t > -INFINITY && (m_ref == -INFINITY || t > m_ref + RESCALE_TAU);
       float corr = 1.f;
       if (need) {
-        const float m_new = t;
-        corr = m_ref == -INFINITY ? 0.f : exp2f(m_ref - m_new);
+        corr = m_ref == -INFINITY ? 0.f : exp2f(m_ref - t);
         l *= corr;
         lq *= corr;
-        m_ref = m_new;
+        m_ref = t;
       }
       if (j > 0 && __any_sync(0xffffffffu, need)) {
         // the previous P.V has completed (s_full tracks every earlier MMA), so O is quiescent
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
-          tmem_ld32(o_tmem + c * 32, v);
+          tmem_ld32(o_tmem + col0 + c * 32, v);
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-          tmem_st32(o_tmem + c * 32, v);
+          tmem_st32(o_tmem + col0 + c * 32, v);
         }
         tc_wait_st();
       }
 
-      // P as MXFP8: per block of 32 keys an integer exponent e_blk >= block maximum
-      uint32_t sf_word = 0, sf_word_lo = 0;
+      uint32_t sf_pair = 0, sf_pair_lo = 0;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         const bool live = cm[c] > -INFINITY;
         const float kf = live ? ceilf(cm[c] - m_ref) : 0.f;  // block exponent relative to the row reference
         const float bias = live ? (static_cast<float>(P_OFFSET) - kf) - m_ref : 0.f;
-        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-        uint32_t hsum0 = 0, hsum1 = 0;  // f16x2 partial sums of the rounded codes
         uint32_t w[8], wl[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float p0 = fmaf(__uint_as_float(sraw[c][4 * i + 0]), beta, bias);
-          float p1 = fmaf(__uint_as_float(sraw[c][4 * i + 1]), beta, bias);
-          float p2 = fmaf(__uint_as_float(sraw[c][4 * i + 2]), beta, bias);
-          float p3 = fmaf(__uint_as_float(sraw[c][4 * i + 3]), beta, bias);
-          p0 = ex2_approx(p0);
-          p1 = ex2_approx(p1);
-          p2 = ex2_approx(p2);
-          p3 = ex2_approx(p3);
-          const uint16_t h01 = cvt_e4m3x2(p0, p1), h23 = cvt_e4m3x2(p2, p3);
-          w[i] = static_cast<uint32_t>(h01) | (static_cast<uint32_t>(h23) << 16);
-          acc0 += p0;
-          acc1 += p1;
-          acc2 += p2;
-          acc3 += p3;
-          if (!resid) {
-            // the normaliser of O sums what the MMA will see: the rounded codes, exact in f16
-            hsum0 = hadd2(hsum0, e4m3x2_to_f16x2(h01));
-            hsum1 = hadd2(hsum1, e4m3x2_to_f16x2(h23));
-          } else {
-            // second e4m3 term: what the first rounding lost, times 2^4
-            float q0, q1, q2, q3;
-            unpack_e4m3x2(h01, q0, q1);
-            unpack_e4m3x2(h23, q2, q3);
-            wl[i] = pack_e4m3x4((p0 - q0) * 16.f, (p1 - q1) * 16.f, (p2 - q2) * 16.f, (p3 - q3) * 16.f);
-          }
-        }
-        tmem_st8(s_tmem + c * 8, w);
-        if (resid) tmem_st8(s_tmem + PLO_COL + c * 8, wl);
-        // scale of this block relative to the row reference: 2^(e_blk - offset - m_ref)
+        float sum_exact, sum_rounded;
+        softmax_block<RESID>(sraw[c], beta, bias, w, wl, sum_exact, sum_rounded);
+        const int blk = 2 * half + c;
+        tmem_st8(s_tmem + blk * 8, w);
+        if (RESID) tmem_st8(s_tmem + PLO_COL + blk * 8, wl);
         int sf = live ? 127 + static_cast<int>(kf) - P_OFFSET : 0;
         sf = min(max(sf, 0), 254);
         const float blk_scale = __uint_as_float(static_cast<uint32_t>(sf) << 23);
-        const float blk_sum = (acc0 + acc1) + (acc2 + acc3);
-        if (live) l = fmaf(blk_sum, blk_scale, l);
-        if (!resid) {
-          float s0, s1, s2, s3;
-          f16x2_to_float2(hsum0, s0, s1);
-          f16x2_to_float2(hsum1, s2, s3);
-          if (live) lq = fmaf((s0 + s1) + (s2 + s3), blk_scale, lq);
-        } else {
-          if (live) lq = fmaf(blk_sum, blk_scale, lq);
+        if (live) {
+          l = fmaf(sum_exact, blk_scale, l);
+          lq = fmaf(sum_rounded, blk_scale, lq);
         }
-        sf_word |= static_cast<uint32_t>(sf) << (8 * c);
-        sf_word_lo |= static_cast<uint32_t>(max(sf - 4, 0)) << (8 * c);
+        sf_pair |= static_cast<uint32_t>(sf) << (8 * c);
+        sf_pair_lo |= static_cast<uint32_t>(max(sf - 4, 0)) << (8 * c);
       }
-      asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfa_smem + (r % 32) * 16 + (r / 32) * 4), "r"(sf_word)
-                   : "memory");
-      if (resid) {
-        asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfa_lo_smem + (r % 32) * 16 + (r / 32) * 4),
-                     "r"(sf_word_lo)
+      const uint32_t sf_off = (r % 32) * 16 + (r / 32) * 4 + 2 * half;
+      asm volatile("st.shared.u16 [%0], %1;" ::"r"(sfa_smem + sf_off), "h"(static_cast<uint16_t>(sf_pair)) : "memory");
+      if (RESID) {
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(sfa_lo_smem + sf_off), "h"(static_cast<uint16_t>(sf_pair_lo))
                      : "memory");
       }
       fence_proxy_async_smem();
@@ -367,17 +400,26 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
     // epilogue
     if (n_tiles > 0 && ok) ok = mbar_wait_warp(o_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
+    // the two halves of a row add up their sums (every softmax thread takes part, also after a failed wait)
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine + 2 * BM * 4), "f"(l) : "memory");
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine + 4 * BM * 4), "f"(lq) : "memory");
+    pair_sync(1 + quad);
+    float l_other, lq_other;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_other) : "r"(x_other + 2 * BM * 4) : "memory");
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(lq_other) : "r"(x_other + 4 * BM * 4) : "memory");
+    l += l_other;
+    lq += lq_other;
     if (ok) {
       tc_fence_after();
       const bool empty = !(l > 0.f);
       const float inv = empty ? 0.f : sv / lq;
-      __nv_bfloat16* out_row =
-          p.out + b * p.out_stride_b + hq * p.out_stride_h + static_cast<int64_t>(row) * p.out_stride_n;
+      __nv_bfloat16* out_row = p.out + b * p.out_stride_b + hq * p.out_stride_h +
+                               static_cast<int64_t>(row) * p.out_stride_n + col0;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
         if (n_tiles > 0) {
-          tmem_ld32(o_tmem + c * 32, v);
+          tmem_ld32(o_tmem + col0 + c * 32, v);
           tc_wait_ld();
         } else {
 #pragma unroll
@@ -396,7 +438,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           }
         }
       }
-      if (p.write_lse && row < p.Nq) {
+      if (p.write_lse && half == 0 && row < p.Nq) {
         const int64_t off = b * p.lse_stride_b + hq * p.lse_stride_h + row;
         const float lse = empty ? INFINITY : m_ref + log2f(l);
         p.lse[off] = p.lse_natural ? lse * 0.6931471805599453f : lse;

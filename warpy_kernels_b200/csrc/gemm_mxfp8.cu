@@ -15,6 +15,9 @@
 //     atoms.  Warp 1: tcgen05.cp of the atoms into TMEM, then four
 //     tcgen05.mma kind::mxf8f6f4.block_scale (K = 32 each; the scale-factor id selects
 //     the byte of the K block).  Warps 2-5: epilogue from TMEM.
+//     TMEM: two 256-column accumulators that share 64 columns ([0,256) and [192,448)) plus the
+//     scale-factor columns.  The epilogue drains the shared columns of a tile first and then
+//     lets the next tile's main loop start while it drains the rest.
 //
 // Arithmetic follows the reference's block-scaled path (warpy_kernels/gemm/sm120.py:121-146:
 // e4m3 products scaled by 2^(sfa-127) per row and 32-element K block, fp32 accumulate)
@@ -40,8 +43,8 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int ACC_COL = 0;
-constexpr int SF_COL = 256;        // scale-factor columns start here
+constexpr int ACC_STRIDE = 192;    // accumulator slot a lives in columns [192 a, 192 a + 256)
+constexpr int SF_COL = 448;        // scale-factor columns start here
 constexpr int SF_SLOTS = 4;        // one slot per smem stage
 constexpr int SF_SLOT_COLS = 12;   // 4 (A: 128 rows) + 8 (B: 256 rows)
 
@@ -100,9 +103,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  const uint32_t tfull_bar = bar_base + 8u * (2 * STAGES);
-  const uint32_t tempty_bar = bar_base + 8u * (2 * STAGES + 1);
-  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 2);
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t ovl_bar = bar_base + 8u * (2 * STAGES + 4);  // the shared columns of the last tile are drained
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 5);
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -117,8 +121,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(tfull_bar, 1);
-    mbar_init(tempty_bar, 4);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    mbar_init(ovl_bar, 4);
     mbar_fence_init();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
@@ -175,9 +182,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local) {
-        if (!mbar_wait(tempty_bar, (local & 1) ^ 1, p.status, WK_ERR_TIMEOUT_TMEM)) break;
+        const int acc = local & 1;
+        // this slot was drained two tiles ago, and the previous tile has given up the columns it shares
+        if (!mbar_wait(tempty_bar(acc), ((local >> 1) & 1) ^ 1, p.status, WK_ERR_TIMEOUT_TMEM)) break;
+        if (local > 0 && !mbar_wait(ovl_bar, (local - 1) & 1, p.status, WK_ERR_TIMEOUT_TMEM)) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + ACC_COL;
+        const uint32_t d_tmem = tmem_base + acc * ACC_STRIDE;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, p.status, WK_ERR_TIMEOUT_LOAD)) {
             ok = false;
@@ -206,7 +216,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             phase ^= 1;
           }
         }
-        if (ok) tc_commit(tfull_bar);
+        if (ok) tc_commit(tfull_bar(acc));
       }
     }
     __syncwarp();
@@ -218,15 +228,25 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     int local = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const TileCoord tc = tile_coord(tile, num_m, num_n, p.group_m);
-      if (!mbar_wait_warp(tfull_bar, local & 1, p.status, WK_ERR_TIMEOUT_MMA)) break;
+      const int acc = local & 1;
+      if (!mbar_wait_warp(tfull_bar(acc), (local >> 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) break;
       tc_fence_after();
+      // column chunks in the order they are drained: the 64 columns shared with the other slot first
+      const int first_chunk = acc == 0 ? 6 : 0;
       const int row = tc.m_blk * BM + quad * 32 + lane;
       const int64_t row_off = static_cast<int64_t>(row) * p.N + tc.n_blk * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int ci = 0; ci < BN / 32; ++ci) {
+        const int c = (ci + first_chunk) & 7;
         uint32_t v[32];
-        tmem_ld32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ACC_COL + c * 32, v);
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * ACC_STRIDE + c * 32, v);
         tc_wait_ld();
+        if (ci == 1) {
+          // both shared chunks are in registers: the next tile's main loop may overwrite them
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(ovl_bar);
+        }
         if (tc.n_blk * BN + c * 32 < p.N) {
           float f[32];
 #pragma unroll
@@ -270,7 +290,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar);
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
     }
   }
 

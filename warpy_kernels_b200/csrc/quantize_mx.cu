@@ -22,7 +22,7 @@ constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
-  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p));
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -31,8 +31,8 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
   }
 }
 __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
-  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-  const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  const float4 a = __ldcs(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
   v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
   v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
@@ -46,7 +46,9 @@ __device__ __forceinline__ void mx_scale(uint32_t amax_bits, uint32_t& e, float&
   inv = __uint_as_float(static_cast<uint32_t>(max(254 - t, 1)) << 23);
 }
 
-template <typename T>
+// CONTIG: rows are back to back (ld_x == cols), so input, code and scale offsets are all linear in the group
+// index and no division is needed.
+template <typename T, bool CONTIG>
 __global__ void __launch_bounds__(kThreads)
 quantize_mx_kernel(const T* __restrict__ x, int64_t ld_x, uint8_t* __restrict__ q,
                    uint8_t* __restrict__ s, int64_t total_groups, int groups_per_row) {
@@ -55,17 +57,18 @@ quantize_mx_kernel(const T* __restrict__ x, int64_t ld_x, uint8_t* __restrict__ 
   int64_t base = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
   for (; base - threadIdx.x % 32 < total_groups; base += stride * kUnroll) {
     float v[kUnroll][8];
-    int64_t row[kUnroll];
-    int col8[kUnroll];
     bool ok[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t g = base + u * stride;
       ok[u] = g < total_groups;
-      row[u] = g / groups_per_row;
-      col8[u] = static_cast<int>(g - row[u] * groups_per_row);
       if (ok[u]) {
-        load8(x + row[u] * ld_x + static_cast<int64_t>(col8[u]) * 8, v[u]);
+        int64_t off = g * 8;
+        if (!CONTIG) {
+          const uint32_t row = static_cast<uint32_t>(g / groups_per_row);
+          off = row * ld_x + (g - static_cast<int64_t>(row) * groups_per_row) * 8;
+        }
+        load8(x + off, v[u]);
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
@@ -73,6 +76,7 @@ quantize_mx_kernel(const T* __restrict__ x, int64_t ld_x, uint8_t* __restrict__ 
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
+      const int64_t g = base + u * stride;
       uint32_t amax = 0;
 #pragma unroll
       for (int i = 0; i < 8; ++i) amax = max(amax, __float_as_uint(v[u][i]) & 0x7fffffffu);
@@ -87,9 +91,9 @@ quantize_mx_kernel(const T* __restrict__ x, int64_t ld_x, uint8_t* __restrict__ 
                               __fmul_rn(v[u][2], inv), __fmul_rn(v[u][3], inv));
         codes.y = pack_e4m3x4(__fmul_rn(v[u][4], inv), __fmul_rn(v[u][5], inv),
                               __fmul_rn(v[u][6], inv), __fmul_rn(v[u][7], inv));
-        const int64_t cols = static_cast<int64_t>(groups_per_row) * 8;
-        *reinterpret_cast<uint2*>(q + row[u] * cols + static_cast<int64_t>(col8[u]) * 8) = codes;
-        if ((col8[u] & 3) == 0) s[row[u] * (groups_per_row / 4) + (col8[u] >> 2)] = static_cast<uint8_t>(e);
+        // the outputs are contiguous [rows, cols] and [rows, cols / 32]: linear in g whatever ld_x is
+        __stcs(reinterpret_cast<uint2*>(q + g * 8), codes);
+        if ((g & 3) == 0) s[g >> 2] = static_cast<uint8_t>(e);
       }
     }
   }
@@ -105,8 +109,13 @@ int launch(const T* x, int64_t rows, int64_t cols, int64_t ld_x, uint8_t* q, uin
   // 8 resident CTAs of 256 threads fill an SM; more CTAs than that only add tail.
   int64_t grid = want < static_cast<int64_t>(sms) * 8 ? want : static_cast<int64_t>(sms) * 8;
   if (grid < 1) grid = 1;
-  quantize_mx_kernel<T><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-      x, ld_x, q, s, total, static_cast<int>(cols / 8));
+  if (ld_x == cols) {
+    quantize_mx_kernel<T, true><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+        x, ld_x, q, s, total, static_cast<int>(cols / 8));
+  } else {
+    quantize_mx_kernel<T, false><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+        x, ld_x, q, s, total, static_cast<int>(cols / 8));
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
 }
 
@@ -116,7 +125,7 @@ int launch(const T* x, int64_t rows, int64_t cols, int64_t ld_x, uint8_t* q, uin
 extern "C" int wk_quantize_mx(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ld_x,
                               void* q, void* s, void* stream) {
   if (rows < 0 || cols < 0 || cols % 32 != 0 || ld_x < cols || ld_x % 8 != 0) return WK_E_ARG;
-  if (cols / 8 > 0x7fffffff) return WK_E_ARG;
+  if (cols / 8 > 0x7fffffff || rows > 0x7fffffff) return WK_E_ARG;
   if (rows == 0 || cols == 0) return 0;
   if (!x || !q || !s || !wk::aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 7)) return WK_E_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
