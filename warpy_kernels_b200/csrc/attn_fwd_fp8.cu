@@ -38,6 +38,9 @@
 #include "host_common.h"
 
 namespace wk {
+#ifdef WK_FWD_TRACE
+__device__ long long g_trace[16 * 64];
+#endif
 namespace {
 
 constexpr int BM = 128;       // queries per CTA
@@ -53,13 +56,26 @@ constexpr int O_COL = 128;
 constexpr int P_OFFSET = 8;          // a block's largest P is stored in (2^7, 2^8]
 constexpr float RESCALE_TAU = 1.0f;  // refresh the row reference when the maximum outgrew it by more than this (log2)
 constexpr int SF_BYTES = 512;        // one scale-factor atom: 128 rows x 4 blocks of 32 keys
-constexpr int SFA_COL = 64;          // TMEM columns (inside the consumed part of S) the scales are copied to
-constexpr int SFB_COL = 68;
-constexpr int SFA_LO_COL = 72;       // scales of the residual term
-constexpr int PLO_COL = 32;          // residual P codes (S columns 32..63)
+// After the softmax the 128 S columns are reused: block k of 32 keys keeps its P codes in columns
+// [32 k, 32 k + 8) and its residual codes in [32 k + 8, 32 k + 16); the scale factors are copied to 16..27.
+constexpr int PLO_OFF = 8;
+constexpr int SFA_COL = 16;
+constexpr int SFB_COL = 20;
+constexpr int SFA_LO_COL = 24;
 constexpr int RESID_MAX_TILES = 4;   // query blocks that see at most this many key tiles carry the residual term
 constexpr int XCH_BYTES = 3 * 2 * BM * 4;  // pair exchange: maximum, row sum, rounded row sum
 constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 3 * SF_BYTES + XCH_BYTES + 1024 + 256;
+
+#ifdef WK_FWD_TRACE
+#define TRACE(slot, idx)                                                                  \
+  do {                                                                                    \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 64) g_trace[(slot) * 64 + (idx)] = clock64(); \
+  } while (0)
+#else
+#define TRACE(slot, idx) \
+  do {                   \
+  } while (0)
+#endif
 
 struct FwdParams {
   __nv_bfloat16* out;
@@ -250,6 +266,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const uint32_t ph = (j / KV_STAGES) & 1;
         if (!mbar_wait_warp(k_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) break;
         tc_fence_after();
+        if (leader) TRACE(0, j);
         if (leader) {
           const uint64_t k_desc = smem_desc_sw128(k_smem + s * TILE_BYTES, 16, 1024);
 #pragma unroll
@@ -259,9 +276,11 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           }
           tc_commit(k_empty(s));
           tc_commit(s_full);
+          TRACE(1, j);
         }
         __syncwarp();
         if (!mbar_wait_warp(p_full, j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
+        if (leader) TRACE(2, j);
         if (!mbar_wait_warp(v_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) break;
         tc_fence_after();
         if (leader) {
@@ -272,19 +291,20 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           tmem_cp_32x128b_warpx4(s_tmem + SFB_COL, sfb_desc);
 #pragma unroll
           for (int k = 0; k < BN / 32; ++k) {
-            // P: 32 e4m3 per K step = 8 TMEM columns; scale byte k of the row's scale word
-            mma_mxf8_ts(o_tmem, s_tmem + 8 * k, v_desc + 256 * k, make_idesc_mx_major(BM, D, k, 0, 0, 1),
+            // P: 32 e4m3 per K step = 8 TMEM columns at column 32 k; scale byte k of the row's scale word
+            mma_mxf8_ts(o_tmem, s_tmem + 32 * k, v_desc + 256 * k, make_idesc_mx_major(BM, D, k, 0, 0, 1),
                         s_tmem + SFA_COL, s_tmem + SFB_COL, (j | k) != 0);
           }
           if (RESID) {
             tmem_cp_32x128b_warpx4(s_tmem + SFA_LO_COL, sfa_lo_desc);
 #pragma unroll
             for (int k = 0; k < BN / 32; ++k) {
-              mma_mxf8_ts(o_tmem, s_tmem + PLO_COL + 8 * k, v_desc + 256 * k,
+              mma_mxf8_ts(o_tmem, s_tmem + 32 * k + PLO_OFF, v_desc + 256 * k,
                           make_idesc_mx_major(BM, D, k, 0, 0, 1), s_tmem + SFA_LO_COL, s_tmem + SFB_COL, 1);
             }
           }
           tc_commit(v_empty(s));
+          TRACE(3, j);
           if (j == n_tiles - 1) tc_commit(o_full);
         }
         __syncwarp();
@@ -317,27 +337,30 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         break;
       }
       tc_fence_after();
+      if (warp == 2 && lane == 0) TRACE(8, j);
       const int key0 = j * BN;
       const bool tile_masked = (key0 + BN > nk) || (p.causal && key0 + BN - 1 > m0 + shift);
       const int limit = min(row_limit, nk - 1) - key0 - col0;  // of this thread's 64 columns, those > limit are masked
 
-      uint32_t sraw[2][32];
-      tmem_ld32(s_tmem + col0, sraw[0]);
-      tmem_ld32(s_tmem + col0 + 32, sraw[1]);
-      tc_wait_ld();
-      if (tile_masked) {
+      // pass 1: block maxima (the scores are read again in pass 2; holding all of them would spill)
+      float cm[2];
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sraw[32];
+        tmem_ld32(s_tmem + col0 + c * 32, sraw);
+        tc_wait_ld();
+        if (tile_masked) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i > limit) sraw[c][i] = 0xff800000u;  // -inf
+            if (c * 32 + i > limit) sraw[i] = 0xff800000u;  // -inf
+        }
+        cm[c] = block_max(sraw) * beta;  // beta > 0 (checked on the host)
       }
-      float cm[2];
-      cm[0] = block_max(sraw[0]) * beta;  // beta > 0 (checked on the host)
-      cm[1] = block_max(sraw[1]) * beta;
       const float own = fmaxf(cm[0], cm[1]);
       asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine), "f"(own) : "memory");
+      if (warp == 2 && lane == 0) TRACE(10, j);
       pair_sync(1 + quad);
+      if (warp == 2 && lane == 0) TRACE(11, j);
       float other;
       asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(x_other) : "memory");
       const float t = fmaxf(own, other);
@@ -370,12 +393,20 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const bool live = cm[c] > -INFINITY;
         const float kf = live ? ceilf(cm[c] - m_ref) : 0.f;  // block exponent relative to the row reference
         const float bias = live ? (static_cast<float>(P_OFFSET) - kf) - m_ref : 0.f;
+        uint32_t sraw[32];
+        tmem_ld32(s_tmem + col0 + c * 32, sraw);
+        tc_wait_ld();
+        if (tile_masked) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i > limit) sraw[i] = 0xff800000u;  // -inf
+        }
         uint32_t w[8], wl[8];
         float sum_exact, sum_rounded;
-        softmax_block<RESID>(sraw[c], beta, bias, w, wl, sum_exact, sum_rounded);
-        const int blk = 2 * half + c;
-        tmem_st8(s_tmem + blk * 8, w);
-        if (RESID) tmem_st8(s_tmem + PLO_COL + blk * 8, wl);
+        softmax_block<RESID>(sraw, beta, bias, w, wl, sum_exact, sum_rounded);
+        // the codes go to the first columns of the 32 score columns this thread has just consumed
+        tmem_st8(s_tmem + col0 + c * 32, w);
+        if (RESID) tmem_st8(s_tmem + col0 + c * 32 + PLO_OFF, wl);
         int sf = live ? 127 + static_cast<int>(kf) - P_OFFSET : 0;
         sf = min(max(sf, 0), 254);
         const float blk_scale = __uint_as_float(static_cast<uint32_t>(sf) << 23);
@@ -386,6 +417,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         sf_pair |= static_cast<uint32_t>(sf) << (8 * c);
         sf_pair_lo |= static_cast<uint32_t>(max(sf - 4, 0)) << (8 * c);
       }
+      if (warp == 2 && lane == 0) TRACE(12, j);
       const uint32_t sf_off = (r % 32) * 16 + (r / 32) * 4 + 2 * half;
       asm volatile("st.shared.u16 [%0], %1;" ::"r"(sfa_smem + sf_off), "h"(static_cast<uint16_t>(sf_pair)) : "memory");
       if (RESID) {
@@ -396,6 +428,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(p_full);
+      if (warp == 2 && lane == 0) TRACE(13, j);
     }
 
     // epilogue
@@ -535,3 +568,9 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
   return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
 }
 
+
+#ifdef WK_FWD_TRACE
+extern "C" int wk_debug_read(long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, wk::g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : -2;
+}
+#endif
