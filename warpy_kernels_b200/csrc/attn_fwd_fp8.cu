@@ -1,17 +1,18 @@
 // FP8 (e4m3) flash-attention forward for sm_100a, head dimension 128.
 //
-// One CTA = 128 queries of one (batch, query head); two CTAs share an SM so that
-// one CTA's softmax overlaps the other's tensor-core work.  320 threads:
-//   warp 0      TMA producer: Q tile once, then K and V tiles (128 keys x 128 bytes,
-//               128-byte swizzle) into two-stage rings
-//   warp 1      allocates 256 TMEM columns (S: 0..127, O: 128..255) and issues
-//               tcgen05.mma:  S = Q.K^T (kind::f8f6f4, both operands K-major from shared
-//               memory), O += P.V (kind::mxf8f6f4.block_scale, P read from TMEM, V MN-major
-//               from shared memory)
-//   warps 2-9   softmax, two threads per query row (64 keys of the tile each): read S from
-//               TMEM, P as MXFP8 (e4m3 codes written back over the S columns plus one
-//               power-of-two scale per row and 32 keys, staged through shared memory), row
-//               sums; finally O . v_descale / l -> bf16, lse (base 2) and pmax
+// One CTA = 128 queries of one (batch, query head), two CTAs per SM, key tiles of 64.
+// 192 threads:
+//   warp 0      TMA producer: Q tile once, then K and V tiles (64 keys x 128 bytes,
+//               128-byte swizzle) into four-stage rings
+//   warp 1      allocates 256 TMEM columns (two S buffers of 64 columns, O: 128..255) and
+//               issues tcgen05.mma:  S = Q.K^T (kind::f8f6f4, both operands K-major from
+//               shared memory) always two tiles ahead, so the softmax never waits for it;
+//               O += P.V (kind::mxf8f6f4.block_scale, P read from TMEM, V MN-major from
+//               shared memory) as soon as a tile's P is there
+//   warps 2-5   softmax, one thread per query row: read S from TMEM, P as MXFP8 (e4m3
+//               codes written back over the S columns plus one power-of-two scale per row
+//               and 32 keys, staged through shared memory), row sums; finally
+//               O . v_descale / l -> bf16, lse (base 2) and pmax
 //
 // Numerics follow the reference's forward (warpy_kernels/attn/fwd_base.py:297-360,
 // 939-988; fwd_sm120.py:93-136): logits in base 2 with beta = softmax_scale .
@@ -38,44 +39,30 @@
 #include "host_common.h"
 
 namespace wk {
-#ifdef WK_FWD_TRACE
-__device__ long long g_trace[16 * 64];
-#endif
 namespace {
 
 constexpr int BM = 128;       // queries per CTA
-constexpr int BN = 128;       // keys per tile
+constexpr int BN = 64;        // keys per tile
 constexpr int D = 128;        // head dimension (bytes per row in e4m3)
-constexpr int KV_STAGES = 2;
-constexpr int TILE_BYTES = BN * D;  // 16 KiB
-constexpr int THREADS = 320;
-constexpr int SOFTMAX_THREADS = 256;
+constexpr int KV_STAGES = 4;
+constexpr int Q_BYTES = BM * D;     // 16 KiB
+constexpr int KV_BYTES = BN * D;    // 8 KiB
+constexpr int THREADS = 192;
+constexpr int SOFTMAX_THREADS = 128;
 constexpr int TMEM_COLS = 256;
-constexpr int S_COL = 0;
+constexpr int S_COLS = 64;    // one S buffer; buffer b starts at column 64 b
 constexpr int O_COL = 128;
 constexpr int P_OFFSET = 8;          // a block's largest P is stored in (2^7, 2^8]
 constexpr float RESCALE_TAU = 1.0f;  // refresh the row reference when the maximum outgrew it by more than this (log2)
 constexpr int SF_BYTES = 512;        // one scale-factor atom: 128 rows x 4 blocks of 32 keys
-// After the softmax the 128 S columns are reused: block k of 32 keys keeps its P codes in columns
+// After the softmax the 64 columns of an S buffer are reused: block k of 32 keys keeps its P codes in columns
 // [32 k, 32 k + 8) and its residual codes in [32 k + 8, 32 k + 16); the scale factors are copied to 16..27.
 constexpr int PLO_OFF = 8;
 constexpr int SFA_COL = 16;
 constexpr int SFB_COL = 20;
 constexpr int SFA_LO_COL = 24;
-constexpr int RESID_MAX_TILES = 4;   // query blocks that see at most this many key tiles carry the residual term
-constexpr int XCH_BYTES = 3 * 2 * BM * 4;  // pair exchange: maximum, row sum, rounded row sum
-constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 3 * SF_BYTES + XCH_BYTES + 1024 + 256;
-
-#ifdef WK_FWD_TRACE
-#define TRACE(slot, idx)                                                                  \
-  do {                                                                                    \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 64) g_trace[(slot) * 64 + (idx)] = clock64(); \
-  } while (0)
-#else
-#define TRACE(slot, idx) \
-  do {                   \
-  } while (0)
-#endif
+constexpr int RESID_MAX_TILES = 8;   // query blocks that see at most this many key tiles carry the residual term
+constexpr int SMEM_BYTES = Q_BYTES + 2 * KV_STAGES * KV_BYTES + 5 * SF_BYTES + 1024 + 256;
 
 struct FwdParams {
   __nv_bfloat16* out;
@@ -94,10 +81,6 @@ struct FwdParams {
   float softmax_scale;
   int* status;
 };
-
-__device__ __forceinline__ void pair_sync(int id) {
-  asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
-}
 
 // One block of 32 keys of one row: P codes (and the residual codes), the exact and the rounded sum.
 template <bool RESID>
@@ -164,22 +147,24 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = smem_base;
-  const uint32_t k_smem = smem_base + TILE_BYTES;
-  const uint32_t v_smem = k_smem + KV_STAGES * TILE_BYTES;
-  const uint32_t sfa_smem = v_smem + KV_STAGES * TILE_BYTES;  // P scales of the current tile
-  const uint32_t sfb_smem = sfa_smem + SF_BYTES;              // unit scales for V
-  const uint32_t sfa_lo_smem = sfb_smem + SF_BYTES;           // P residual scales
-  const uint32_t xch_smem = sfa_lo_smem + SF_BYTES;           // exchange between the two threads of a row
-  const uint32_t bar_base = xch_smem + XCH_BYTES;
+  const uint32_t k_smem = q_smem + Q_BYTES;
+  const uint32_t v_smem = k_smem + KV_STAGES * KV_BYTES;
+  const uint32_t sf_smem = v_smem + KV_STAGES * KV_BYTES;
+  auto sfa_smem = [&](int b) { return sf_smem + b * SF_BYTES; };            // P scales, one atom per S buffer
+  auto sfa_lo_smem = [&](int b) { return sf_smem + (2 + b) * SF_BYTES; };   // residual scales
+  const uint32_t sfb_smem = sf_smem + 4 * SF_BYTES;                         // unit scales for V
+  const uint32_t bar_base = sf_smem + 5 * SF_BYTES;
   const uint32_t q_full = bar_base;
   auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto k_empty = [&](int s) { return bar_base + 8u * (1 + KV_STAGES + s); };
   auto v_full = [&](int s) { return bar_base + 8u * (1 + 2 * KV_STAGES + s); };
   auto v_empty = [&](int s) { return bar_base + 8u * (1 + 3 * KV_STAGES + s); };
-  const uint32_t s_full = bar_base + 8u * (1 + 4 * KV_STAGES);
-  const uint32_t p_full = s_full + 8;
-  const uint32_t o_full = s_full + 16;
-  const uint32_t tmem_slot = s_full + 24;
+  const uint32_t misc_bar = bar_base + 8u * (1 + 4 * KV_STAGES);
+  auto s_full = [&](int b) { return misc_bar + 8u * b; };
+  auto p_full = [&](int b) { return misc_bar + 8u * (2 + b); };
+  const uint32_t pv_done = misc_bar + 8u * 4;
+  const uint32_t o_full = misc_bar + 8u * 5;
+  const uint32_t tmem_slot = misc_bar + 8u * 6;
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -211,8 +196,11 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(v_full(s), 1);
       mbar_init(v_empty(s), 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, SOFTMAX_THREADS);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(s_full(i), 1);
+      mbar_init(p_full(i), SOFTMAX_THREADS);
+    }
+    mbar_init(pv_done, 1);
     mbar_init(o_full, 1);
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
@@ -235,135 +223,122 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(q_full, TILE_BYTES);
+      mbar_expect_tx(q_full, Q_BYTES);
       tma_load_4d(q_smem, &tmap_q, q_full, 0, m0, hq, b);
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
         if (!mbar_wait(k_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
-        mbar_expect_tx(k_full(s), TILE_BYTES);
-        tma_load_4d(k_smem + s * TILE_BYTES, &tmap_k, k_full(s), 0, j * BN, hkv, b);
+        mbar_expect_tx(k_full(s), KV_BYTES);
+        tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, k_full(s), 0, j * BN, hkv, b);
         if (!mbar_wait(v_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
-        mbar_expect_tx(v_full(s), TILE_BYTES);
-        tma_load_4d(v_smem + s * TILE_BYTES, &tmap_v, v_full(s), 0, j * BN, hkv, b);
+        mbar_expect_tx(v_full(s), KV_BYTES);
+        tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, v_full(s), 0, j * BN, hkv, b);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // The whole warp walks the loop (so addresses and descriptors stay warp-uniform); lane 0 issues.
-    if (n_tiles > 0) {
+    if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_qk = make_idesc(0, 0, 0, 0, BM, BN);
-      const bool leader = lane == 0;
-      const uint32_t s_tmem = tmem_base + S_COL;
       const uint32_t o_tmem = tmem_base + O_COL;
-      bool ok = mbar_wait_warp(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
       const uint64_t q_desc = smem_desc_sw128(q_smem, 16, 1024);
-      const uint64_t sfa_desc = smem_desc_plain(sfa_smem, 16, 128);
       const uint64_t sfb_desc = smem_desc_plain(sfb_smem, 16, 128);
-      const uint64_t sfa_lo_desc = smem_desc_plain(sfa_lo_smem, 16, 128);
+      bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
+      // S(j) = Q.K(j)^T into buffer j & 1.  The tensor pipe runs in issue order, so this also waits for the
+      // P.V product that last read that buffer.
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j % KV_STAGES;
+        if (!mbar_wait(k_full(s), (j / KV_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) return false;
+        tc_fence_after();
+        const uint64_t k_desc = smem_desc_sw128(k_smem + s * KV_BYTES, 16, 1024);
+        const uint32_t s_tmem = tmem_base + (j & 1) * S_COLS;
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) {
+          // 32 e4m3 = 32 bytes along the head dimension inside the 128-byte swizzle span
+          mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k != 0);
+        }
+        tc_commit(k_empty(s));
+        tc_commit(s_full(j & 1));
+        return true;
+      };
+      ok = ok && issue_qk(0);
+      if (ok && n_tiles > 1) ok = issue_qk(1);
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int s = j % KV_STAGES;
-        const uint32_t ph = (j / KV_STAGES) & 1;
-        if (!mbar_wait_warp(k_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        const int sb = j & 1;
+        const uint32_t s_tmem = tmem_base + sb * S_COLS;
+        if (!mbar_wait(p_full(sb), (j >> 1) & 1, p.status, WK_ERR_TIMEOUT_P)) break;
+        if (!mbar_wait(v_full(s), (j / KV_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
         tc_fence_after();
-        if (leader) TRACE(0, j);
-        if (leader) {
-          const uint64_t k_desc = smem_desc_sw128(k_smem + s * TILE_BYTES, 16, 1024);
+        // V tile: 64 keys (the MMA's K) x 128 bytes of head dim (the MMA's N): MN-major,
+        // one 128-byte span wide, 8-key groups 1024 bytes apart, 32 keys per MMA = 4096 bytes
+        const uint64_t v_desc = smem_desc_sw128(v_smem + s * KV_BYTES, 16, 1024);
+        tmem_cp_32x128b_warpx4(s_tmem + SFA_COL, smem_desc_plain(sfa_smem(sb), 16, 128));
+        tmem_cp_32x128b_warpx4(s_tmem + SFB_COL, sfb_desc);
 #pragma unroll
-          for (int k = 0; k < D / 32; ++k) {
-            // 32 e4m3 = 32 bytes along the head dimension inside the 128-byte swizzle span
-            mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k != 0);
-          }
-          tc_commit(k_empty(s));
-          tc_commit(s_full);
-          TRACE(1, j);
+        for (int k = 0; k < BN / 32; ++k) {
+          // P: 32 e4m3 per K step = 8 TMEM columns at column 32 k; scale byte k of the row's scale word
+          mma_mxf8_ts(o_tmem, s_tmem + 32 * k, v_desc + 256 * k, make_idesc_mx_major(BM, D, k, 0, 0, 1),
+                      s_tmem + SFA_COL, s_tmem + SFB_COL, (j | k) != 0);
         }
-        __syncwarp();
-        if (!mbar_wait_warp(p_full, j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
-        if (leader) TRACE(2, j);
-        if (!mbar_wait_warp(v_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) break;
-        tc_fence_after();
-        if (leader) {
-          // V tile: 128 keys (the MMA's K) x 128 bytes of head dim (the MMA's N): MN-major,
-          // one 128-byte span wide, 8-key groups 1024 bytes apart, 32 keys per MMA = 4096 bytes
-          const uint64_t v_desc = smem_desc_sw128(v_smem + s * TILE_BYTES, 16, 1024);
-          tmem_cp_32x128b_warpx4(s_tmem + SFA_COL, sfa_desc);
-          tmem_cp_32x128b_warpx4(s_tmem + SFB_COL, sfb_desc);
+        if (RESID) {
+          tmem_cp_32x128b_warpx4(s_tmem + SFA_LO_COL, smem_desc_plain(sfa_lo_smem(sb), 16, 128));
 #pragma unroll
           for (int k = 0; k < BN / 32; ++k) {
-            // P: 32 e4m3 per K step = 8 TMEM columns at column 32 k; scale byte k of the row's scale word
-            mma_mxf8_ts(o_tmem, s_tmem + 32 * k, v_desc + 256 * k, make_idesc_mx_major(BM, D, k, 0, 0, 1),
-                        s_tmem + SFA_COL, s_tmem + SFB_COL, (j | k) != 0);
+            mma_mxf8_ts(o_tmem, s_tmem + 32 * k + PLO_OFF, v_desc + 256 * k,
+                        make_idesc_mx_major(BM, D, k, 0, 0, 1), s_tmem + SFA_LO_COL, s_tmem + SFB_COL, 1);
           }
-          if (RESID) {
-            tmem_cp_32x128b_warpx4(s_tmem + SFA_LO_COL, sfa_lo_desc);
-#pragma unroll
-            for (int k = 0; k < BN / 32; ++k) {
-              mma_mxf8_ts(o_tmem, s_tmem + 32 * k + PLO_OFF, v_desc + 256 * k,
-                          make_idesc_mx_major(BM, D, k, 0, 0, 1), s_tmem + SFA_LO_COL, s_tmem + SFB_COL, 1);
-            }
-          }
-          tc_commit(v_empty(s));
-          TRACE(3, j);
-          if (j == n_tiles - 1) tc_commit(o_full);
         }
-        __syncwarp();
+        tc_commit(v_empty(s));
+        tc_commit(pv_done);
+        if (j == n_tiles - 1) tc_commit(o_full);
+        if (j + 2 < n_tiles) ok = issue_qk(j + 2);
       }
     }
+    __syncwarp();
   } else {
-    // two threads per row: `half` selects keys [64 half, 64 half + 64) of every tile
     const int quad = warp & 3;  // TMEM lanes [32 quad, 32 quad + 32) are the ones this warp may touch
-    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;  // row of the tile == TMEM lane
     const int row = m0 + r;
-    const int col0 = 64 * half;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t s_tmem = tmem_base + lane_addr + S_COL;
     const uint32_t o_tmem = tmem_base + lane_addr + O_COL;
-    const uint32_t x_mine = xch_smem + (half * BM + r) * 4;
-    const uint32_t x_other = xch_smem + ((half ^ 1) * BM + r) * 4;
+    const uint32_t sf_off = (r % 32) * 16 + (r / 32) * 4;
     const int sc = b * p.Hkv + hkv;
     const float beta = p.softmax_scale * p.q_descale[sc] * p.k_descale[sc] * 1.4426950408889634f;
     const float sv = p.v_descale[sc];
     const int row_limit = p.causal ? row + shift : nk - 1;  // last visible key of this row
     // m_ref: reference exponent of the row (O and the sums are in units of 2^-m_ref)
-    // l: exact sum of this thread's half (for lse and pmax); lq: sum of the rounded P (normaliser of O)
+    // l: exact row sum (for lse and pmax); lq: sum of the rounded P the MMA multiplies V with (normaliser of O)
     float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f, lq = 0.f;
     bool ok = true;
 
     for (int j = 0; j < n_tiles; ++j) {
-      if (!mbar_wait_warp(s_full, j & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+      const int sb = j & 1;
+      const uint32_t s_tmem = tmem_base + lane_addr + sb * S_COLS;
+      if (!mbar_wait_warp(s_full(sb), (j >> 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      if (warp == 2 && lane == 0) TRACE(8, j);
       const int key0 = j * BN;
       const bool tile_masked = (key0 + BN > nk) || (p.causal && key0 + BN - 1 > m0 + shift);
-      const int limit = min(row_limit, nk - 1) - key0 - col0;  // of this thread's 64 columns, those > limit are masked
+      const int limit = min(row_limit, nk - 1) - key0;  // columns > limit are masked
 
-      // pass 1: block maxima (the scores are read again in pass 2; holding all of them would spill)
-      float cm[2];
+      uint32_t sraw[2][32];
+      tmem_ld32(s_tmem, sraw[0]);
+      tmem_ld32(s_tmem + 32, sraw[1]);
+      tc_wait_ld();
+      if (tile_masked) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sraw[32];
-        tmem_ld32(s_tmem + col0 + c * 32, sraw);
-        tc_wait_ld();
-        if (tile_masked) {
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i > limit) sraw[i] = 0xff800000u;  // -inf
-        }
-        cm[c] = block_max(sraw) * beta;  // beta > 0 (checked on the host)
+            if (c * 32 + i > limit) sraw[c][i] = 0xff800000u;  // -inf
       }
-      const float own = fmaxf(cm[0], cm[1]);
-      asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine), "f"(own) : "memory");
-      if (warp == 2 && lane == 0) TRACE(10, j);
-      pair_sync(1 + quad);
-      if (warp == 2 && lane == 0) TRACE(11, j);
-      float other;
-      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(x_other) : "memory");
-      const float t = fmaxf(own, other);
+      float cm[2];
+      cm[0] = block_max(sraw[0]) * beta;  // beta > 0 (checked on the host)
+      cm[1] = block_max(sraw[1]) * beta;
+      const float t = fmaxf(cm[0], cm[1]);
       m_true = fmaxf(m_true, t);
       const bool need = t > -INFINITY && (m_ref == -INFINITY || t > m_ref + RESCALE_TAU);
       float corr = 1.f;
@@ -374,39 +349,36 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         m_ref = t;
       }
       if (j > 0 && __any_sync(0xffffffffu, need)) {
-        // the previous P.V has completed (s_full tracks every earlier MMA), so O is quiescent
+        // O may only be touched once the previous tile's P.V has completed
+        if (!mbar_wait_warp(pv_done, (j - 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 4; ++c) {
           uint32_t v[32];
-          tmem_ld32(o_tmem + col0 + c * 32, v);
+          tmem_ld32(o_tmem + c * 32, v);
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-          tmem_st32(o_tmem + col0 + c * 32, v);
+          tmem_st32(o_tmem + c * 32, v);
         }
         tc_wait_st();
       }
 
-      uint32_t sf_pair = 0, sf_pair_lo = 0;
+      uint32_t sf_word = 0, sf_word_lo = 0;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         const bool live = cm[c] > -INFINITY;
         const float kf = live ? ceilf(cm[c] - m_ref) : 0.f;  // block exponent relative to the row reference
         const float bias = live ? (static_cast<float>(P_OFFSET) - kf) - m_ref : 0.f;
-        uint32_t sraw[32];
-        tmem_ld32(s_tmem + col0 + c * 32, sraw);
-        tc_wait_ld();
-        if (tile_masked) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i > limit) sraw[i] = 0xff800000u;  // -inf
-        }
         uint32_t w[8], wl[8];
         float sum_exact, sum_rounded;
-        softmax_block<RESID>(sraw, beta, bias, w, wl, sum_exact, sum_rounded);
-        // the codes go to the first columns of the 32 score columns this thread has just consumed
-        tmem_st8(s_tmem + col0 + c * 32, w);
-        if (RESID) tmem_st8(s_tmem + col0 + c * 32 + PLO_OFF, wl);
+        softmax_block<RESID>(sraw[c], beta, bias, w, wl, sum_exact, sum_rounded);
+        // the codes go to the first columns of the 32 score columns they were made from
+        tmem_st8(s_tmem + c * 32, w);
+        if (RESID) tmem_st8(s_tmem + c * 32 + PLO_OFF, wl);
         int sf = live ? 127 + static_cast<int>(kf) - P_OFFSET : 0;
         sf = min(max(sf, 0), 254);
         const float blk_scale = __uint_as_float(static_cast<uint32_t>(sf) << 23);
@@ -414,45 +386,32 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           l = fmaf(sum_exact, blk_scale, l);
           lq = fmaf(sum_rounded, blk_scale, lq);
         }
-        sf_pair |= static_cast<uint32_t>(sf) << (8 * c);
-        sf_pair_lo |= static_cast<uint32_t>(max(sf - 4, 0)) << (8 * c);
+        sf_word |= static_cast<uint32_t>(sf) << (8 * c);
+        sf_word_lo |= static_cast<uint32_t>(max(sf - 4, 0)) << (8 * c);
       }
-      if (warp == 2 && lane == 0) TRACE(12, j);
-      const uint32_t sf_off = (r % 32) * 16 + (r / 32) * 4 + 2 * half;
-      asm volatile("st.shared.u16 [%0], %1;" ::"r"(sfa_smem + sf_off), "h"(static_cast<uint16_t>(sf_pair)) : "memory");
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfa_smem(sb) + sf_off), "r"(sf_word) : "memory");
       if (RESID) {
-        asm volatile("st.shared.u16 [%0], %1;" ::"r"(sfa_lo_smem + sf_off), "h"(static_cast<uint16_t>(sf_pair_lo))
-                     : "memory");
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfa_lo_smem(sb) + sf_off), "r"(sf_word_lo) : "memory");
       }
       fence_proxy_async_smem();
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(p_full);
-      if (warp == 2 && lane == 0) TRACE(13, j);
+      mbar_arrive(p_full(sb));
     }
 
     // epilogue
     if (n_tiles > 0 && ok) ok = mbar_wait_warp(o_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
-    // the two halves of a row add up their sums (every softmax thread takes part, also after a failed wait)
-    asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine + 2 * BM * 4), "f"(l) : "memory");
-    asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine + 4 * BM * 4), "f"(lq) : "memory");
-    pair_sync(1 + quad);
-    float l_other, lq_other;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_other) : "r"(x_other + 2 * BM * 4) : "memory");
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(lq_other) : "r"(x_other + 4 * BM * 4) : "memory");
-    l += l_other;
-    lq += lq_other;
     if (ok) {
       tc_fence_after();
       const bool empty = !(l > 0.f);
       const float inv = empty ? 0.f : sv / lq;
-      __nv_bfloat16* out_row = p.out + b * p.out_stride_b + hq * p.out_stride_h +
-                               static_cast<int64_t>(row) * p.out_stride_n + col0;
+      __nv_bfloat16* out_row =
+          p.out + b * p.out_stride_b + hq * p.out_stride_h + static_cast<int64_t>(row) * p.out_stride_n;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
         if (n_tiles > 0) {
-          tmem_ld32(o_tmem + col0 + c * 32, v);
+          tmem_ld32(o_tmem + c * 32, v);
           tc_wait_ld();
         } else {
 #pragma unroll
@@ -471,7 +430,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           }
         }
       }
-      if (p.write_lse && half == 0 && row < p.Nq) {
+      if (p.write_lse && row < p.Nq) {
         const int64_t off = b * p.lse_stride_b + hq * p.lse_stride_h + row;
         const float lse = empty ? INFINITY : m_ref + log2f(l);
         p.lse[off] = p.lse_natural ? lse * 0.6931471805599453f : lse;
@@ -513,6 +472,7 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
 
   CUtensorMap tq, tk, tv;
   const uint32_t box[4] = {D, BM, 1, 1};
+  const uint32_t box_kv[4] = {D, BN, 1, 1};
   {
     const uint64_t dims[4] = {D, static_cast<uint64_t>(a->Nq), static_cast<uint64_t>(a->Hq),
                               static_cast<uint64_t>(a->B)};
@@ -528,9 +488,9 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
                               static_cast<uint64_t>(ks[0])};
     const uint64_t strv[3] = {static_cast<uint64_t>(vs[2]), static_cast<uint64_t>(vs[1]),
                               static_cast<uint64_t>(vs[0])};
-    int r = encode_tmap(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, a->k, dims, strk, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    int r = encode_tmap(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, a->k, dims, strk, box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
     if (r) return r;
-    r = encode_tmap(&tv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, a->v, dims, strv, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    r = encode_tmap(&tv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, a->v, dims, strv, box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
     if (r) return r;
   }
   FwdParams p;
@@ -569,8 +529,3 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
 }
 
 
-#ifdef WK_FWD_TRACE
-extern "C" int wk_debug_read(long long* host, int n) {
-  return cudaMemcpyFromSymbol(host, wk::g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : -2;
-}
-#endif
