@@ -25,10 +25,10 @@
 // smallest integer with e_blk >= block maximum,
 //   P8 = e4m3(2^(s.beta - e_blk + 8)),   scale = 2^(k - 8),
 // and lets the block-scaled MMA apply the scale, so O accumulates in the units of one
-// reference m_ref per row.  m_ref is the row's running maximum at its last refresh: the
-// largest probability of the row is then stored exactly (2^8), as in the reference.  It
-// is refreshed (with a rescale of O and l) only when the running maximum has grown by
-// more than a factor of two.  Query blocks that see at most 512 keys carry P as two
+// reference m_ref per row.  m_ref is the row maximum of the first tile (its largest
+// probability is then stored exactly, 2^8, as in the reference); block exponents above it
+// are as good as below it, so it is refreshed (with a rescale of O and l) only when the
+// running maximum has outgrown it by 2^16, to stay clear of fp32 overflow.  Query blocks that see at most 512 keys carry P as two
 // e4m3 terms (value + 2^-4 . residual): with so few keys the rounding of P would not
 // average out.
 //
@@ -53,7 +53,7 @@ constexpr int TMEM_COLS = 256;
 constexpr int S_COLS = 64;    // one S buffer; buffer b starts at column 64 b
 constexpr int O_COL = 128;
 constexpr int P_OFFSET = 8;          // a block's largest P is stored in (2^7, 2^8]
-constexpr float RESCALE_TAU = 1.0f;  // refresh the row reference when the maximum outgrew it by more than this (log2)
+constexpr float RESCALE_TAU = 16.0f;  // refresh the row reference when the maximum outgrew it by more than this (log2)
 constexpr int SF_BYTES = 512;        // one scale-factor atom: 128 rows x 4 blocks of 32 keys
 // After the softmax the 64 columns of an S buffer are reused: block k of 32 keys keeps its P codes in columns
 // [32 k, 32 k + 8) and its residual codes in [32 k + 8, 32 k + 16); the scale factors are copied to 16..27.
@@ -273,8 +273,10 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // V tile: 64 keys (the MMA's K) x 128 bytes of head dim (the MMA's N): MN-major,
         // one 128-byte span wide, 8-key groups 1024 bytes apart, 32 keys per MMA = 4096 bytes
         const uint64_t v_desc = smem_desc_sw128(v_smem + s * KV_BYTES, 16, 1024);
+#ifdef WK_SF_VIA_SMEM
         tmem_cp_32x128b_warpx4(s_tmem + SFA_COL, smem_desc_plain(sfa_smem(sb), 16, 128));
         tmem_cp_32x128b_warpx4(s_tmem + SFB_COL, sfb_desc);
+#endif
 #pragma unroll
         for (int k = 0; k < BN / 32; ++k) {
           // P: 32 e4m3 per K step = 8 TMEM columns at column 32 k; scale byte k of the row's scale word
@@ -282,7 +284,9 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                       s_tmem + SFA_COL, s_tmem + SFB_COL, (j | k) != 0);
         }
         if (RESID) {
+#ifdef WK_SF_VIA_SMEM
           tmem_cp_32x128b_warpx4(s_tmem + SFA_LO_COL, smem_desc_plain(sfa_lo_smem(sb), 16, 128));
+#endif
 #pragma unroll
           for (int k = 0; k < BN / 32; ++k) {
             mma_mxf8_ts(o_tmem, s_tmem + 32 * k + PLO_OFF, v_desc + 256 * k,
@@ -389,11 +393,18 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         sf_word |= static_cast<uint32_t>(sf) << (8 * c);
         sf_word_lo |= static_cast<uint32_t>(max(sf - 4, 0)) << (8 * c);
       }
+#ifdef WK_SF_VIA_SMEM
       asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfa_smem(sb) + sf_off), "r"(sf_word) : "memory");
       if (RESID) {
         asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfa_lo_smem(sb) + sf_off), "r"(sf_word_lo) : "memory");
       }
       fence_proxy_async_smem();
+#else
+      // scale factors straight into TMEM: the MMA reads the scale of row r from lane r, column r / 32
+      tmem_st1(s_tmem + SFA_COL + quad, sf_word);
+      tmem_st4(s_tmem + SFB_COL, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+      if (RESID) tmem_st1(s_tmem + SFA_LO_COL + quad, sf_word_lo);
+#endif
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(p_full(sb));
