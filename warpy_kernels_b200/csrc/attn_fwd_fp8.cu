@@ -1,7 +1,7 @@
 // FP8 (e4m3) flash-attention forward for sm_100a, head dimension 128.
 //
 // One CTA = 128 queries of one (batch, query head), two CTAs per SM, key tiles of 64.
-// 192 threads:
+// 320 threads:
 //   warp 0      TMA producer: Q tile once, then K and V tiles (64 keys x 128 bytes,
 //               128-byte swizzle) into four-stage rings
 //   warp 1      allocates 256 TMEM columns (two S buffers of 64 columns, O: 128..255) and
@@ -9,10 +9,11 @@
 //               shared memory) always two tiles ahead, so the softmax never waits for it;
 //               O += P.V (kind::mxf8f6f4.block_scale, P read from TMEM, V MN-major from
 //               shared memory) as soon as a tile's P is there
-//   warps 2-5   softmax, one thread per query row: read S from TMEM, P as MXFP8 (e4m3
-//               codes written back over the S columns plus one power-of-two scale per row
-//               and 32 keys, staged through shared memory), row sums; finally
-//               O . v_descale / l -> bf16, lse (base 2) and pmax
+//   warps 2-9   softmax in two groups of four warps that take the key tiles in turn (group
+//               g owns S buffer g); inside a group one thread per query row: read S from
+//               TMEM, write P as MXFP8 back over the S columns (e4m3 codes plus one
+//               power-of-two scale per row and 32 keys, both straight into TMEM), row sums;
+//               finally O . v_descale / l -> bf16, lse (base 2) and pmax
 //
 // Numerics follow the reference's forward (warpy_kernels/attn/fwd_base.py:297-360,
 // 939-988; fwd_sm120.py:93-136): logits in base 2 with beta = softmax_scale .
@@ -26,9 +27,10 @@
 //   P8 = e4m3(2^(s.beta - e_blk + 8)),   scale = 2^(k - 8),
 // and lets the block-scaled MMA apply the scale, so O accumulates in the units of one
 // reference m_ref per row.  m_ref is the row maximum of the first tile (its largest
-// probability is then stored exactly, 2^8, as in the reference); block exponents above it
-// are as good as below it, so it is refreshed (with a rescale of O and l) only when the
-// running maximum has outgrown it by 2^16, to stay clear of fp32 overflow.  Query blocks that see at most 512 keys carry P as two
+// probability is then stored exactly, 2^8, as in the reference) and never moves: block
+// exponents above it are as good as below it.  Scores that outgrow it by more than 2^100
+// (69 nats) cannot be represented; the kernel then reports WK_ERR_RANGE through the
+// status word instead of returning a wrong result.  Query blocks that see at most 512 keys carry P as two
 // e4m3 terms (value + 2^-4 . residual): with so few keys the rounding of P would not
 // average out.
 //
@@ -47,22 +49,22 @@ constexpr int D = 128;        // head dimension (bytes per row in e4m3)
 constexpr int KV_STAGES = 4;
 constexpr int Q_BYTES = BM * D;     // 16 KiB
 constexpr int KV_BYTES = BN * D;    // 8 KiB
-constexpr int THREADS = 192;
-constexpr int SOFTMAX_THREADS = 128;
+constexpr int THREADS = 320;
+constexpr int GROUP_THREADS = 128;  // one softmax group
 constexpr int TMEM_COLS = 256;
 constexpr int S_COLS = 64;    // one S buffer; buffer b starts at column 64 b
 constexpr int O_COL = 128;
 constexpr int P_OFFSET = 8;          // a block's largest P is stored in (2^7, 2^8]
-constexpr float RESCALE_TAU = 16.0f;  // refresh the row reference when the maximum outgrew it by more than this (log2)
-constexpr int SF_BYTES = 512;        // one scale-factor atom: 128 rows x 4 blocks of 32 keys
+constexpr float MAX_BLOCK_EXP = 100.f;  // how far (log2) a block may rise above the row reference
 // After the softmax the 64 columns of an S buffer are reused: block k of 32 keys keeps its P codes in columns
-// [32 k, 32 k + 8) and its residual codes in [32 k + 8, 32 k + 16); the scale factors are copied to 16..27.
+// [32 k, 32 k + 8) and its residual codes in [32 k + 8, 32 k + 16); the scale factors sit in 16..27.
 constexpr int PLO_OFF = 8;
 constexpr int SFA_COL = 16;
 constexpr int SFB_COL = 20;
 constexpr int SFA_LO_COL = 24;
 constexpr int RESID_MAX_TILES = 8;   // query blocks that see at most this many key tiles carry the residual term
-constexpr int SMEM_BYTES = Q_BYTES + 2 * KV_STAGES * KV_BYTES + 5 * SF_BYTES + 1024 + 256;
+constexpr int XCH_BYTES = 7 * BM * 4;  // row reference plus (l, lq, m_true) of each group
+constexpr int SMEM_BYTES = Q_BYTES + 2 * KV_STAGES * KV_BYTES + XCH_BYTES + 1024 + 256;
 
 struct FwdParams {
   __nv_bfloat16* out;
@@ -149,11 +151,8 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t q_smem = smem_base;
   const uint32_t k_smem = q_smem + Q_BYTES;
   const uint32_t v_smem = k_smem + KV_STAGES * KV_BYTES;
-  const uint32_t sf_smem = v_smem + KV_STAGES * KV_BYTES;
-  auto sfa_smem = [&](int b) { return sf_smem + b * SF_BYTES; };            // P scales, one atom per S buffer
-  auto sfa_lo_smem = [&](int b) { return sf_smem + (2 + b) * SF_BYTES; };   // residual scales
-  const uint32_t sfb_smem = sf_smem + 4 * SF_BYTES;                         // unit scales for V
-  const uint32_t bar_base = sf_smem + 5 * SF_BYTES;
+  const uint32_t xch_smem = v_smem + KV_STAGES * KV_BYTES;  // exchange between the two softmax groups
+  const uint32_t bar_base = xch_smem + XCH_BYTES;
   const uint32_t q_full = bar_base;
   auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto k_empty = [&](int s) { return bar_base + 8u * (1 + KV_STAGES + s); };
@@ -162,9 +161,8 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t misc_bar = bar_base + 8u * (1 + 4 * KV_STAGES);
   auto s_full = [&](int b) { return misc_bar + 8u * b; };
   auto p_full = [&](int b) { return misc_bar + 8u * (2 + b); };
-  const uint32_t pv_done = misc_bar + 8u * 4;
-  const uint32_t o_full = misc_bar + 8u * 5;
-  const uint32_t tmem_slot = misc_bar + 8u * 6;
+  const uint32_t o_full = misc_bar + 8u * 4;
+  const uint32_t tmem_slot = misc_bar + 8u * 5;
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -198,9 +196,8 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(s_full(i), 1);
-      mbar_init(p_full(i), SOFTMAX_THREADS);
+      mbar_init(p_full(i), GROUP_THREADS);
     }
-    mbar_init(pv_done, 1);
     mbar_init(o_full, 1);
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
@@ -211,10 +208,6 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
-  if (threadIdx.x < SF_BYTES / 4) {
-    asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfb_smem + 4u * threadIdx.x), "r"(0x7f7f7f7fu) : "memory");
-  }
-  fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -242,7 +235,6 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       constexpr uint32_t idesc_qk = make_idesc(0, 0, 0, 0, BM, BN);
       const uint32_t o_tmem = tmem_base + O_COL;
       const uint64_t q_desc = smem_desc_sw128(q_smem, 16, 1024);
-      const uint64_t sfb_desc = smem_desc_plain(sfb_smem, 16, 128);
       bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
       // S(j) = Q.K(j)^T into buffer j & 1.  The tensor pipe runs in issue order, so this also waits for the
       // P.V product that last read that buffer.
@@ -273,10 +265,6 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // V tile: 64 keys (the MMA's K) x 128 bytes of head dim (the MMA's N): MN-major,
         // one 128-byte span wide, 8-key groups 1024 bytes apart, 32 keys per MMA = 4096 bytes
         const uint64_t v_desc = smem_desc_sw128(v_smem + s * KV_BYTES, 16, 1024);
-#ifdef WK_SF_VIA_SMEM
-        tmem_cp_32x128b_warpx4(s_tmem + SFA_COL, smem_desc_plain(sfa_smem(sb), 16, 128));
-        tmem_cp_32x128b_warpx4(s_tmem + SFB_COL, sfb_desc);
-#endif
 #pragma unroll
         for (int k = 0; k < BN / 32; ++k) {
           // P: 32 e4m3 per K step = 8 TMEM columns at column 32 k; scale byte k of the row's scale word
@@ -284,9 +272,6 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                       s_tmem + SFA_COL, s_tmem + SFB_COL, (j | k) != 0);
         }
         if (RESID) {
-#ifdef WK_SF_VIA_SMEM
-          tmem_cp_32x128b_warpx4(s_tmem + SFA_LO_COL, smem_desc_plain(sfa_lo_smem(sb), 16, 128));
-#endif
 #pragma unroll
           for (int k = 0; k < BN / 32; ++k) {
             mma_mxf8_ts(o_tmem, s_tmem + 32 * k + PLO_OFF, v_desc + 256 * k,
@@ -294,32 +279,35 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           }
         }
         tc_commit(v_empty(s));
-        tc_commit(pv_done);
         if (j == n_tiles - 1) tc_commit(o_full);
         if (j + 2 < n_tiles) ok = issue_qk(j + 2);
       }
     }
     __syncwarp();
   } else {
+    // Two groups of four warps take the key tiles in turn: group g handles tiles g, g + 2, ... out of S buffer g.
+    // Inside a group one thread owns one query row.
     const int quad = warp & 3;  // TMEM lanes [32 quad, 32 quad + 32) are the ones this warp may touch
+    const int grp = (warp - 2) >> 2;
     const int r = quad * 32 + lane;  // row of the tile == TMEM lane
     const int row = m0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_addr + grp * S_COLS;
     const uint32_t o_tmem = tmem_base + lane_addr + O_COL;
-    const uint32_t sf_off = (r % 32) * 16 + (r / 32) * 4;
+    const uint32_t x_ref = xch_smem + r * 4;
     const int sc = b * p.Hkv + hkv;
     const float beta = p.softmax_scale * p.q_descale[sc] * p.k_descale[sc] * 1.4426950408889634f;
     const float sv = p.v_descale[sc];
     const int row_limit = p.causal ? row + shift : nk - 1;  // last visible key of this row
-    // m_ref: reference exponent of the row (O and the sums are in units of 2^-m_ref)
-    // l: exact row sum (for lse and pmax); lq: sum of the rounded P the MMA multiplies V with (normaliser of O)
+    // m_ref: reference exponent of the row, fixed by the first tile (O and the sums are in units of 2^-m_ref)
+    // l: exact sum over this group's tiles (for lse and pmax); lq: sum of the rounded P (normaliser of O)
     float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f, lq = 0.f;
     bool ok = true;
+    bool met = false;  // the one-time meeting of the two groups has taken place
 
-    for (int j = 0; j < n_tiles; ++j) {
-      const int sb = j & 1;
-      const uint32_t s_tmem = tmem_base + lane_addr + sb * S_COLS;
-      if (!mbar_wait_warp(s_full(sb), (j >> 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+    for (int j = grp; j < n_tiles; j += 2) {
+      const int it = j >> 1;
+      if (!mbar_wait_warp(s_full(grp), it & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
         ok = false;
         break;
       }
@@ -328,58 +316,55 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const bool tile_masked = (key0 + BN > nk) || (p.causal && key0 + BN - 1 > m0 + shift);
       const int limit = min(row_limit, nk - 1) - key0;  // columns > limit are masked
 
-      uint32_t sraw[2][32];
-      tmem_ld32(s_tmem, sraw[0]);
-      tmem_ld32(s_tmem + 32, sraw[1]);
-      tc_wait_ld();
-      if (tile_masked) {
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i > limit) sraw[c][i] = 0xff800000u;  // -inf
-      }
-      float cm[2];
-      cm[0] = block_max(sraw[0]) * beta;  // beta > 0 (checked on the host)
-      cm[1] = block_max(sraw[1]) * beta;
-      const float t = fmaxf(cm[0], cm[1]);
-      m_true = fmaxf(m_true, t);
-      const bool need = t > -INFINITY && (m_ref == -INFINITY || t > m_ref + RESCALE_TAU);
-      float corr = 1.f;
-      if (need) {
-        corr = m_ref == -INFINITY ? 0.f : exp2f(m_ref - t);
-        l *= corr;
-        lq *= corr;
-        m_ref = t;
-      }
-      if (j > 0 && __any_sync(0xffffffffu, need)) {
-        // O may only be touched once the previous tile's P.V has completed
-        if (!mbar_wait_warp(pv_done, (j - 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
+      if (j == 0) {
+        // the row reference: maximum of the first tile (every row that sees any key sees one here)
+        float t = -INFINITY;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld32(o_tmem + c * 32, v);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t sraw[32];
+          tmem_ld32(s_tmem + c * 32, sraw);
           tc_wait_ld();
+          if (tile_masked) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-          tmem_st32(o_tmem + c * 32, v);
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i > limit) sraw[i] = 0xff800000u;
+          }
+          t = fmaxf(t, block_max(sraw) * beta);
         }
-        tc_wait_st();
+        m_ref = t;
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_ref), "f"(t) : "memory");
+      }
+      if (it == 0) {
+        // both groups meet once: the second one picks up the reference the first one has just published
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        met = true;
+        if (grp == 1) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(m_ref) : "r"(x_ref) : "memory");
       }
 
       uint32_t sf_word = 0, sf_word_lo = 0;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        const bool live = cm[c] > -INFINITY;
-        const float kf = live ? ceilf(cm[c] - m_ref) : 0.f;  // block exponent relative to the row reference
+        uint32_t sraw[32];
+        tmem_ld32(s_tmem + c * 32, sraw);
+        tc_wait_ld();
+        if (tile_masked) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i > limit) sraw[i] = 0xff800000u;  // -inf
+        }
+        const float cm = block_max(sraw) * beta;  // beta > 0 (checked on the host)
+        m_true = fmaxf(m_true, cm);
+        const bool live = cm > -INFINITY;
+        float kf = live ? ceilf(cm - m_ref) : 0.f;  // block exponent relative to the row reference
+        if (kf > MAX_BLOCK_EXP) {
+          // the scores have outgrown the first tile's maximum by more than 2^100: not representable here
+          atomicCAS(p.status, 0, WK_ERR_RANGE);
+          kf = MAX_BLOCK_EXP;
+        }
         const float bias = live ? (static_cast<float>(P_OFFSET) - kf) - m_ref : 0.f;
         uint32_t w[8], wl[8];
         float sum_exact, sum_rounded;
-        softmax_block<RESID>(sraw[c], beta, bias, w, wl, sum_exact, sum_rounded);
+        softmax_block<RESID>(sraw, beta, bias, w, wl, sum_exact, sum_rounded);
         // the codes go to the first columns of the 32 score columns they were made from
         tmem_st8(s_tmem + c * 32, w);
         if (RESID) tmem_st8(s_tmem + c * 32 + PLO_OFF, wl);
@@ -393,36 +378,49 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         sf_word |= static_cast<uint32_t>(sf) << (8 * c);
         sf_word_lo |= static_cast<uint32_t>(max(sf - 4, 0)) << (8 * c);
       }
-#ifdef WK_SF_VIA_SMEM
-      asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfa_smem(sb) + sf_off), "r"(sf_word) : "memory");
-      if (RESID) {
-        asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfa_lo_smem(sb) + sf_off), "r"(sf_word_lo) : "memory");
-      }
-      fence_proxy_async_smem();
-#else
       // scale factors straight into TMEM: the MMA reads the scale of row r from lane r, column r / 32
       tmem_st1(s_tmem + SFA_COL + quad, sf_word);
       tmem_st4(s_tmem + SFB_COL, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
       if (RESID) tmem_st1(s_tmem + SFA_LO_COL + quad, sf_word_lo);
-#endif
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(p_full(sb));
+      mbar_arrive(p_full(grp));
+    }
+    if (!met) {
+      // this group had no tile (or gave up on a wait): it still owes the other group the meeting above
+      asm volatile("bar.sync 1, 256;" ::: "memory");
     }
 
-    // epilogue
+    // epilogue: the groups add up their sums; group g stores head-dim columns [64 g, 64 g + 64)
     if (n_tiles > 0 && ok) ok = mbar_wait_warp(o_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
+    const uint32_t x_mine = xch_smem + (1 + 3 * grp) * BM * 4 + r * 4;
+    const uint32_t x_other = xch_smem + (1 + 3 * (grp ^ 1)) * BM * 4 + r * 4;
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine), "f"(l) : "memory");
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine + BM * 4), "f"(lq) : "memory");
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine + 2 * BM * 4), "f"(m_true) : "memory");
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    {
+      float l_o, lq_o, mt_o;
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_o) : "r"(x_other) : "memory");
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(lq_o) : "r"(x_other + BM * 4) : "memory");
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(mt_o) : "r"(x_other + 2 * BM * 4) : "memory");
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(m_ref) : "r"(x_ref) : "memory");
+      l += l_o;
+      lq += lq_o;
+      m_true = fmaxf(m_true, mt_o);
+    }
     if (ok) {
       tc_fence_after();
       const bool empty = !(l > 0.f);
       const float inv = empty ? 0.f : sv / lq;
-      __nv_bfloat16* out_row =
-          p.out + b * p.out_stride_b + hq * p.out_stride_h + static_cast<int64_t>(row) * p.out_stride_n;
+      const int col0 = 64 * grp;
+      __nv_bfloat16* out_row = p.out + b * p.out_stride_b + hq * p.out_stride_h +
+                               static_cast<int64_t>(row) * p.out_stride_n + col0;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
         if (n_tiles > 0) {
-          tmem_ld32(o_tmem + c * 32, v);
+          tmem_ld32(o_tmem + col0 + c * 32, v);
           tc_wait_ld();
         } else {
 #pragma unroll
@@ -441,7 +439,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           }
         }
       }
-      if (p.write_lse && row < p.Nq) {
+      if (p.write_lse && grp == 0 && row < p.Nq) {
         const int64_t off = b * p.lse_stride_b + hq * p.lse_stride_h + row;
         const float lse = empty ? INFINITY : m_ref + log2f(l);
         p.lse[off] = p.lse_natural ? lse * 0.6931471805599453f : lse;

@@ -22,6 +22,7 @@ enum : int {
   WK_ERR_TIMEOUT_MMA = 103,    // an epilogue / softmax thread waited too long for the tensor core
   WK_ERR_TIMEOUT_TMEM = 104,   // the MMA thread waited too long for a drained accumulator
   WK_ERR_TIMEOUT_P = 105,      // the MMA thread waited too long for softmax output
+  WK_ERR_RANGE = 110,          // attention scores outgrew the row reference by more than 2^100
 };
 
 // Upper bound for any single wait, in nanoseconds of %globaltimer.

@@ -143,6 +143,7 @@ const char* wk_error_string(int code) {
     case wk::WK_ERR_TIMEOUT_MMA: return "kernel gave up waiting for the tensor core";
     case wk::WK_ERR_TIMEOUT_TMEM: return "kernel gave up waiting for a drained accumulator";
     case wk::WK_ERR_TIMEOUT_P: return "kernel gave up waiting for softmax output";
+    case wk::WK_ERR_RANGE: return "attention scores span more than 2^100 within a row";
     default: return "unknown code";
   }
 }
