@@ -16,7 +16,7 @@
 //     memory, loop over the group's query heads and query tiles.  Per tile:
 //       S^T = K Q^T and dP^T = V dO8^T            (tcgen05.mma kind::f8f6f4, into TMEM)
 //       threads (one per key): P^T . g and dS^T as MXFP8 (e4m3 codes back into TMEM, one
-//                              power-of-two scale per key and 32 queries through smem)
+//                              power-of-two scale per key and 32 queries, also into TMEM)
 //       dV += (P g)^T dO8 and dK += dS^T Q8       (kind::mxf8f6f4, A from TMEM, B = the same
 //                                                  Q / dO8 tiles read MN-major)
 //     dV and dK stay in TMEM for the whole CTA (4 x 128 columns in use).
@@ -213,10 +213,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
-  if (threadIdx.x < SF_BYTES / 4) {
-    asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfu_smem + 4u * threadIdx.x), "r"(0x7f7f7f7fu) : "memory");
-  }
-  fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -266,9 +262,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         tc_commit(s_full);
         if (!mbar_wait(p_full, it & 1, p.status, WK_ERR_TIMEOUT_P)) break;
         tc_fence_after();
-        tmem_cp_32x128b_warpx4(st_tmem + A_SF_P, smem_desc_plain(sfp_smem, 16, 128));
-        tmem_cp_32x128b_warpx4(st_tmem + A_SF_UNIT, smem_desc_plain(sfu_smem, 16, 128));
-        tmem_cp_32x128b_warpx4(st_tmem + A_SF_DS, smem_desc_plain(sfd_smem, 16, 128));
         // B operands: the dO8 / Q8 tiles again, now read MN-major (K = queries, N = head dim)
 #pragma unroll
         for (int k = 0; k < BM / 32; ++k) {
@@ -338,10 +331,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         sf_p |= bp << (8 * c);
         sf_d |= bd << (8 * c);
       }
-      const uint32_t sf_off = (r % 32) * 16 + (r / 32) * 4;
-      asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfp_smem + sf_off), "r"(sf_p) : "memory");
-      asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfd_smem + sf_off), "r"(sf_d) : "memory");
-      fence_proxy_async_smem();
+      // scale factors straight into TMEM: the MMA reads the scale of row r from lane r, column r / 32
+      tmem_st1(st_tmem + A_SF_P + quad, sf_p);
+      tmem_st4(st_tmem + A_SF_UNIT, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+      tmem_st1(st_tmem + A_SF_DS + quad, sf_d);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(p_full);
@@ -454,10 +447,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
-  if (threadIdx.x < SF_BYTES / 4) {
-    asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfu_smem + 4u * threadIdx.x), "r"(0x7f7f7f7fu) : "memory");
-  }
-  fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -503,8 +492,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tc_commit(s_full);
         if (!mbar_wait(p_full, j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
         tc_fence_after();
-        tmem_cp_32x128b_warpx4(s_tmem + B_SF_DS, smem_desc_plain(sfd_smem, 16, 128));
-        tmem_cp_32x128b_warpx4(s_tmem + B_SF_UNIT, smem_desc_plain(sfu_smem, 16, 128));
         // dQ += dS K: A = dS codes in the dP columns, B = the K tile read MN-major
 #pragma unroll
         for (int k = 0; k < BN / 32; ++k) {
@@ -559,9 +546,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         quantize_block_to_tmem(ds, dp_tmem + c * 8, inv_d);
         sf_d |= bd << (8 * c);
       }
-      asm volatile("st.shared.b32 [%0], %1;" ::"r"(sfd_smem + (r % 32) * 16 + (r / 32) * 4), "r"(sf_d)
-                   : "memory");
-      fence_proxy_async_smem();
+      tmem_st1(s_tmem + B_SF_DS + quad, sf_d);
+      tmem_st4(s_tmem + B_SF_UNIT, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(p_full);

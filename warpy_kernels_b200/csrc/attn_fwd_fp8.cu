@@ -19,7 +19,8 @@
 // 939-988; fwd_sm120.py:93-136): logits in base 2 with beta = softmax_scale .
 // q_descale . k_descale . log2(e), bottom-right aligned causal mask, lse =
 // m_ref + log2(l), pmax = 2^(m_true - lse), empty rows give out = 0, lse = +inf,
-// pmax = 0, and O is normalised by the sum of the *rounded* P (fwd_sm120.py:95-118).
+// pmax = 0.  O is normalised by the exact row sum; the reference sums the rounded P instead
+// (fwd_sm120.py:95-118), which measured worse here once the row maximum is stored exactly.
 // Where the reference quantises P against each 128-key tile's own maximum
 // ("tile_local") and rescales O by the ratio of consecutive references, this kernel
 // quantises every block of 32 keys against its own exponent e_blk = m_ref + k, k the
@@ -81,31 +82,32 @@ struct FwdParams {
   int lse_natural;
   const int* seqused_k;  // [B] or null
   float softmax_scale;
+  int m_first;  // first query block of this launch (the grid covers gridDim.x blocks from here)
   int* status;
 };
 
-// One block of 32 keys of one row: P codes (and the residual codes), the exact and the rounded sum.
+// One block of 32 keys of one row: P codes (and the residual codes) and the sum of the exact values.
 template <bool RESID>
 __device__ __forceinline__ void softmax_block(const uint32_t (&sraw)[32], float beta, float bias, uint32_t (&w)[8],
-                                              uint32_t (&wl)[8], float& sum_exact, float& sum_rounded) {
-  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-  uint32_t hsum0 = 0, hsum1 = 0;  // f16x2 partial sums of the rounded codes (exact in f16)
+                                              uint32_t (&wl)[8], float& sum_exact) {
+  const uint64_t beta2 = pack_f32x2(beta, beta), bias2 = pack_f32x2(bias, bias);
+  uint64_t acc01 = 0, acc23 = 0;  // packed fp32 partial sums of the exact values
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const float p0 = ex2_approx(fmaf(__uint_as_float(sraw[4 * i + 0]), beta, bias));
-    const float p1 = ex2_approx(fmaf(__uint_as_float(sraw[4 * i + 1]), beta, bias));
-    const float p2 = ex2_approx(fmaf(__uint_as_float(sraw[4 * i + 2]), beta, bias));
-    const float p3 = ex2_approx(fmaf(__uint_as_float(sraw[4 * i + 3]), beta, bias));
-    acc0 += p0;
-    acc1 += p1;
-    acc2 += p2;
-    acc3 += p3;
+    float p0, p1, p2, p3;
+    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[4 * i + 0]), __uint_as_float(sraw[4 * i + 1])), beta2, bias2),
+                 p0, p1);
+    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[4 * i + 2]), __uint_as_float(sraw[4 * i + 3])), beta2, bias2),
+                 p2, p3);
+    p0 = ex2_approx(p0);
+    p1 = ex2_approx(p1);
+    p2 = ex2_approx(p2);
+    p3 = ex2_approx(p3);
+    acc01 = add_f32x2(acc01, pack_f32x2(p0, p1));
+    acc23 = add_f32x2(acc23, pack_f32x2(p2, p3));
     const uint16_t h01 = cvt_e4m3x2(p0, p1), h23 = cvt_e4m3x2(p2, p3);
     w[i] = static_cast<uint32_t>(h01) | (static_cast<uint32_t>(h23) << 16);
-    if (!RESID) {
-      hsum0 = hadd2(hsum0, e4m3x2_to_f16x2(h01));
-      hsum1 = hadd2(hsum1, e4m3x2_to_f16x2(h23));
-    } else {
+    if (RESID) {
       // second e4m3 term: what the first rounding lost, times 2^4
       float q0, q1, q2, q3;
       unpack_e4m3x2(h01, q0, q1);
@@ -113,14 +115,11 @@ __device__ __forceinline__ void softmax_block(const uint32_t (&sraw)[32], float 
       wl[i] = pack_e4m3x4((p0 - q0) * 16.f, (p1 - q1) * 16.f, (p2 - q2) * 16.f, (p3 - q3) * 16.f);
     }
   }
-  sum_exact = (acc0 + acc1) + (acc2 + acc3);
-  if (!RESID) {
-    float s0, s1, s2, s3;
-    f16x2_to_float2(hsum0, s0, s1);
-    f16x2_to_float2(hsum1, s2, s3);
-    sum_rounded = (s0 + s1) + (s2 + s3);
-  } else {
-    sum_rounded = sum_exact;
+  {
+    float a0, a1, a2, a3;
+    unpack_f32x2(acc01, a0, a1);
+    unpack_f32x2(acc23, a2, a3);
+    sum_exact = (a0 + a1) + (a2 + a3);
   }
 }
 
@@ -166,7 +165,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
-  const int m_blk = gridDim.x - 1 - blockIdx.x;  // longest (latest) causal blocks first
+  const int m_blk = p.m_first + gridDim.x - 1 - blockIdx.x;  // longest (latest) causal blocks first
   const int hq = blockIdx.y;
   const int b = blockIdx.z;
   const int hkv = hq / (p.Hq / p.Hkv);
@@ -300,8 +299,8 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const float sv = p.v_descale[sc];
     const int row_limit = p.causal ? row + shift : nk - 1;  // last visible key of this row
     // m_ref: reference exponent of the row, fixed by the first tile (O and the sums are in units of 2^-m_ref)
-    // l: exact sum over this group's tiles (for lse and pmax); lq: sum of the rounded P (normaliser of O)
-    float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f, lq = 0.f;
+    // l: sum of the exact probabilities over this group's tiles (normaliser of O, lse, pmax)
+    float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
     bool ok = true;
     bool met = false;  // the one-time meeting of the two groups has taken place
 
@@ -363,18 +362,15 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
         const float bias = live ? (static_cast<float>(P_OFFSET) - kf) - m_ref : 0.f;
         uint32_t w[8], wl[8];
-        float sum_exact, sum_rounded;
-        softmax_block<RESID>(sraw, beta, bias, w, wl, sum_exact, sum_rounded);
+        float sum_exact;
+        softmax_block<RESID>(sraw, beta, bias, w, wl, sum_exact);
         // the codes go to the first columns of the 32 score columns they were made from
         tmem_st8(s_tmem + c * 32, w);
         if (RESID) tmem_st8(s_tmem + c * 32 + PLO_OFF, wl);
         int sf = live ? 127 + static_cast<int>(kf) - P_OFFSET : 0;
         sf = min(max(sf, 0), 254);
         const float blk_scale = __uint_as_float(static_cast<uint32_t>(sf) << 23);
-        if (live) {
-          l = fmaf(sum_exact, blk_scale, l);
-          lq = fmaf(sum_rounded, blk_scale, lq);
-        }
+        if (live) l = fmaf(sum_exact, blk_scale, l);
         sf_word |= static_cast<uint32_t>(sf) << (8 * c);
         sf_word_lo |= static_cast<uint32_t>(max(sf - 4, 0)) << (8 * c);
       }
@@ -396,23 +392,20 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint32_t x_mine = xch_smem + (1 + 3 * grp) * BM * 4 + r * 4;
     const uint32_t x_other = xch_smem + (1 + 3 * (grp ^ 1)) * BM * 4 + r * 4;
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine), "f"(l) : "memory");
-    asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine + BM * 4), "f"(lq) : "memory");
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_mine + 2 * BM * 4), "f"(m_true) : "memory");
     asm volatile("bar.sync 1, 256;" ::: "memory");
     {
-      float l_o, lq_o, mt_o;
+      float l_o, mt_o;
       asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_o) : "r"(x_other) : "memory");
-      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(lq_o) : "r"(x_other + BM * 4) : "memory");
       asm volatile("ld.shared.f32 %0, [%1];" : "=f"(mt_o) : "r"(x_other + 2 * BM * 4) : "memory");
       asm volatile("ld.shared.f32 %0, [%1];" : "=f"(m_ref) : "r"(x_ref) : "memory");
       l += l_o;
-      lq += lq_o;
       m_true = fmaxf(m_true, mt_o);
     }
     if (ok) {
       tc_fence_after();
       const bool empty = !(l > 0.f);
-      const float inv = empty ? 0.f : sv / lq;
+      const float inv = empty ? 0.f : sv / l;
       const int col0 = 64 * grp;
       __nv_bfloat16* out_row = p.out + b * p.out_stride_b + hq * p.out_stride_h +
                                static_cast<int64_t>(row) * p.out_stride_n + col0;
@@ -528,12 +521,37 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
 
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<false>), SMEM_BYTES)) return WK_E_CUDA;
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<true>), SMEM_BYTES)) return WK_E_CUDA;
-  dim3 grid((a->Nq + BM - 1) / BM, a->Hq, a->B);
+  const int num_m = (a->Nq + BM - 1) / BM;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // long blocks first, then the few short ones that need the two-term P
-  attn_fwd_fp8_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
-  if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
-  attn_fwd_fp8_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
+  // Query blocks that see few key tiles run the two-term variant.  The tile count never decreases with the
+  // block index, so without per-batch key lengths the two variants get disjoint block ranges; with seqused_k
+  // both cover the whole grid and every CTA picks its variant itself.
+  int m_split = 0;
+  if (!a->seqused_k) {
+    const int shift = a->Nk - a->Nq;
+    const int all_tiles = (a->Nk + BN - 1) / BN;
+    for (int m = 0; m < num_m; ++m) {
+      int n = all_tiles;
+      if (a->causal) {
+        const int last_key = (m * BM + BM < a->Nq ? m * BM + BM : a->Nq) - 1 + shift;
+        n = last_key < 0 ? 0 : (last_key / BN + 1 < all_tiles ? last_key / BN + 1 : all_tiles);
+      }
+      if (n <= RESID_MAX_TILES) m_split = m + 1;
+    }
+  }
+  const int main_first = a->seqused_k ? 0 : m_split;
+  const int resid_count = a->seqused_k ? num_m : m_split;
+  if (num_m - main_first > 0) {
+    p.m_first = main_first;
+    dim3 grid(num_m - main_first, a->Hq, a->B);
+    attn_fwd_fp8_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
+    if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+  }
+  if (resid_count > 0) {
+    p.m_first = 0;
+    dim3 grid(resid_count, a->Hq, a->B);
+    attn_fwd_fp8_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
 }
 
