@@ -344,14 +344,25 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        steps = max(1, args.steps)
-        vals = []
-        for _ in range(min(steps, 3)):
-            vals.append(cpu_baseline(args.workload, budget_s=8.0))
+        # torchrun pins OMP_NUM_THREADS=1; the CPU arm may use every host core
+        torch.set_num_threads(os.cpu_count() or 1)
+        base = args.workload
+        if base.startswith(("attn_fwd", "attn_bwd")):
+            base = "attn_fwd"
+        elif base.startswith("gemm"):
+            base = "gemm_bf16"
+        for _ in range(max(0, min(args.warmup, 1))):
+            cpu_baseline(base, budget_s=2.0)
+        vals, times = [], []
+        for _ in range(max(1, min(args.steps, 3))):
+            t0 = time.perf_counter()
+            vals.append(cpu_baseline(base, budget_s=6.0))
+            times.append(time.perf_counter() - t0)
         best = max(vals, key=lambda c: c["value"])
         line = {
             "impl": "reference", "metric": f"{wl['desc']} throughput", "value": best["value"], "unit": best["unit"],
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None,
+            "n_gpus": args.gpus, "steps": len(vals), "warmup": min(args.warmup, 1),
+            "ms_per_step": 1e3 * sum(times) / len(times),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": wl["desc"], "note": "reference CPU path = its torch fp32 test oracle on host cores"},
@@ -481,6 +492,7 @@ def main():
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
+            torch.set_num_threads(os.cpu_count() or 1)
             base = "attn_fwd" if args.workload.startswith(("attn_fwd", "attn_bwd")) else args.workload
             line["cpu_baseline"] = cpu_baseline(base if base in ("attn_fwd", "attn_gqa", "quant") else "gemm_bf16")
             if args.workload.startswith("gemm_mx"):

@@ -164,10 +164,10 @@ def _attn_offset(q, k, v, offset, softmax_scale):
     Nq, Nk = q.shape[2], k.shape[2]
     scale = 1.0 / math.sqrt(d) if softmax_scale is None else softmax_scale
     s = (q @ k.transpose(-1, -2)) * scale
-    row = torch.arange(Nq)[:, None]
-    col = torch.arange(Nk)[None, :]
+    row = torch.arange(Nq, device=q.device)[:, None]
+    col = torch.arange(Nk, device=q.device)[None, :]
     s = s.masked_fill(col > row + offset, -1e30)
-    visible = (torch.arange(Nq) + offset) >= 0
+    visible = (torch.arange(Nq, device=q.device) + offset) >= 0
     out = (torch.softmax(s, dim=-1) @ v) * visible[:, None]
     lse = torch.where(visible, torch.logsumexp(s, dim=-1) / LN2, -math.inf)
     return out, lse

@@ -134,7 +134,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, in
 }
 
 // ---------------------------------------------------------------------------
-// TMA (cp.async.bulk.tensor), no multicast anywhere.
+// TMA (cp.async.bulk.tensor): every CTA loads its own tiles.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

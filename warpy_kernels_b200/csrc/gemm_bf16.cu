@@ -115,6 +115,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(1, 1, 0, 0, BM, BN);
+      // descriptors of stage 0; a later stage only moves the 16-byte-granular start address field
+      const uint64_t a_desc0 = smem_desc_sw128(smem_base, 16, 1024);
+      const uint64_t b_desc0 = smem_desc_sw128(smem_base + A_BYTES, 16, 1024);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -131,9 +134,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_base + stage * STAGE_BYTES;
-          const uint64_t a_desc = smem_desc_sw128(sa, 16, 1024);
-          const uint64_t b_desc = smem_desc_sw128(sa + A_BYTES, 16, 1024);
+          const uint64_t step = static_cast<uint64_t>(stage) * (STAGE_BYTES / 16);
+          const uint64_t a_desc = a_desc0 + step;
+          const uint64_t b_desc = b_desc0 + step;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // 16 bf16 = 32 bytes along K inside the 128-byte swizzle span

@@ -181,6 +181,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
+      // descriptors of stage 0; a later stage only moves the 16-byte-granular start address field
+      constexpr uint64_t kStageStep = STAGE_BYTES / 16;
+      static_assert(STAGE_BYTES % 16 == 0, "stage size must keep descriptors 16-byte granular");
+      const uint64_t a_desc0 = smem_desc_sw128(smem_base, 16, 1024);
+      const uint64_t b_desc0 = smem_desc_sw128(smem_base + A_BYTES, 16, 1024);
+      const uint64_t sfa_desc0 = smem_desc_plain(smem_base + A_BYTES + B_BYTES, 16, 128);
+      const uint64_t sfb_desc0 = smem_desc_plain(smem_base + A_BYTES + B_BYTES + SFA_BYTES, 16, 128);
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local) {
         const int acc = local & 1;
         // this slot was drained two tiles ago, and the previous tile has given up the columns it shares
@@ -194,17 +201,14 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_base + stage * STAGE_BYTES;
-          const uint32_t sb = sa + A_BYTES;
-          const uint32_t ssfa = sb + B_BYTES;
-          const uint32_t ssfb = ssfa + SFA_BYTES;
+          const uint64_t step = static_cast<uint64_t>(stage) * kStageStep;
           const uint32_t sf_tmem = tmem_base + SF_COL + stage * SF_SLOT_COLS;
           // 32 rows x 16 bytes per copy; the shared-memory source is a plain (unswizzled) block
-          tmem_cp_32x128b_warpx4(sf_tmem + 0, smem_desc_plain(ssfa, 16, 128));
-          tmem_cp_32x128b_warpx4(sf_tmem + 4, smem_desc_plain(ssfb, 16, 128));
-          tmem_cp_32x128b_warpx4(sf_tmem + 8, smem_desc_plain(ssfb + SF_ATOM, 16, 128));
-          const uint64_t a_desc = smem_desc_sw128(sa, 16, 1024);
-          const uint64_t b_desc = smem_desc_sw128(sb, 16, 1024);
+          tmem_cp_32x128b_warpx4(sf_tmem + 0, sfa_desc0 + step);
+          tmem_cp_32x128b_warpx4(sf_tmem + 4, sfb_desc0 + step);
+          tmem_cp_32x128b_warpx4(sf_tmem + 8, sfb_desc0 + step + SF_ATOM / 16);
+          const uint64_t a_desc = a_desc0 + step;
+          const uint64_t b_desc = b_desc0 + step;
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k) {
             mma_mxf8_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, make_idesc_mx(BM, BN, k, k), sf_tmem,
