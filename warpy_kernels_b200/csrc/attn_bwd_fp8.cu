@@ -40,7 +40,8 @@ constexpr int BN = 128;  // keys per tile
 constexpr int D = 128;
 constexpr int TILE_BYTES = 128 * 128;
 constexpr int SF_BYTES = 512;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;          // TMA warp, MMA warp, 8 element-wise warps (two threads per row)
+constexpr int ELEMWISE_THREADS = 256;
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -128,11 +129,29 @@ __device__ __forceinline__ uint32_t block_scale(uint32_t amax_bits, float& inv) 
 }
 
 __device__ __forceinline__ void quantize_block_to_tmem(const float (&x)[32], uint32_t taddr, float inv) {
+  const uint64_t inv2 = pack_f32x2(inv, inv);
   uint32_t w[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
-    w[i] = pack_e4m3x4(x[4 * i] * inv, x[4 * i + 1] * inv, x[4 * i + 2] * inv, x[4 * i + 3] * inv);
+  for (int i = 0; i < 8; ++i) {
+    float a, b, c, d;
+    unpack_f32x2(mul_f32x2(pack_f32x2(x[4 * i], x[4 * i + 1]), inv2), a, b);
+    unpack_f32x2(mul_f32x2(pack_f32x2(x[4 * i + 2], x[4 * i + 3]), inv2), c, d);
+    w[i] = pack_e4m3x4(a, b, c, d);
+  }
   tmem_st8(taddr, w);
+}
+
+// Largest magnitude of 32 values, as an fp32 bit pattern.
+__device__ __forceinline__ uint32_t absmax_bits(const float (&x)[32]) {
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; i += 8) {
+    a0 = fmaxf(fmaxf(a0, fabsf(x[i + 0])), fabsf(x[i + 1]));
+    a1 = fmaxf(fmaxf(a1, fabsf(x[i + 2])), fabsf(x[i + 3]));
+    a2 = fmaxf(fmaxf(a2, fabsf(x[i + 4])), fabsf(x[i + 5]));
+    a3 = fmaxf(fmaxf(a3, fabsf(x[i + 6])), fabsf(x[i + 7]));
+  }
+  return __float_as_uint(fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)));
 }
 
 struct BwdParams {
@@ -154,9 +173,13 @@ struct BwdParams {
 constexpr int A_STAGES = 2;
 constexpr int A_STAT_BYTES = BM * 16;
 constexpr int A_STAGE_BYTES = 2 * TILE_BYTES + A_STAT_BYTES;
-constexpr int A_SMEM_BYTES = 2 * TILE_BYTES + A_STAGES * A_STAGE_BYTES + 3 * SF_BYTES + 1024 + 256;
+// Requested size is padded past half an SM's shared memory: each CTA allocates all 512 TMEM columns, so a second
+// resident CTA could only spin in tcgen05.alloc.
+constexpr int A_SMEM_NEED = 2 * TILE_BYTES + A_STAGES * A_STAGE_BYTES + 3 * SF_BYTES + 1024 + 256;
+constexpr int A_SMEM_BYTES = A_SMEM_NEED > 120 * 1024 ? A_SMEM_NEED : 120 * 1024;
 constexpr int A_ST_COL = 0, A_DPT_COL = 128, A_DV_COL = 256, A_DK_COL = 384;
-constexpr int A_SF_P = 64, A_SF_UNIT = 68, A_SF_DS = 72;  // inside the consumed S^T columns
+// scale-factor columns inside the consumed S^T columns; the two threads of a row own 4 columns each
+constexpr int A_SF_P = 64, A_SF_UNIT = 72, A_SF_DS = 76;
 
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -201,7 +224,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       mbar_init(q_empty(s), 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, ELEMWISE_THREADS);
     mbar_init(acc_full, 1);
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
@@ -266,14 +289,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
         for (int k = 0; k < BM / 32; ++k) {
           mma_mxf8_ts(tmem_base + A_DV_COL, st_tmem + 8 * k, do_desc + 256 * k,
-                      make_idesc_mx_major(BN, D, k, 0, 0, 1), st_tmem + A_SF_P, st_tmem + A_SF_UNIT,
-                      (it | k) != 0);
+                      make_idesc_mx_major(BN, D, k & 1, 0, 0, 1), st_tmem + A_SF_P + 4 * (k >> 1),
+                      st_tmem + A_SF_UNIT, (it | k) != 0);
         }
 #pragma unroll
         for (int k = 0; k < BM / 32; ++k) {
           mma_mxf8_ts(tmem_base + A_DK_COL, dpt_tmem + 8 * k, q_desc + 256 * k,
-                      make_idesc_mx_major(BN, D, k, 0, 0, 1), st_tmem + A_SF_DS, st_tmem + A_SF_UNIT,
-                      (it | k) != 0);
+                      make_idesc_mx_major(BN, D, k & 1, 0, 0, 1), st_tmem + A_SF_DS + 4 * (k >> 1),
+                      st_tmem + A_SF_UNIT, (it | k) != 0);
         }
         tc_commit(q_empty(s));
         if (it == n_iter - 1) tc_commit(acc_full);
@@ -282,6 +305,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     __syncwarp();
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // which 64 of the tile's 128 columns this thread handles
     const int r = quad * 32 + lane;  // key row of the tile == TMEM lane
     const int key = n0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
@@ -304,37 +328,47 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                                                            2 * TILE_BYTES);
       // query column c is visible to this key iff key < Nk and (not causal or key <= m0 + c + shift)
       const int first_col = key >= p.Nk ? BM : (p.causal ? max(0, key - shift - m0) : 0);
+      // uniform over the CTA: does this (key block, query tile) pair contain any masked score?
+      const bool tile_masked = (n0 + BN > p.Nk) || (p.causal && n0 + BN - 1 > m0 + shift);
       uint32_t sf_p = 0, sf_d = 0;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * half + cc;
         uint32_t sraw[32], draw[32];
         tmem_ld32(st_tmem + c * 32, sraw);
         tmem_ld32(dpt_tmem + c * 32, draw);
         tc_wait_ld();
         float pt[32], ds[32];
-        uint32_t pmax_bits = 0, dmax_bits = 0;
+        if (tile_masked) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float4 st = stat[c * 32 + i];  // (L, g, g*sv, D): same address for every thread
-          float pr = ex2_approx(fmaf(__uint_as_float(sraw[i]), beta, -st.x));
-          if (c * 32 + i < first_col) pr = 0.f;
-          pt[i] = pr * st.y;
-          ds[i] = pr * fmaf(__uint_as_float(draw[i]), st.z, -st.w);
-          pmax_bits = max(pmax_bits, __float_as_uint(pt[i]) & 0x7fffffffu);
-          dmax_bits = max(dmax_bits, __float_as_uint(ds[i]) & 0x7fffffffu);
+          for (int i = 0; i < 32; ++i) {
+            const float4 st = stat[c * 32 + i];  // (L, g, g*sv, D): same address for every thread
+            float pr = ex2_approx(fmaf(__uint_as_float(sraw[i]), beta, -st.x));
+            if (c * 32 + i < first_col) pr = 0.f;
+            pt[i] = pr * st.y;
+            ds[i] = pr * fmaf(__uint_as_float(draw[i]), st.z, -st.w);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float4 st = stat[c * 32 + i];
+            const float pr = ex2_approx(fmaf(__uint_as_float(sraw[i]), beta, -st.x));
+            pt[i] = pr * st.y;
+            ds[i] = pr * fmaf(__uint_as_float(draw[i]), st.z, -st.w);
+          }
         }
         float inv_p, inv_d;
-        const uint32_t bp = block_scale(pmax_bits, inv_p);
-        const uint32_t bd = block_scale(dmax_bits, inv_d);
+        const uint32_t bp = block_scale(absmax_bits(pt), inv_p);
+        const uint32_t bd = block_scale(absmax_bits(ds), inv_d);
         quantize_block_to_tmem(pt, st_tmem + c * 8, inv_p);
         quantize_block_to_tmem(ds, dpt_tmem + c * 8, inv_d);
-        sf_p |= bp << (8 * c);
-        sf_d |= bd << (8 * c);
+        sf_p |= bp << (8 * cc);
+        sf_d |= bd << (8 * cc);
       }
       // scale factors straight into TMEM: the MMA reads the scale of row r from lane r, column r / 32
-      tmem_st1(st_tmem + A_SF_P + quad, sf_p);
+      tmem_st1(st_tmem + A_SF_P + 4 * half + quad, sf_p);
       tmem_st4(st_tmem + A_SF_UNIT, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-      tmem_st1(st_tmem + A_SF_DS + quad, sf_d);
+      tmem_st1(st_tmem + A_SF_DS + 4 * half + quad, sf_d);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(p_full);
@@ -346,12 +380,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       const float dk_scale = p.softmax_scale * sq;
       const int64_t row_off = ((static_cast<int64_t>(b) * p.Hkv + hkv) * p.Nk + key) * D;
 #pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
-        const uint32_t src = tmem_base + lane_addr + (half == 0 ? A_DV_COL : A_DK_COL);
-        __nv_bfloat16* dst_row = (half == 0 ? p.dv : p.dk) + row_off;
-        const float scale = half == 0 ? 1.f : dk_scale;
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t src = tmem_base + lane_addr + (which == 0 ? A_DV_COL : A_DK_COL);
+        __nv_bfloat16* dst_row = (which == 0 ? p.dv : p.dk) + row_off;
+        const float scale = which == 0 ? 1.f : dk_scale;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 2 * half; c < 2 * half + 2; ++c) {
           uint32_t v[32];
           if (n_iter > 0) {  // uniform: TMEM loads are warp-wide
             tmem_ld32(src + c * 32, v);
@@ -390,9 +424,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 // ---------------------------------------------------------------------------
 constexpr int B_STAGES = 2;
 constexpr int B_STAGE_BYTES = 2 * TILE_BYTES;  // K tile, V tile
-constexpr int B_SMEM_BYTES = 2 * TILE_BYTES + B_STAGES * B_STAGE_BYTES + 2 * SF_BYTES + 1024 + 256;
+constexpr int B_SMEM_NEED = 2 * TILE_BYTES + B_STAGES * B_STAGE_BYTES + 2 * SF_BYTES + 1024 + 256;
+constexpr int B_SMEM_BYTES = B_SMEM_NEED > 120 * 1024 ? B_SMEM_NEED : 120 * 1024;
 constexpr int B_S_COL = 0, B_DP_COL = 128, B_DQ_COL = 256;
-constexpr int B_SF_DS = 64, B_SF_UNIT = 68;
+constexpr int B_SF_DS = 64, B_SF_UNIT = 72;
 
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -435,7 +470,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       mbar_init(kv_empty(s), 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, ELEMWISE_THREADS);
     mbar_init(acc_full, 1);
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
@@ -496,8 +531,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 #pragma unroll
         for (int k = 0; k < BN / 32; ++k) {
           mma_mxf8_ts(tmem_base + B_DQ_COL, dp_tmem + 8 * k, k_desc + 256 * k,
-                      make_idesc_mx_major(BM, D, k, 0, 0, 1), s_tmem + B_SF_DS, s_tmem + B_SF_UNIT,
-                      (j | k) != 0);
+                      make_idesc_mx_major(BM, D, k & 1, 0, 0, 1), s_tmem + B_SF_DS + 4 * (k >> 1),
+                      s_tmem + B_SF_UNIT, (j | k) != 0);
         }
         tc_commit(kv_empty(s));
         if (j == n_tiles - 1) tc_commit(acc_full);
@@ -506,6 +541,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     __syncwarp();
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // which 64 of the tile's 128 columns this thread handles
     const int r = quad * 32 + lane;
     const int row = m0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
@@ -525,28 +561,37 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       }
       tc_fence_after();
       const int limit = row_limit - j * BN;  // columns > limit are masked
+      // uniform over the CTA: does this tile contain any masked score?
+      const bool tile_masked = (j * BN + BN > p.Nk) || (p.causal && j * BN + BN - 1 > m0 + shift);
       uint32_t sf_d = 0;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * half + cc;
         uint32_t sraw[32], draw[32];
         tmem_ld32(s_tmem + c * 32, sraw);
         tmem_ld32(dp_tmem + c * 32, draw);
         tc_wait_ld();
         float ds[32];
-        uint32_t dmax_bits = 0;
+        if (tile_masked) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float pr = ex2_approx(fmaf(__uint_as_float(sraw[i]), beta, -st.x));
-          if (c * 32 + i > limit) pr = 0.f;
-          ds[i] = pr * fmaf(__uint_as_float(draw[i]), st.z, -st.w);
-          dmax_bits = max(dmax_bits, __float_as_uint(ds[i]) & 0x7fffffffu);
+          for (int i = 0; i < 32; ++i) {
+            float pr = ex2_approx(fmaf(__uint_as_float(sraw[i]), beta, -st.x));
+            if (c * 32 + i > limit) pr = 0.f;
+            ds[i] = pr * fmaf(__uint_as_float(draw[i]), st.z, -st.w);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float pr = ex2_approx(fmaf(__uint_as_float(sraw[i]), beta, -st.x));
+            ds[i] = pr * fmaf(__uint_as_float(draw[i]), st.z, -st.w);
+          }
         }
         float inv_d;
-        const uint32_t bd = block_scale(dmax_bits, inv_d);
+        const uint32_t bd = block_scale(absmax_bits(ds), inv_d);
         quantize_block_to_tmem(ds, dp_tmem + c * 8, inv_d);
-        sf_d |= bd << (8 * c);
+        sf_d |= bd << (8 * cc);
       }
-      tmem_st1(s_tmem + B_SF_DS + quad, sf_d);
+      tmem_st1(s_tmem + B_SF_DS + 4 * half + quad, sf_d);
       tmem_st4(s_tmem + B_SF_UNIT, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
       tc_wait_st();
       tc_fence_before();
@@ -559,7 +604,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const float scale = p.softmax_scale * sk;
       __nv_bfloat16* dst_row = p.dq + ((static_cast<int64_t>(b) * p.Hq + hq) * p.Nq + row) * D;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t v[32];
         if (n_tiles > 0) {
           tmem_ld32(tmem_base + lane_addr + B_DQ_COL + c * 32, v);
