@@ -70,6 +70,30 @@ int wk_quantize_mx(const void* x, int dtype, int64_t rows, int64_t cols, int64_t
  * K % 64 == 0. */
 int wk_gemm_bf16(const void* a, const void* b, void* out, int m, int n, int k, void* stream);
 
+/* 16-bit GEMM with the reference's fused epilogue (warpy_kernels/gemm/base.py:436-497):
+ *   out = act((a @ b^T) . scale_a . scale_b [+ out])
+ * a, b, out (and the pre buffers) are bf16, or fp16 when f16 != 0.  Other fields as in
+ * wk_gemm_mx_args.  wk_gemm_bf16 is this call with every option off. */
+typedef struct {
+  const void* a;
+  const void* b;
+  void* out;
+  int32_t m, n, k;
+  int32_t f16;
+  const float* scale_a;
+  const float* scale_b;
+  int32_t scale_a_rows;
+  int32_t scale_b_cols;
+  int32_t accum;
+  int32_t act;
+  void* pre_out;
+  const void* pre_in;
+  void* q_mx; /* optional [M, N] e4m3 copy of out, with s_mx [M, N/32]; N % 32 == 0 */
+  void* s_mx;
+} wk_gemm16_args;
+
+int wk_gemm_16bit(const wk_gemm16_args* args, void* stream);
+
 /* MXFP8 block-scaled GEMM,
  *   out[M,N] = scale_a . scale_b . (a . 2^(a_scale_mx-127)) @ (b . 2^(b_scale_mx-127))^T,
  * e4m3 operands, fp32 accumulation, bf16 output.  Replaces the launch of GemmSm120 for
@@ -78,8 +102,9 @@ int wk_gemm_bf16(const void* a, const void* b, void* out, int m, int n, int k, v
  *   a [M,K], b [N,K]           e4m3 bytes, contiguous, 16-byte aligned
  *   a_scale_mx [M,K/32]        ue8m0 bytes, contiguous, 4-byte aligned, or NULL for unit scales
  *   b_scale_mx [N,K/32]        same for b (the reference scales only a; NULL reproduces it)
- *   scale_a, scale_b           optional device pointers to one fp32 each (NULL = 1)
- *   out [M,N] bf16             contiguous, 16-byte aligned
+ *   scale_a, scale_b           optional device pointers to fp32 scales (NULL = 1): one entry, or one per
+ *                              output row / column when scale_a_rows / scale_b_cols is set
+ *   out [M,N] bf16 (fp16 when out_f16)   contiguous, 16-byte aligned
  *   q_mx [M,N] e4m3, s_mx [M,N/32] ue8m0   optional (both or neither): the fp32 results
  *                              quantised per row and 32 columns before the bf16 rounding
  *   workspace                  scratch of at least wk_gemm_mxfp8_workspace_bytes(M,N,K) bytes,
@@ -98,6 +123,14 @@ typedef struct {
   void* workspace;
   int64_t workspace_bytes;
   int32_t m, n, k;
+  /* fused epilogue, warpy_kernels/gemm/base.py:436-497; all zero = plain product */
+  int32_t scale_a_rows; /* 1: scale_a holds M entries (one per output row) instead of one */
+  int32_t scale_b_cols; /* 1: scale_b holds N entries (one per output column), 16-byte aligned */
+  int32_t accum;        /* 1: add the scaled product to the values out already holds */
+  int32_t act;          /* 0 none, 1 exact-erf GELU, 2 multiply by GELU'(pre_in) */
+  int32_t out_f16;      /* 0: out / pre buffers are bf16, 1: fp16 */
+  void* pre_out;        /* optional [M,N]: the value before the activation (act = 1) */
+  const void* pre_in;   /* [M,N] pre-activation values, required for act = 2 */
 } wk_gemm_mx_args;
 
 int64_t wk_gemm_mxfp8_workspace_bytes(int m, int n, int k);

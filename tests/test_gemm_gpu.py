@@ -184,5 +184,147 @@ def test_fp8_rejects_bad_arguments(cuda):
         gemm(a, b, a_scale_mx=torch.zeros(128, 8, device=cuda))  # wrong dtype
     with pytest.raises(ValueError):
         gemm(a[:, :64].contiguous(), b[:, :64].contiguous())  # K not a multiple of 128
-    with pytest.raises(NotImplementedError):
-        gemm(a, b, act="gelu")
+    with pytest.raises(ValueError):
+        gemm(a, b, act="relu")
+    with pytest.raises(ValueError):
+        gemm(a, b, act="dgelu")  # no pre
+    with pytest.raises(ValueError):
+        gemm(a, b, store_pre=True)  # store_pre without gelu
+    with pytest.raises(ValueError):
+        gemm(a, b, accum=True)  # no addend
+    with pytest.raises(ValueError):
+        gemm(a, b, scale_a=torch.ones(7, device=cuda))  # neither 1 nor M entries
+    with pytest.raises(ValueError):
+        gemm(a, b, b_trans=True)  # transposed operands are for 16-bit inputs
+
+
+# ---- fused epilogue: scales, accum, GELU and its derivative, fp16 ----------------------------------------------
+EPI_SHAPES = [(256, 512, 1024), (4096, 4096, 2048)]
+
+
+def _dgelu(x):
+    return 0.5 * (1 + torch.erf(x * 0.7071067811865476)) + x * torch.exp(-0.5 * x * x) * 0.3989422804014327
+
+
+def _operands(cuda, kind, m, n, k, g):
+    a = torch.randn(m, k, device=cuda, generator=g)
+    b = torch.randn(n, k, device=cuda, generator=g)
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp8": FP8}[kind]
+    odt = torch.float16 if kind == "fp16" else torch.bfloat16
+    return a.to(dt), b.to(dt), odt
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "fp8"])
+@pytest.mark.parametrize("shape", EPI_SHAPES)
+def test_epilogue_accum_gelu_dgelu(cuda, kind, shape):
+    """The reference's ``epilogue`` case (``tests/gemm/test_gemm.py:65-97``), for every input dtype."""
+    from warpy_kernels import gemm
+
+    m, n, k = shape
+    g = torch.Generator(device=cuda).manual_seed(0)
+    a, b, odt = _operands(cuda, kind, m, n, k, g)
+    c0 = torch.randn(m, n, device=cuda, generator=g).to(odt)
+    prod = a.float() @ b.float().T
+    x = prod + c0.float()
+    tol = 1e-2  # the reference's tolerance; bf16 rounding is about 4e-3
+    assert R.rel_l2(gemm(a, b).float(), prod) <= tol
+    got = gemm(a, b, out=c0.clone(), accum=True)
+    assert got.dtype == odt and R.rel_l2(got.float(), x) <= tol
+    post, pre = gemm(a, b, out=c0.clone(), accum=True, act="gelu", store_pre=True)
+    assert R.rel_l2(post.float(), torch.nn.functional.gelu(x)) <= tol
+    assert R.rel_l2(pre.float(), x) <= tol
+    assert torch.equal(pre, got)  # pre is the accum result before the activation, rounded the same way
+    d = gemm(a, b, out=c0.clone(), act="dgelu", pre=pre, accum=True)
+    assert R.rel_l2(d.float(), x * _dgelu(pre.float())) <= tol
+    post_only, none = gemm(a, b, act="gelu")
+    assert none is None and R.rel_l2(post_only.float(), torch.nn.functional.gelu(prod)) <= tol
+    assert torch.equal(gemm(a, b, act="gelu")[0], post_only), "repeated launches differ"
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "fp8"])
+@pytest.mark.parametrize("shape", EPI_SHAPES)
+def test_vector_scales(cuda, kind, shape):
+    """The reference's ``vector_scales`` case (``tests/gemm/test_gemm.py:99-138``)."""
+    from warpy_kernels import gemm
+
+    m, n, k = shape
+    g = torch.Generator(device=cuda).manual_seed(0)
+    a, b, odt = _operands(cuda, kind, m, n, k, g)
+    rows = torch.rand(m, device=cuda, generator=g) * 4 + 0.05
+    cols = torch.rand(n, device=cuda, generator=g) * 4 + 0.05
+    if kind == "fp16":  # keep |x| well inside the fp16 range
+        rows, cols = rows * 0.25, cols * 0.25
+    c0 = torch.randn(m, n, device=cuda, generator=g).to(odt)
+    prod = (a.float() @ b.float().T) * rows[:, None] * cols
+    x = prod + c0.float()
+    tol = 1e-2
+    assert R.rel_l2(gemm(a, b, scale_a=rows, scale_b=cols).float(), prod) <= tol
+    half = torch.full((1,), 0.5, device=cuda)
+    got = gemm(a, b, scale_a=rows, scale_b=half).float()
+    # a one-element scale on the other side applies to fp8 inputs only (warpy_kernels/gemm/api.py:93-95)
+    assert R.rel_l2(got, prod / cols * (0.5 if kind == "fp8" else 1.0)) <= tol
+    got = gemm(a, b, scale_b=cols).float()
+    assert R.rel_l2(got, prod / rows[:, None]) <= tol
+    got = gemm(a, b, out=c0.clone(), accum=True, scale_a=rows, scale_b=cols).float()
+    assert R.rel_l2(got, x) <= tol
+    post, pre = gemm(a, b, out=c0.clone(), accum=True, scale_a=rows, scale_b=cols, act="gelu", store_pre=True)
+    assert R.rel_l2(post.float(), torch.nn.functional.gelu(x)) <= tol
+    assert R.rel_l2(pre.float(), x) <= tol
+
+
+def test_vector_scales_are_exact_per_row_and_column(cuda):
+    """Power-of-two scales on an integer product: a scale read from the wrong row or column changes an integer."""
+    from warpy_kernels import gemm
+
+    m, n, k = 256, 512, 128
+    g = torch.Generator(device=cuda).manual_seed(1)
+    ai = torch.randint(-2, 3, (m, k), device=cuda, generator=g).float()
+    bi = torch.randint(-2, 3, (n, k), device=cuda, generator=g).float()
+    rows = torch.exp2((torch.arange(m, device=cuda) % 5).float() - 2)
+    cols = torch.exp2((torch.arange(n, device=cuda) % 7).float() - 3)
+    want = ((ai @ bi.T) * rows[:, None] * cols).bfloat16()
+    for dt in (torch.bfloat16, FP8):
+        assert torch.equal(gemm(ai.to(dt), bi.to(dt), scale_a=rows, scale_b=cols), want)
+    # a column-scale vector that is 8- but not 16-byte aligned
+    buf = torch.zeros(n + 2, device=cuda)
+    buf[2:] = cols
+    assert torch.equal(gemm(ai.bfloat16(), bi.bfloat16(), scale_a=rows, scale_b=buf[2:]), want)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8"])
+@pytest.mark.parametrize("shape", EPI_SHAPES)
+def test_mx_output_after_gelu(cuda, kind, shape):
+    """MXFP8 output of the activated value, for 16-bit inputs too (``tests/gemm/test_gemm.py:151-190``)."""
+    from warpy_kernels import gemm
+
+    m, n, k = shape
+    g = torch.Generator(device=cuda).manual_seed(0)
+    a, b, odt = _operands(cuda, kind, m, n, k, g)
+    c0 = torch.randn(m, n, device=cuda, generator=g).to(odt)
+    out, q, sc = gemm(a, b, out_mx=True)
+    assert R.rel_l2(R.mx_dequant(q, sc), out.float()) <= 4e-2
+    peak = q.float().abs().view(m, n // 32, 32).amax(-1)
+    assert bool(((peak >= 224) & (peak <= 448)).all()), "block scales are not tight"
+    post, pre, q, sc = gemm(a, b, out=c0.clone(), accum=True, act="gelu", store_pre=True, out_mx=True)
+    assert R.rel_l2(R.mx_dequant(q, sc), post.float()) <= 4e-2
+    assert R.rel_l2(pre.float(), a.float() @ b.float().T + c0.float()) <= 1e-2
+
+
+def test_fp16_matches_fp32_product(cuda):
+    from warpy_kernels import gemm
+
+    g = torch.Generator(device=cuda).manual_seed(0)
+    a = torch.randn(384, 192, device=cuda, generator=g).half()
+    b = torch.randn(640, 192, device=cuda, generator=g).half()
+    out = gemm(a, b)
+    assert out.dtype == torch.float16
+    want = R.gemm_reference(a.cpu(), b.cpu())
+    assert R.rel_l2(out.cpu(), want.half()) <= 1e-3
+    with pytest.raises(ValueError):
+        gemm(a, b, out=torch.empty(384, 640, device=cuda, dtype=torch.bfloat16))
+    # fp8 inputs with an fp16 output
+    a8, b8 = a.to(FP8), b.to(FP8)
+    a8, b8 = a8[:, :128].contiguous(), b8[:, :128].contiguous()
+    o16 = gemm(a8, b8, out_dtype=torch.float16)
+    assert o16.dtype == torch.float16
+    assert R.rel_l2(o16.cpu(), R.gemm_reference(a8.cpu(), b8.cpu()).half()) <= 1e-3

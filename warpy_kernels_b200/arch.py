@@ -15,9 +15,9 @@ _SMEM_LIMIT = {100: 232448}
 
 _FEATURES = {
     "gemm": (100,),
-    "gemm_gelu": (),
-    "gemm_dgelu": (),
-    "gemm_accum": (),
+    "gemm_gelu": (100,),
+    "gemm_dgelu": (100,),
+    "gemm_accum": (100,),
     "gemm_fp8": (100,),
     "gemm_mx": (100,),
     "gemm_mx_out": (100,),

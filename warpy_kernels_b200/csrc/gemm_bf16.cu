@@ -14,6 +14,7 @@
 //
 // Tensor-core bound: 2*M*N*K flops per launch.
 #include "common.cuh"
+#include "gemm_epilogue.cuh"
 #include "host_common.h"
 
 namespace wk {
@@ -47,7 +48,8 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
 
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 __nv_bfloat16* __restrict__ out, int M, int N, int K, int group_m, int* status) {
+                 void* __restrict__ out, int M, int N, int K, int group_m, int in_f16,
+                 const __grid_constant__ Epilogue epi, int* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
@@ -114,7 +116,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(1, 1, 0, 0, BM, BN);
+      const uint32_t idesc = in_f16 ? make_idesc(0, 0, 0, 0, BM, BN) : make_idesc(1, 1, 0, 0, BM, BN);
       // descriptors of stage 0; a later stage only moves the 16-byte-granular start address field
       const uint64_t a_desc0 = smem_desc_sw128(smem_base, 16, 1024);
       const uint64_t b_desc0 = smem_desc_sw128(smem_base + A_BYTES, 16, 1024);
@@ -162,24 +164,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (!mbar_wait_warp(tfull_bar(acc), acc_phase, status, WK_ERR_TIMEOUT_MMA)) break;
       tc_fence_after();
       const int row = tc.m_blk * BM + quad * 32 + lane;
-      __nv_bfloat16* out_row = out + static_cast<int64_t>(row) * N + tc.n_blk * BN;
+      const float row_scale = epilogue_row_scale(epi, row);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
         tmem_ld32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, v);
         tc_wait_ld();
-        if (tc.n_blk * BN + c * 32 < N) {
-          uint4* dst = reinterpret_cast<uint4*>(out_row + c * 32);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
-            w.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
-            w.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
-            w.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
-            dst[i] = w;
-          }
-        }
+        const int col = tc.n_blk * BN + c * 32;
+        if (col < N) epilogue_chunk(epi, v, row_scale, row, col, N, out);
       }
       tc_fence_before();
       __syncwarp();
@@ -198,39 +190,66 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }  // namespace
 }  // namespace wk
 
-extern "C" int wk_gemm_bf16(const void* a, const void* b, void* out, int m, int n, int k,
-                            void* stream) {
+extern "C" int wk_gemm_16bit(const wk_gemm16_args* g, void* stream) {
   using namespace wk;
+  if (!g) return WK_E_ARG;
+  const int m = g->m, n = g->n, k = g->k;
   if (m < 0 || n < 0 || k < 0 || m % BM || n % 128 || k % BK) return WK_E_ARG;
   if (m == 0 || n == 0) return 0;
   if (k == 0) return WK_E_ARG;
-  if (!a || !b || !out || !aligned16(a) || !aligned16(b) || !aligned16(out)) return WK_E_ARG;
+  if (!g->a || !g->b || !g->out || !aligned16(g->a) || !aligned16(g->b) || !aligned16(g->out)) return WK_E_ARG;
+  if (g->act < 0 || g->act > 2 || (g->act == ACT_DGELU && !g->pre_in)) return WK_E_ARG;
+  if ((g->pre_out && !aligned16(g->pre_out)) || (g->pre_in && !aligned16(g->pre_in))) return WK_E_ARG;
+  if (g->scale_b && g->scale_b_cols && !aligned16(g->scale_b)) return WK_E_ARG;
+  if ((g->q_mx != nullptr) != (g->s_mx != nullptr) || (g->q_mx && !aligned16(g->q_mx))) return WK_E_ARG;
   int* status = status_word();
   if (!status) return WK_E_CUDA;
 
+  const CUtensorMapDataType dt = g->f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap ta, tb;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
     const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
     const uint32_t box[2] = {BK, BM};
-    int r = encode_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, dims, strides, box,
-                        CU_TENSOR_MAP_SWIZZLE_128B);
+    int r = encode_tmap(&ta, dt, 2, g->a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (r) return r;
   }
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
     const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
     const uint32_t box[2] = {BK, BN};
-    int r = encode_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b, dims, strides, box,
-                        CU_TENSOR_MAP_SWIZZLE_128B);
+    int r = encode_tmap(&tb, dt, 2, g->b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (r) return r;
   }
+  Epilogue e;
+  e.scale_a = g->scale_a;
+  e.scale_b = g->scale_b;
+  e.scale_a_rows = g->scale_a_rows;
+  e.scale_b_cols = g->scale_b_cols;
+  e.accum = g->accum;
+  e.act = g->act;
+  e.out_f16 = g->f16;
+  e.pre_out = g->pre_out;
+  e.pre_in = g->pre_in;
+  e.q_mx = static_cast<uint8_t*>(g->q_mx);
+  e.s_mx = static_cast<uint8_t*>(g->s_mx);
   if (allow_smem(reinterpret_cast<const void*>(gemm_bf16_kernel), SMEM_BYTES)) return WK_E_CUDA;
   const int num_tiles = (m / BM) * ((n + BN - 1) / BN);
   const int sms = sm_count();
   if (sms <= 0) return WK_E_CUDA;
   const int grid = num_tiles < sms ? num_tiles : sms;
-  gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
-      ta, tb, static_cast<__nv_bfloat16*>(out), m, n, k, 8, status);
+  gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ta, tb, g->out, m, n, k, 8,
+                                                                                     g->f16, e, status);
   return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
+}
+
+extern "C" int wk_gemm_bf16(const void* a, const void* b, void* out, int m, int n, int k, void* stream) {
+  wk_gemm16_args g = {};
+  g.a = a;
+  g.b = b;
+  g.out = out;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  return wk_gemm_16bit(&g, stream);
 }

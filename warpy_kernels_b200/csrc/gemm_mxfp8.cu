@@ -25,6 +25,7 @@
 //
 // Tensor-core bound: 2*M*N*K flops per launch.
 #include "common.cuh"
+#include "gemm_epilogue.cuh"
 #include "host_common.h"
 
 namespace wk {
@@ -83,13 +84,10 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
 }
 
 struct GemmParams {
-  __nv_bfloat16* out;
-  uint8_t* q_mx;        // optional [M,N] e4m3
-  uint8_t* s_mx;        // optional [M,N/32]
+  void* out;
   const uint8_t* sfa;   // swizzled atoms [M/128][K/128][512]
   const uint8_t* sfb;   // swizzled atoms [N/128][K/128][512]
-  const float* scale_a; // optional scalar
-  const float* scale_b; // optional scalar
+  Epilogue epi;         // scales, accumulate, activation, MXFP8 copy
   int M, N, K;
   int group_m;
   int* status;
@@ -226,9 +224,6 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     __syncwarp();
   } else {
     const int quad = warp & 3;
-    float alpha = 1.f;
-    if (p.scale_a) alpha *= *p.scale_a;
-    if (p.scale_b) alpha *= *p.scale_b;
     int local = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const TileCoord tc = tile_coord(tile, num_m, num_n, p.group_m);
@@ -238,7 +233,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       // column chunks in the order they are drained: the 64 columns shared with the other slot first
       const int first_chunk = acc == 0 ? 6 : 0;
       const int row = tc.m_blk * BM + quad * 32 + lane;
-      const int64_t row_off = static_cast<int64_t>(row) * p.N + tc.n_blk * BN;
+      const float row_scale = epilogue_row_scale(p.epi, row);
 #pragma unroll 1
       for (int ci = 0; ci < BN / 32; ++ci) {
         const int c = (ci + first_chunk) & 7;
@@ -251,46 +246,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           __syncwarp();
           if (lane == 0) mbar_arrive(ovl_bar);
         }
-        if (tc.n_blk * BN + c * 32 < p.N) {
-          float f[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]) * alpha;
-          uint4* dst = reinterpret_cast<uint4*>(p.out + row_off + c * 32);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 w;
-            w.x = pack_bf16x2(f[8 * i + 0], f[8 * i + 1]);
-            w.y = pack_bf16x2(f[8 * i + 2], f[8 * i + 3]);
-            w.z = pack_bf16x2(f[8 * i + 4], f[8 * i + 5]);
-            w.w = pack_bf16x2(f[8 * i + 6], f[8 * i + 7]);
-            dst[i] = w;
-          }
-          if (p.q_mx) {
-            // this thread's 32 consecutive columns are exactly one MX block
-            uint32_t amax = 0;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) amax = max(amax, __float_as_uint(f[i]) & 0x7fffffffu);
-            int e = static_cast<int>((amax + 0x1fffffu) >> 23) - 8;
-            e = min(max(e, 0), 254);
-            const float inv = __uint_as_float(static_cast<uint32_t>(max(254 - e, 1)) << 23);
-            uint4* qdst = reinterpret_cast<uint4*>(p.q_mx + row_off + c * 32);
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              uint4 w;
-              w.x = pack_e4m3x4(__fmul_rn(f[16 * i + 0], inv), __fmul_rn(f[16 * i + 1], inv),
-                                __fmul_rn(f[16 * i + 2], inv), __fmul_rn(f[16 * i + 3], inv));
-              w.y = pack_e4m3x4(__fmul_rn(f[16 * i + 4], inv), __fmul_rn(f[16 * i + 5], inv),
-                                __fmul_rn(f[16 * i + 6], inv), __fmul_rn(f[16 * i + 7], inv));
-              w.z = pack_e4m3x4(__fmul_rn(f[16 * i + 8], inv), __fmul_rn(f[16 * i + 9], inv),
-                                __fmul_rn(f[16 * i + 10], inv), __fmul_rn(f[16 * i + 11], inv));
-              w.w = pack_e4m3x4(__fmul_rn(f[16 * i + 12], inv), __fmul_rn(f[16 * i + 13], inv),
-                                __fmul_rn(f[16 * i + 14], inv), __fmul_rn(f[16 * i + 15], inv));
-              qdst[i] = w;
-            }
-            p.s_mx[static_cast<int64_t>(row) * (p.N / 32) + (tc.n_blk * BN + c * 32) / 32] =
-                static_cast<uint8_t>(e);
-          }
-        }
+        const int col = tc.n_blk * BN + c * 32;
+        if (col < p.N) epilogue_chunk(p.epi, v, row_scale, row, col, p.N, p.out);
       }
       tc_fence_before();
       __syncwarp();
@@ -304,6 +261,29 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+Epilogue epilogue_of(const wk_gemm_mx_args* a) {
+  Epilogue e;
+  e.scale_a = a->scale_a;
+  e.scale_b = a->scale_b;
+  e.scale_a_rows = a->scale_a_rows;
+  e.scale_b_cols = a->scale_b_cols;
+  e.accum = a->accum;
+  e.act = a->act;
+  e.out_f16 = a->out_f16;
+  e.pre_out = a->pre_out;
+  e.pre_in = a->pre_in;
+  e.q_mx = static_cast<uint8_t*>(a->q_mx);
+  e.s_mx = static_cast<uint8_t*>(a->s_mx);
+  return e;
+}
+
+bool epilogue_args_ok(const wk_gemm_mx_args* a) {
+  if (a->act < 0 || a->act > 2 || (a->act == ACT_DGELU && !a->pre_in)) return false;
+  if ((a->pre_out && !aligned16(a->pre_out)) || (a->pre_in && !aligned16(a->pre_in))) return false;
+  if (a->scale_b && a->scale_b_cols && !aligned16(a->scale_b)) return false;
+  return true;
 }
 
 int swizzle(const void* s, void* dst, int rows, int k, cudaStream_t st) {
@@ -337,6 +317,7 @@ extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
   if (a->b_scale_mx && (reinterpret_cast<uintptr_t>(a->b_scale_mx) & 3)) return WK_E_ARG;
   if ((a->q_mx == nullptr) != (a->s_mx == nullptr)) return WK_E_ARG;
   if (a->q_mx && !aligned16(a->q_mx)) return WK_E_ARG;
+  if (!epilogue_args_ok(a)) return WK_E_ARG;
   if (a->workspace_bytes < wk_gemm_mxfp8_workspace_bytes(m, n, k)) return WK_E_ARG;
   int* status = status_word();
   if (!status) return WK_E_CUDA;
@@ -365,13 +346,10 @@ extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
     if (r) return r;
   }
   GemmParams p;
-  p.out = static_cast<__nv_bfloat16*>(a->out);
-  p.q_mx = static_cast<uint8_t*>(a->q_mx);
-  p.s_mx = static_cast<uint8_t*>(a->s_mx);
+  p.out = a->out;
   p.sfa = sfa;
   p.sfb = sfb;
-  p.scale_a = a->scale_a;
-  p.scale_b = a->scale_b;
+  p.epi = epilogue_of(a);
   p.M = m;
   p.N = n;
   p.K = k;
@@ -440,6 +418,7 @@ extern "C" int wk_gemm_mxfp8_noalloc(const wk_gemm_mx_args* a, void* stream) {
   if (a->b_scale_mx && (reinterpret_cast<uintptr_t>(a->b_scale_mx) & 3)) return WK_E_ARG;
   if ((a->q_mx == nullptr) != (a->s_mx == nullptr)) return WK_E_ARG;
   if (a->q_mx && !aligned16(a->q_mx)) return WK_E_ARG;
+  if (!epilogue_args_ok(a)) return WK_E_ARG;
   // the fixed array bounds the problem size: (M + N) * K / 32 scale bytes must fit
   if (wk_gemm_mxfp8_workspace_bytes(m, n, k) > kNoAllocScratchBytes) return WK_E_TOO_LARGE;
   int dev = 0;
@@ -472,13 +451,10 @@ extern "C" int wk_gemm_mxfp8_noalloc(const wk_gemm_mx_args* a, void* stream) {
     if (r) return r;
   }
   GemmParams p;
-  p.out = static_cast<__nv_bfloat16*>(a->out);
-  p.q_mx = static_cast<uint8_t*>(a->q_mx);
-  p.s_mx = static_cast<uint8_t*>(a->s_mx);
+  p.out = a->out;
   p.sfa = sfa;
   p.sfb = sfb;
-  p.scale_a = a->scale_a;
-  p.scale_b = a->scale_b;
+  p.epi = epilogue_of(a);
   p.M = m;
   p.N = n;
   p.K = k;

@@ -19,6 +19,12 @@ _TYPES = {torch.bfloat16: "bf16", torch.float16: "f16"}
 BM = 128
 
 
+_EPILOGUE_FIELDS = [
+    ("scale_a_rows", ctypes.c_int32), ("scale_b_cols", ctypes.c_int32), ("accum", ctypes.c_int32),
+    ("act", ctypes.c_int32),
+]
+
+
 class _MxArgs(ctypes.Structure):
     _fields_ = [
         ("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("a_scale_mx", ctypes.c_void_p),
@@ -26,7 +32,23 @@ class _MxArgs(ctypes.Structure):
         ("out", ctypes.c_void_p), ("q_mx", ctypes.c_void_p), ("s_mx", ctypes.c_void_p),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64),
         ("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32),
+        *_EPILOGUE_FIELDS, ("out_f16", ctypes.c_int32),
+        ("pre_out", ctypes.c_void_p), ("pre_in", ctypes.c_void_p),
     ]
+
+
+class _Gemm16Args(ctypes.Structure):
+    _fields_ = [
+        ("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("out", ctypes.c_void_p),
+        ("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32), ("f16", ctypes.c_int32),
+        ("scale_a", ctypes.c_void_p), ("scale_b", ctypes.c_void_p),
+        *_EPILOGUE_FIELDS,
+        ("pre_out", ctypes.c_void_p), ("pre_in", ctypes.c_void_p),
+        ("q_mx", ctypes.c_void_p), ("s_mx", ctypes.c_void_p),
+    ]
+
+
+_ACT = {"": 0, "gelu": 1, "dgelu": 2}
 
 
 def _gemm_arch(a, fp8, act, accum, mx_in, mx_out):
@@ -81,7 +103,7 @@ def make_gemm(
     """Prepare ``out = a @ b.T * scale_a * scale_b``.
 
     Args:
-        a: ``[M, K]`` bf16 or ``torch.float8_e4m3fn``, contiguous.
+        a: ``[M, K]`` bf16, fp16 or ``torch.float8_e4m3fn``, contiguous.
         b: ``[N, K]`` with the dtype of ``a``, contiguous.
         out: Optional contiguous ``[M, N]`` bf16 output, 16-byte aligned. Allocated if ``None``.
         bk: K elements per pipeline stage in the reference; here only the divisibility rule ``K % bk == 0`` is
@@ -89,11 +111,17 @@ def make_gemm(
         stages, group_m, min_blocks, frag_pipe, tma, warp_spec, persistent, setmaxnreg: Accepted for
             compatibility and ignored: the sm_100a kernels are always TMA-fed, warp-specialised and persistent.
         bn: Output columns per CTA in the reference, 128 or 256; ``N`` must be a multiple of it.
-        scale_a: Float32 CUDA tensor with one element that scales ``a`` (fp8 inputs only).
-        scale_b: As ``scale_a``, for ``b``.
-        out_dtype: Output dtype when ``out`` is ``None`` and the inputs are fp8; must be bf16.
-        act, store_pre, pre, a_trans, b_trans, accum: The reference's epilogue fusions and transposed operands.
-            Not implemented by this build; anything but the defaults raises ``NotImplementedError``.
+        scale_a: Float32 CUDA tensor that scales ``a``: one element (used for fp8 inputs only), or ``M`` elements
+            to scale each output row (any input dtype), applied before ``accum`` and ``act``.
+        scale_b: As ``scale_a``, for ``b``, with ``N`` elements to scale each output column.
+        out_dtype: Output dtype when ``out`` is ``None`` and the inputs are fp8: bf16 or fp16.
+        act: ``"gelu"`` to apply the exact erf GELU to the scaled product before storing it in ``out``, or
+            ``"dgelu"`` to multiply the scaled product by the GELU derivative at ``pre``.
+        store_pre: Whether to also store the product before the activation. Needs ``act="gelu"``.
+        pre: The pre-activation values the forward stored, ``[M, N]`` with the dtype of ``out``. Needed for
+            ``act="dgelu"``.
+        a_trans, b_trans: Transposed operands; not implemented by this build (``NotImplementedError``).
+        accum: Whether to add the scaled product to the values ``out`` already holds, before the activation.
         a_scale_mx: ``[M, K / 32]`` uint8 ue8m0 scales of ``a``, one per row and block of 32 along K, as
             ``out_mx`` writes them. Needs fp8 inputs.
         out_mx: Whether to also write the result as MXFP8: e4m3 values ``[M, N]`` and ``[M, N / 32]`` uint8 ue8m0
@@ -102,7 +130,8 @@ def make_gemm(
             ``None`` gives the reference's behaviour.
 
     Returns:
-        ``(launch, out)``; with ``out_mx``, the e4m3 values and their scales follow. ``launch()`` runs the kernel
+        ``(launch, out)``, or ``(launch, out, pre)`` if ``act="gelu"``, where ``pre`` is ``None`` unless
+        ``store_pre`` is set. With ``out_mx``, the e4m3 values and their scales follow. ``launch()`` runs the kernel
         on the current stream and fills the outputs.
 
     Raises:
@@ -114,19 +143,19 @@ def make_gemm(
     if (a.dtype not in _TYPES and not fp8) or b.dtype != a.dtype:
         raise ValueError("a and b must share a bf16, fp16 or float8_e4m3fn dtype")
     _gemm_arch(a, fp8, act, accum, a_scale_mx is not None or b_scale_mx is not None, out_mx)
-    if a.dtype == torch.float16:
-        raise NotImplementedError("warpy_kernels has no fp16 gemm for SM100 yet; supported: bfloat16 and float8_e4m3fn")
-    if act or store_pre or pre is not None or a_trans or b_trans or accum:
-        raise NotImplementedError(
-            "warpy_kernels for SM100 has no act/store_pre/pre/a_trans/b_trans/accum gemm epilogue yet"
-        )
+    if act not in _ACT:
+        raise ValueError(f"act must be '', 'gelu' or 'dgelu', got {act!r}")
+    if a_trans or b_trans:
+        if fp8:
+            raise ValueError("transposed operands need bf16 or fp16 inputs")
+        raise NotImplementedError("warpy_kernels for SM100 has no transposed-operand gemm yet")
+    if store_pre and act != "gelu":
+        raise ValueError("store_pre needs act='gelu'")
     odt = out_dtype if fp8 and out is None else out.dtype if out is not None else a.dtype
     if odt not in _TYPES:
         raise ValueError("the output must be bf16 or fp16")
     if not fp8 and odt != a.dtype:
         raise ValueError(f"out must have the dtype of a and b for 16-bit inputs, got {odt} and {a.dtype}")
-    if odt != torch.bfloat16:
-        raise NotImplementedError("warpy_kernels for SM100 writes bf16 outputs only")
     bk = bk or (128 if fp8 else 64)
     if bn not in (128, 256):
         raise ValueError("bn must be 128 or 256")
@@ -138,52 +167,79 @@ def make_gemm(
         raise ValueError("a and b must be contiguous")
     if m % BM or n % bn or k % bk or k % (128 if fp8 else 64):
         raise ValueError(f"M must be a multiple of 128, N of {bn} and K of {bk}, got {m}, {n}, {k}")
+    if accum and out is None:
+        raise ValueError("accum needs an out tensor holding the addend")
     if out is None:
         out = torch.empty(m, n, dtype=odt, device=a.device)
     elif out.shape != (m, n) or not out.is_contiguous() or out.data_ptr() % 16:
         raise ValueError("out must be a contiguous [M, N] tensor aligned to 16 bytes")
-    alpha = 1.0
+    if act == "dgelu" and (
+        pre is None or pre.shape != out.shape or pre.dtype != out.dtype or not pre.is_contiguous()
+    ):
+        raise ValueError("act='dgelu' needs a contiguous pre shaped and typed like out")
+    pre_out = torch.empty_like(out) if store_pre else None
+    pre_in = pre if act == "dgelu" else None
     for name, s, size in (("scale_a", scale_a, m), ("scale_b", scale_b, n)):
         if s is None:
             continue
-        if s.dtype != torch.float32 or not s.is_cuda or s.numel() not in (1, size):
+        if (
+            s.dtype != torch.float32
+            or not s.is_cuda
+            or s.numel() not in (1, size)
+            or (s.numel() > 1 and (not s.is_contiguous() or s.data_ptr() % 8))
+        ):
             raise ValueError(
                 f"{name} must be a float32 CUDA tensor of 1 or {size} elements, contiguous and 8-byte aligned"
             )
-        if s.numel() > 1 and size != 1:
-            raise NotImplementedError("warpy_kernels for SM100 has no per-row / per-column gemm scales yet")
+    # a one-element scale is only used for fp8 inputs (as in the reference); vectors apply to every dtype
+    row_scale = scale_a is not None and scale_a.numel() > 1 and m > 1
+    col_scale = scale_b is not None and scale_b.numel() > 1 and n > 1
+    if not fp8:
+        scale_a = scale_a if row_scale else None
+        scale_b = scale_b if col_scale else None
+    if col_scale and scale_b.data_ptr() % 16:
+        scale_b = scale_b.clone()  # the kernel reads column scales as 16-byte vectors
     _check_mx("a_scale_mx", a_scale_mx, m, k, fp8)
     _check_mx("b_scale_mx", b_scale_mx, n, k, fp8)
     q_mx = torch.empty(m, n, dtype=torch.float8_e4m3fn, device=a.device) if out_mx else None
     s_mx = torch.empty(m, n // 32, dtype=torch.uint8, device=a.device) if out_mx else None
     lib = _lib.lib()
     dev = a.device
+    ptr = lambda t: t.data_ptr() if t is not None else None
+
+    def fill_epilogue(args):
+        args.scale_a, args.scale_b = ptr(scale_a), ptr(scale_b)
+        args.scale_a_rows, args.scale_b_cols = int(row_scale), int(col_scale)
+        args.accum, args.act = int(bool(accum)), _ACT[act]
+        args.pre_out, args.pre_in = ptr(pre_out), ptr(pre_in)
 
     if not fp8:
-        if out_mx:
-            raise NotImplementedError("warpy_kernels for SM100 writes MXFP8 outputs from the fp8 gemm only")
+        args = _Gemm16Args()
+        args.q_mx, args.s_mx = ptr(q_mx), ptr(s_mx)
+        args.a, args.b, args.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
+        args.m, args.n, args.k = m, n, k
+        args.f16 = int(a.dtype == torch.float16)
+        fill_epilogue(args)
+        keep = (a, b, scale_a, scale_b, pre_out, pre_in)
 
         def launch():
             with torch.cuda.device(dev):
-                code = lib.wk_gemm_bf16(
-                    a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, _lib.stream_ptr(dev)
-                )
-            _lib.check(code, "gemm (bf16)")
+                code = lib.wk_gemm_16bit(ctypes.byref(args), _lib.stream_ptr(dev))
+            _lib.check(code, "gemm (16-bit)")
+            return keep
 
     else:
         ws_bytes = lib.wk_gemm_mxfp8_workspace_bytes(m, n, k)
         workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)  # re-tiled scale factors
         args = _MxArgs()
         args.a, args.b, args.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
-        args.a_scale_mx = a_scale_mx.data_ptr() if a_scale_mx is not None else None
-        args.b_scale_mx = b_scale_mx.data_ptr() if b_scale_mx is not None else None
-        args.scale_a = scale_a.data_ptr() if scale_a is not None else None
-        args.scale_b = scale_b.data_ptr() if scale_b is not None else None
-        args.q_mx = q_mx.data_ptr() if out_mx else None
-        args.s_mx = s_mx.data_ptr() if out_mx else None
+        args.a_scale_mx, args.b_scale_mx = ptr(a_scale_mx), ptr(b_scale_mx)
+        args.q_mx, args.s_mx = ptr(q_mx), ptr(s_mx)
         args.workspace, args.workspace_bytes = workspace.data_ptr(), ws_bytes
         args.m, args.n, args.k = m, n, k
-        keep = (a, b, a_scale_mx, b_scale_mx, scale_a, scale_b, workspace)
+        args.out_f16 = int(odt == torch.float16)
+        fill_epilogue(args)
+        keep = (a, b, a_scale_mx, b_scale_mx, scale_a, scale_b, workspace, pre_out, pre_in)
 
         def launch():
             with torch.cuda.device(dev):
@@ -192,18 +248,19 @@ def make_gemm(
             return keep
 
     mx = (q_mx, s_mx) if out_mx else ()
-    return (launch, out, *mx)
+    return (launch, out, pre_out, *mx) if act == "gelu" else (launch, out, *mx)
 
 
 def gemm(a, b, out=None, **kwargs):
     """Compute ``(a @ b.T) * scale_a * scale_b``; arguments as in ``make_gemm``.
 
     Returns:
-        ``[M, N]`` in the output dtype. With ``out_mx``, a tuple that ends with the e4m3 values and their scales.
+        ``[M, N]`` in the output dtype, or ``(out, pre)`` if ``act="gelu"``. With ``out_mx``, a tuple that ends with
+        the e4m3 values and their scales.
     """
     launch, out, *rest = make_gemm(a, b, out, **kwargs)
     launch()
-    return (out, *rest) if rest else out
+    return (out, *rest) if kwargs.get("act") == "gelu" or kwargs.get("out_mx") else out
 
 
 def autotune_gemm(a, b, candidates=None, iters=20, verbose=True, **kwargs):
