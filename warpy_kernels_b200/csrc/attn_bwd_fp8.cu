@@ -42,6 +42,8 @@ constexpr int TILE_BYTES = 128 * 128;
 constexpr int SF_BYTES = 512;
 constexpr int THREADS = 320;          // TMA warp, MMA warp, 8 element-wise warps (two threads per row)
 constexpr int ELEMWISE_THREADS = 256;
+constexpr int HALF_THREADS = 128;     // the element-wise threads of one 64-column half of a tile
+constexpr int HALF_COLS = 64;
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -179,7 +181,7 @@ constexpr int A_SMEM_NEED = 2 * TILE_BYTES + A_STAGES * A_STAGE_BYTES + 3 * SF_B
 constexpr int A_SMEM_BYTES = A_SMEM_NEED > 120 * 1024 ? A_SMEM_NEED : 120 * 1024;
 constexpr int A_ST_COL = 0, A_DPT_COL = 128, A_DV_COL = 256, A_DK_COL = 384;
 // scale-factor columns inside the consumed S^T columns; the two threads of a row own 4 columns each
-constexpr int A_SF_P = 64, A_SF_UNIT = 72, A_SF_DS = 76;
+constexpr int A_SF_P = 16, A_SF_UNIT = 20, A_SF_DS = 24;
 
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -197,10 +199,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const uint32_t kv_full = bar_base;
   auto q_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto q_empty = [&](int s) { return bar_base + 8u * (1 + A_STAGES + s); };
-  const uint32_t s_full = bar_base + 8u * (1 + 2 * A_STAGES);
-  const uint32_t p_full = s_full + 8;
-  const uint32_t acc_full = s_full + 16;
-  const uint32_t tmem_slot = s_full + 24;
+  // the two 64-query halves of a tile are handed back and forth separately (h = 0, 1)
+  auto s_full = [&](int h) { return bar_base + 8u * (1 + 2 * A_STAGES + h); };
+  auto p_full = [&](int h) { return bar_base + 8u * (3 + 2 * A_STAGES + h); };
+  const uint32_t acc_full = bar_base + 8u * (5 + 2 * A_STAGES);
+  const uint32_t tmem_slot = acc_full + 8;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));  // generic pointer to the aligned base
 
   const int warp = threadIdx.x / 32;
@@ -223,8 +226,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       mbar_init(q_full(s), 1);
       mbar_init(q_empty(s), 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, ELEMWISE_THREADS);
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(s_full(h), 1);
+      mbar_init(p_full(h), HALF_THREADS);
+    }
     mbar_init(acc_full, 1);
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
@@ -264,42 +269,69 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0 && n_iter > 0) {
-      constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BN, BM);
+      // A tile is processed as two halves of 64 queries, each with its own pair of barriers, so that the tensor
+      // pipe works on one half while the element-wise warps of the other half are busy:
+      //   S^T, dP^T (h) -> element-wise (h) -> dV, dK += (h) -> S^T, dP^T of the next tile (h) -> ...
+      // All MMAs come from this one thread, so the products of the next tile overwrite a half's columns only
+      // after the products that read its codes (the tensor pipe runs in issue order).
+      constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BN, BM / 2);
       const uint32_t st_tmem = tmem_base + A_ST_COL;
       const uint32_t dpt_tmem = tmem_base + A_DPT_COL;
       bool ok = mbar_wait(kv_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
       const uint64_t k_desc = smem_desc_sw128(k_smem, 16, 1024);
       const uint64_t v_desc = smem_desc_sw128(v_smem, 16, 1024);
+      auto q_desc_of = [&](int it) { return smem_desc_sw128(stage_smem + (it % A_STAGES) * A_STAGE_BYTES, 16, 1024); };
+      // S^T = K Q^T and dP^T = V dO8^T for queries [64 h, 64 h + 64) of tile `it`: rows 64 h.. of the Q and dO8
+      // tiles are 64 x 128 bytes further on (+512 in descriptor units)
+      auto ss_half = [&](int it, int h) {
+        const uint64_t q_desc = q_desc_of(it) + 512 * h;
+        const uint64_t do_desc = q_desc + (TILE_BYTES >> 4);
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) mma_f8_ss(st_tmem + HALF_COLS * h, k_desc + 2 * k, q_desc + 2 * k, idesc_ss, k != 0);
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) mma_f8_ss(dpt_tmem + HALF_COLS * h, v_desc + 2 * k, do_desc + 2 * k, idesc_ss, k != 0);
+        tc_commit(s_full(h));
+      };
+      // dV += (P g)^T dO8 and dK += dS^T Q8 over the same 64 queries.  B operands: the dO8 / Q8 tiles again, now
+      // read MN-major (K = queries, 32 per step = 4096 bytes, N = head dim)
+      auto ts_half = [&](int it, int h) {
+        const uint64_t q_desc = q_desc_of(it);
+        const uint64_t do_desc = q_desc + (TILE_BYTES >> 4);
+        const uint32_t hb = st_tmem + HALF_COLS * h;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          mma_mxf8_ts(tmem_base + A_DV_COL, hb + 8 * k, do_desc + 256 * (2 * h + k), make_idesc_mx_major(BN, D, k, 0, 0, 1),
+                      hb + A_SF_P, hb + A_SF_UNIT, (it | h | k) != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          mma_mxf8_ts(tmem_base + A_DK_COL, dpt_tmem + HALF_COLS * h + 8 * k, q_desc + 256 * (2 * h + k),
+                      make_idesc_mx_major(BN, D, k, 0, 0, 1), hb + A_SF_DS, hb + A_SF_UNIT, (it | h | k) != 0);
+        }
+      };
+      ok = ok && mbar_wait(q_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD);
+      if (ok) {
+        tc_fence_after();
+        ss_half(0, 0);
+        ss_half(0, 1);
+      }
       for (int it = 0; ok && it < n_iter; ++it) {
         const int s = it % A_STAGES;
-        const uint32_t ph = (it / A_STAGES) & 1;
-        if (!mbar_wait(q_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        const bool more = it + 1 < n_iter;
+        if (!mbar_wait(p_full(0), it & 1, p.status, WK_ERR_TIMEOUT_P)) break;
         tc_fence_after();
-        const uint32_t base = stage_smem + s * A_STAGE_BYTES;
-        const uint64_t q_desc = smem_desc_sw128(base, 16, 1024);
-        const uint64_t do_desc = smem_desc_sw128(base + TILE_BYTES, 16, 1024);
-#pragma unroll
-        for (int k = 0; k < D / 32; ++k) mma_f8_ss(st_tmem, k_desc + 2 * k, q_desc + 2 * k, idesc_ss, k != 0);
-#pragma unroll
-        for (int k = 0; k < D / 32; ++k) mma_f8_ss(dpt_tmem, v_desc + 2 * k, do_desc + 2 * k, idesc_ss, k != 0);
-        tc_commit(s_full);
-        if (!mbar_wait(p_full, it & 1, p.status, WK_ERR_TIMEOUT_P)) break;
+        ts_half(it, 0);
+        if (more) {
+          if (!mbar_wait(q_full((it + 1) % A_STAGES), ((it + 1) / A_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+          tc_fence_after();
+          ss_half(it + 1, 0);
+        }
+        if (!mbar_wait(p_full(1), it & 1, p.status, WK_ERR_TIMEOUT_P)) break;
         tc_fence_after();
-        // B operands: the dO8 / Q8 tiles again, now read MN-major (K = queries, N = head dim)
-#pragma unroll
-        for (int k = 0; k < BM / 32; ++k) {
-          mma_mxf8_ts(tmem_base + A_DV_COL, st_tmem + 8 * k, do_desc + 256 * k,
-                      make_idesc_mx_major(BN, D, k & 1, 0, 0, 1), st_tmem + A_SF_P + 4 * (k >> 1),
-                      st_tmem + A_SF_UNIT, (it | k) != 0);
-        }
-#pragma unroll
-        for (int k = 0; k < BM / 32; ++k) {
-          mma_mxf8_ts(tmem_base + A_DK_COL, dpt_tmem + 8 * k, q_desc + 256 * k,
-                      make_idesc_mx_major(BN, D, k & 1, 0, 0, 1), st_tmem + A_SF_DS + 4 * (k >> 1),
-                      st_tmem + A_SF_UNIT, (it | k) != 0);
-        }
+        ts_half(it, 1);
         tc_commit(q_empty(s));
-        if (it == n_iter - 1) tc_commit(acc_full);
+        if (more) ss_half(it + 1, 1);
+        if (!more) tc_commit(acc_full);
       }
     }
     __syncwarp();
@@ -309,8 +341,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const int r = quad * 32 + lane;  // key row of the tile == TMEM lane
     const int key = n0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t st_tmem = tmem_base + lane_addr + A_ST_COL;
-    const uint32_t dpt_tmem = tmem_base + lane_addr + A_DPT_COL;
+    // this thread's half of the tile: scores in columns [64 half, 64 half + 64) of both buffers
+    const uint32_t st_tmem = tmem_base + lane_addr + A_ST_COL + HALF_COLS * half;
+    const uint32_t dpt_tmem = tmem_base + lane_addr + A_DPT_COL + HALF_COLS * half;
     const int sc = b * p.Hkv + hkv;
     const float sq = p.q_descale[sc], sk = p.k_descale[sc];
     const float beta = p.softmax_scale * sq * sk * LOG2E;
@@ -319,7 +352,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     for (int it = 0; it < n_iter; ++it) {
       const int s = it % A_STAGES;
       const int m0 = (m_first + it % tiles_per_head) * BM;
-      if (!mbar_wait_warp(s_full, it & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+      if (!mbar_wait_warp(s_full(half), it & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
         ok = false;
         break;
       }
@@ -333,10 +366,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       uint32_t sf_p = 0, sf_d = 0;
 #pragma unroll 1
       for (int cc = 0; cc < 2; ++cc) {
-        const int c = 2 * half + cc;
+        const int c = 2 * half + cc;  // block of 32 queries within the tile
         uint32_t sraw[32], draw[32];
-        tmem_ld32(st_tmem + c * 32, sraw);
-        tmem_ld32(dpt_tmem + c * 32, draw);
+        tmem_ld32(st_tmem + cc * 32, sraw);
+        tmem_ld32(dpt_tmem + cc * 32, draw);
         tc_wait_ld();
         float pt[32], ds[32];
         if (tile_masked) {
@@ -360,18 +393,19 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         float inv_p, inv_d;
         const uint32_t bp = block_scale(absmax_bits(pt), inv_p);
         const uint32_t bd = block_scale(absmax_bits(ds), inv_d);
-        quantize_block_to_tmem(pt, st_tmem + c * 8, inv_p);
-        quantize_block_to_tmem(ds, dpt_tmem + c * 8, inv_d);
+        // the codes go to the first columns of the half, which block 0's scores have left
+        quantize_block_to_tmem(pt, st_tmem + cc * 8, inv_p);
+        quantize_block_to_tmem(ds, dpt_tmem + cc * 8, inv_d);
         sf_p |= bp << (8 * cc);
         sf_d |= bd << (8 * cc);
       }
       // scale factors straight into TMEM: the MMA reads the scale of row r from lane r, column r / 32
-      tmem_st1(st_tmem + A_SF_P + 4 * half + quad, sf_p);
+      tmem_st1(st_tmem + A_SF_P + quad, sf_p);
       tmem_st4(st_tmem + A_SF_UNIT, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-      tmem_st1(st_tmem + A_SF_DS + 4 * half + quad, sf_d);
+      tmem_st1(st_tmem + A_SF_DS + quad, sf_d);
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(p_full(half));
     }
 
     if (n_iter > 0 && ok) ok = mbar_wait_warp(acc_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
@@ -427,7 +461,7 @@ constexpr int B_STAGE_BYTES = 2 * TILE_BYTES;  // K tile, V tile
 constexpr int B_SMEM_NEED = 2 * TILE_BYTES + B_STAGES * B_STAGE_BYTES + 2 * SF_BYTES + 1024 + 256;
 constexpr int B_SMEM_BYTES = B_SMEM_NEED > 120 * 1024 ? B_SMEM_NEED : 120 * 1024;
 constexpr int B_S_COL = 0, B_DP_COL = 128, B_DQ_COL = 256;
-constexpr int B_SF_DS = 64, B_SF_UNIT = 72;
+constexpr int B_SF_DS = 16, B_SF_UNIT = 20;
 
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -444,10 +478,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const uint32_t q_full = bar_base;
   auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + B_STAGES + s); };
-  const uint32_t s_full = bar_base + 8u * (1 + 2 * B_STAGES);
-  const uint32_t p_full = s_full + 8;
-  const uint32_t acc_full = s_full + 16;
-  const uint32_t tmem_slot = s_full + 24;
+  // the two 64-key halves of a tile are handed back and forth separately (h = 0, 1)
+  auto s_full = [&](int h) { return bar_base + 8u * (1 + 2 * B_STAGES + h); };
+  auto p_full = [&](int h) { return bar_base + 8u * (3 + 2 * B_STAGES + h); };
+  const uint32_t acc_full = bar_base + 8u * (5 + 2 * B_STAGES);
+  const uint32_t tmem_slot = acc_full + 8;
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -469,8 +504,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, ELEMWISE_THREADS);
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(s_full(h), 1);
+      mbar_init(p_full(h), HALF_THREADS);
+    }
     mbar_init(acc_full, 1);
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
@@ -506,36 +543,59 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
-      constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BM, BN);
+      // Key tiles are processed as two halves of 64 keys, as in the dK/dV kernel: the tensor pipe works on one
+      // half while the element-wise warps of the other are busy.
+      constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BM, BN / 2);
       const uint32_t s_tmem = tmem_base + B_S_COL;
       const uint32_t dp_tmem = tmem_base + B_DP_COL;
       bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
       const uint64_t q_desc = smem_desc_sw128(q_smem, 16, 1024);
       const uint64_t do_desc = smem_desc_sw128(do_smem, 16, 1024);
+      auto k_desc_of = [&](int j) { return smem_desc_sw128(stage_smem + (j % B_STAGES) * B_STAGE_BYTES, 16, 1024); };
+      // S = Q K^T and dP = dO8 V^T for keys [64 h, 64 h + 64) of tile j (rows 64 h.. of the K and V tiles: +512 in
+      // descriptor units)
+      auto ss_half = [&](int j, int h) {
+        const uint64_t k_desc = k_desc_of(j) + 512 * h;
+        const uint64_t v_desc = k_desc + (TILE_BYTES >> 4);
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) mma_f8_ss(s_tmem + HALF_COLS * h, q_desc + 2 * k, k_desc + 2 * k, idesc_ss, k != 0);
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) mma_f8_ss(dp_tmem + HALF_COLS * h, do_desc + 2 * k, v_desc + 2 * k, idesc_ss, k != 0);
+        tc_commit(s_full(h));
+      };
+      // dQ += dS K over the same 64 keys: A = dS codes in the dP columns, B = the K tile read MN-major
+      auto ts_half = [&](int j, int h) {
+        const uint64_t k_desc = k_desc_of(j);
+        const uint32_t hb = s_tmem + HALF_COLS * h;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          mma_mxf8_ts(tmem_base + B_DQ_COL, dp_tmem + HALF_COLS * h + 8 * k, k_desc + 256 * (2 * h + k),
+                      make_idesc_mx_major(BM, D, k, 0, 0, 1), hb + B_SF_DS, hb + B_SF_UNIT, (j | h | k) != 0);
+        }
+      };
+      ok = ok && mbar_wait(kv_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD);
+      if (ok) {
+        tc_fence_after();
+        ss_half(0, 0);
+        ss_half(0, 1);
+      }
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int s = j % B_STAGES;
-        const uint32_t ph = (j / B_STAGES) & 1;
-        if (!mbar_wait(kv_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        const bool more = j + 1 < n_tiles;
+        if (!mbar_wait(p_full(0), j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
         tc_fence_after();
-        const uint32_t base = stage_smem + s * B_STAGE_BYTES;
-        const uint64_t k_desc = smem_desc_sw128(base, 16, 1024);
-        const uint64_t v_desc = smem_desc_sw128(base + TILE_BYTES, 16, 1024);
-#pragma unroll
-        for (int k = 0; k < D / 32; ++k) mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_ss, k != 0);
-#pragma unroll
-        for (int k = 0; k < D / 32; ++k) mma_f8_ss(dp_tmem, do_desc + 2 * k, v_desc + 2 * k, idesc_ss, k != 0);
-        tc_commit(s_full);
-        if (!mbar_wait(p_full, j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
-        tc_fence_after();
-        // dQ += dS K: A = dS codes in the dP columns, B = the K tile read MN-major
-#pragma unroll
-        for (int k = 0; k < BN / 32; ++k) {
-          mma_mxf8_ts(tmem_base + B_DQ_COL, dp_tmem + 8 * k, k_desc + 256 * k,
-                      make_idesc_mx_major(BM, D, k & 1, 0, 0, 1), s_tmem + B_SF_DS + 4 * (k >> 1),
-                      s_tmem + B_SF_UNIT, (j | k) != 0);
+        ts_half(j, 0);
+        if (more) {
+          if (!mbar_wait(kv_full((j + 1) % B_STAGES), ((j + 1) / B_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+          tc_fence_after();
+          ss_half(j + 1, 0);
         }
+        if (!mbar_wait(p_full(1), j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
+        tc_fence_after();
+        ts_half(j, 1);
         tc_commit(kv_empty(s));
-        if (j == n_tiles - 1) tc_commit(acc_full);
+        if (more) ss_half(j + 1, 1);
+        if (!more) tc_commit(acc_full);
       }
     }
     __syncwarp();
@@ -545,8 +605,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int r = quad * 32 + lane;
     const int row = m0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t s_tmem = tmem_base + lane_addr + B_S_COL;
-    const uint32_t dp_tmem = tmem_base + lane_addr + B_DP_COL;
+    // this thread's half of the tile: scores in columns [64 half, 64 half + 64) of both buffers
+    const uint32_t s_tmem = tmem_base + lane_addr + B_S_COL + HALF_COLS * half;
+    const uint32_t dp_tmem = tmem_base + lane_addr + B_DP_COL + HALF_COLS * half;
     const int sc = b * p.Hkv + hkv;
     const float sq = p.q_descale[sc], sk = p.k_descale[sc];
     const float beta = p.softmax_scale * sq * sk * LOG2E;
@@ -555,7 +616,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     bool ok = true;
 
     for (int j = 0; j < n_tiles; ++j) {
-      if (!mbar_wait_warp(s_full, j & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+      if (!mbar_wait_warp(s_full(half), j & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
         ok = false;
         break;
       }
@@ -566,10 +627,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       uint32_t sf_d = 0;
 #pragma unroll 1
       for (int cc = 0; cc < 2; ++cc) {
-        const int c = 2 * half + cc;
+        const int c = 2 * half + cc;  // block of 32 keys within the tile
         uint32_t sraw[32], draw[32];
-        tmem_ld32(s_tmem + c * 32, sraw);
-        tmem_ld32(dp_tmem + c * 32, draw);
+        tmem_ld32(s_tmem + cc * 32, sraw);
+        tmem_ld32(dp_tmem + cc * 32, draw);
         tc_wait_ld();
         float ds[32];
         if (tile_masked) {
@@ -588,14 +649,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
         float inv_d;
         const uint32_t bd = block_scale(absmax_bits(ds), inv_d);
-        quantize_block_to_tmem(ds, dp_tmem + c * 8, inv_d);
+        quantize_block_to_tmem(ds, dp_tmem + cc * 8, inv_d);
         sf_d |= bd << (8 * cc);
       }
-      tmem_st1(s_tmem + B_SF_DS + 4 * half + quad, sf_d);
+      tmem_st1(s_tmem + B_SF_DS + quad, sf_d);
       tmem_st4(s_tmem + B_SF_UNIT, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(p_full(half));
     }
 
     if (n_tiles > 0 && ok) ok = mbar_wait_warp(acc_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
