@@ -56,7 +56,7 @@ struct PrepParams {
   const float* lse;           // [B,Hq,*] base 2
   const float* v_descale;     // [B,Hkv]
   uint8_t* do8;               // [B,Hq,Nq,D] contiguous
-  float4* qstat;              // [B,Hq,Nq_pad]: (L, g, g*sv, D)
+  float* qstat;               // [B,Hq,Nq_pad/128][4][128]: per 128 rows the arrays -L, g, g*sv, -D
   int64_t do_sb, do_sh, do_sn;
   int64_t o_sb, o_sh, o_sn;
   int64_t lse_sb, lse_sh;
@@ -72,10 +72,11 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const PrepParams p) 
   const int i = warp % p.nq_pad;
   const int h = (warp / p.nq_pad) % p.Hq;
   const int b = warp / (p.nq_pad * p.Hq);
-  float4* stat = p.qstat + (static_cast<int64_t>(b) * p.Hq + h) * p.nq_pad + i;
+  // the four values of row i sit 128 floats apart inside the row's tile of 128
+  float* stat = p.qstat + ((static_cast<int64_t>(b) * p.Hq + h) * p.nq_pad + (i & ~127)) * 4 + (i & 127);
   if (i >= p.Nq) {
     // padding rows: lse = +inf makes every probability zero
-    if (lane == 0) *stat = make_float4(INFINITY, 0.f, 0.f, 0.f);
+    if (lane < 4) stat[lane * 128] = lane == 0 ? -INFINITY : 0.f;
     return;
   }
   const __nv_bfloat16* dsrc = p.dout + b * p.do_sb + h * p.do_sh + static_cast<int64_t>(i) * p.do_sn + lane * 4;
@@ -114,7 +115,10 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const PrepParams p) 
   if (lane == 0) {
     const float sv = p.v_descale[b * p.Hkv + h / (p.Hq / p.Hkv)];
     const float L = p.lse[b * p.lse_sb + h * p.lse_sh + i];
-    *stat = make_float4(L, g, g * sv, dsum * g);
+    stat[0] = -L;
+    stat[128] = g;
+    stat[256] = g * sv;
+    stat[384] = -dsum * g;
   }
 }
 
@@ -130,34 +134,58 @@ __device__ __forceinline__ uint32_t block_scale(uint32_t amax_bits, float& inv) 
   return static_cast<uint32_t>(sf);
 }
 
-__device__ __forceinline__ void quantize_block_to_tmem(const float (&x)[32], uint32_t taddr, float inv) {
+// The element-wise code keeps a block of 32 values as 16 packed fp32 pairs (fma/mul.f32x2 work on two at once).
+__device__ __forceinline__ void quantize_block_to_tmem(const uint64_t (&x)[16], uint32_t taddr, float inv) {
   const uint64_t inv2 = pack_f32x2(inv, inv);
   uint32_t w[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     float a, b, c, d;
-    unpack_f32x2(mul_f32x2(pack_f32x2(x[4 * i], x[4 * i + 1]), inv2), a, b);
-    unpack_f32x2(mul_f32x2(pack_f32x2(x[4 * i + 2], x[4 * i + 3]), inv2), c, d);
+    unpack_f32x2(mul_f32x2(x[2 * i], inv2), a, b);
+    unpack_f32x2(mul_f32x2(x[2 * i + 1], inv2), c, d);
     w[i] = pack_e4m3x4(a, b, c, d);
   }
   tmem_st8(taddr, w);
 }
 
 // Largest magnitude of 32 values, as an fp32 bit pattern.
-__device__ __forceinline__ uint32_t absmax_bits(const float (&x)[32]) {
+__device__ __forceinline__ uint32_t absmax_bits(const uint64_t (&x)[16]) {
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-  for (int i = 0; i < 32; i += 8) {
-    a0 = fmaxf(fmaxf(a0, fabsf(x[i + 0])), fabsf(x[i + 1]));
-    a1 = fmaxf(fmaxf(a1, fabsf(x[i + 2])), fabsf(x[i + 3]));
-    a2 = fmaxf(fmaxf(a2, fabsf(x[i + 4])), fabsf(x[i + 5]));
-    a3 = fmaxf(fmaxf(a3, fabsf(x[i + 6])), fabsf(x[i + 7]));
+  for (int i = 0; i < 16; i += 4) {
+    float v0, v1, v2, v3, v4, v5, v6, v7;
+    unpack_f32x2(x[i + 0], v0, v1);
+    unpack_f32x2(x[i + 1], v2, v3);
+    unpack_f32x2(x[i + 2], v4, v5);
+    unpack_f32x2(x[i + 3], v6, v7);
+    a0 = fmaxf(fmaxf(a0, fabsf(v0)), fabsf(v1));
+    a1 = fmaxf(fmaxf(a1, fabsf(v2)), fabsf(v3));
+    a2 = fmaxf(fmaxf(a2, fabsf(v4)), fabsf(v5));
+    a3 = fmaxf(fmaxf(a3, fabsf(v6)), fabsf(v7));
+  }
+  return __float_as_uint(fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)));
+}
+
+// Largest of 32 values that are all >= 0, as an fp32 bit pattern.
+__device__ __forceinline__ uint32_t max_bits_nonneg(const uint64_t (&x)[16]) {
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) {
+    float v0, v1, v2, v3, v4, v5, v6, v7;
+    unpack_f32x2(x[i + 0], v0, v1);
+    unpack_f32x2(x[i + 1], v2, v3);
+    unpack_f32x2(x[i + 2], v4, v5);
+    unpack_f32x2(x[i + 3], v6, v7);
+    a0 = max3(a0, v0, v1);
+    a1 = max3(a1, v2, v3);
+    a2 = max3(a2, v4, v5);
+    a3 = max3(a3, v6, v7);
   }
   return __float_as_uint(fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)));
 }
 
 struct BwdParams {
-  const float4* qstat;   // [B,Hq,nq_pad]
+  const float* qstat;    // [B,Hq,nq_pad/128][4][128]: -L, g, g*sv, -D of 128 rows
   const float* q_descale;
   const float* k_descale;
   __nv_bfloat16* dq;     // [B,Hq,Nq,D] contiguous
@@ -262,7 +290,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         mbar_expect_tx(q_full(s), A_STAGE_BYTES);
         tma_load_4d(base, &tmap_q, q_full(s), 0, m0, hq, b);
         tma_load_4d(base + TILE_BYTES, &tmap_do, q_full(s), 0, m0, hq, b);
-        bulk_load(base + 2 * TILE_BYTES, p.qstat + (static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0,
+        bulk_load(base + 2 * TILE_BYTES, p.qstat + ((static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0) * 4,
                   A_STAT_BYTES, q_full(s));
       }
     }
@@ -357,6 +385,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         break;
       }
       tc_fence_after();
+      // the tile's row records: arrays -L, g, g*sv, -D of 128 queries each, read four queries at a time
       const float4* stat = reinterpret_cast<const float4*>(smem_gen + (stage_smem - smem_base) + s * A_STAGE_BYTES +
                                                            2 * TILE_BYTES);
       // query column c is visible to this key iff key < Nk and (not causal or key <= m0 + c + shift)
@@ -371,27 +400,36 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         tmem_ld32(st_tmem + cc * 32, sraw);
         tmem_ld32(dpt_tmem + cc * 32, draw);
         tc_wait_ld();
-        float pt[32], ds[32];
-        if (tile_masked) {
+        uint64_t pt[16], ds[16];  // (P g)^T and dS^T of this key for 32 queries, as packed pairs
+        const uint64_t beta2 = pack_f32x2(beta, beta);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float4 st = stat[c * 32 + i];  // (L, g, g*sv, D): same address for every thread
-            float pr = ex2_approx(fmaf(__uint_as_float(sraw[i]), beta, -st.x));
-            if (c * 32 + i < first_col) pr = 0.f;
-            pt[i] = pr * st.y;
-            ds[i] = pr * fmaf(__uint_as_float(draw[i]), st.z, -st.w);
+        for (int i = 0; i < 8; ++i) {
+          // the same addresses for every thread: shared-memory broadcasts
+          const float4 nl = stat[c * 8 + i], g4 = stat[32 + c * 8 + i], z4 = stat[64 + c * 8 + i],
+                       nd = stat[96 + c * 8 + i];
+          float x0, x1, x2, x3;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[4 * i]), __uint_as_float(sraw[4 * i + 1])), beta2,
+                                 pack_f32x2(nl.x, nl.y)), x0, x1);
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[4 * i + 2]), __uint_as_float(sraw[4 * i + 3])), beta2,
+                                 pack_f32x2(nl.z, nl.w)), x2, x3);
+          float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+          if (tile_masked) {
+            if (c * 32 + 4 * i + 0 < first_col) p0 = 0.f;
+            if (c * 32 + 4 * i + 1 < first_col) p1 = 0.f;
+            if (c * 32 + 4 * i + 2 < first_col) p2 = 0.f;
+            if (c * 32 + 4 * i + 3 < first_col) p3 = 0.f;
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float4 st = stat[c * 32 + i];
-            const float pr = ex2_approx(fmaf(__uint_as_float(sraw[i]), beta, -st.x));
-            pt[i] = pr * st.y;
-            ds[i] = pr * fmaf(__uint_as_float(draw[i]), st.z, -st.w);
-          }
+          const uint64_t p01 = pack_f32x2(p0, p1), p23 = pack_f32x2(p2, p3);
+          pt[2 * i] = mul_f32x2(p01, pack_f32x2(g4.x, g4.y));
+          pt[2 * i + 1] = mul_f32x2(p23, pack_f32x2(g4.z, g4.w));
+          ds[2 * i] = mul_f32x2(p01, fma_f32x2(pack_f32x2(__uint_as_float(draw[4 * i]), __uint_as_float(draw[4 * i + 1])),
+                                               pack_f32x2(z4.x, z4.y), pack_f32x2(nd.x, nd.y)));
+          ds[2 * i + 1] =
+              mul_f32x2(p23, fma_f32x2(pack_f32x2(__uint_as_float(draw[4 * i + 2]), __uint_as_float(draw[4 * i + 3])),
+                                       pack_f32x2(z4.z, z4.w), pack_f32x2(nd.z, nd.w)));
         }
         float inv_p, inv_d;
-        const uint32_t bp = block_scale(absmax_bits(pt), inv_p);
+        const uint32_t bp = block_scale(max_bits_nonneg(pt), inv_p);  // P >= 0 and g > 0
         const uint32_t bd = block_scale(absmax_bits(ds), inv_d);
         // the codes go to the first columns of the half, which block 0's scores have left
         quantize_block_to_tmem(pt, st_tmem + cc * 8, inv_p);
@@ -611,7 +649,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int sc = b * p.Hkv + hkv;
     const float sq = p.q_descale[sc], sk = p.k_descale[sc];
     const float beta = p.softmax_scale * sq * sk * LOG2E;
-    const float4 st = p.qstat[(static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + row];  // (L, g, g*sv, D)
+    const float* rec = p.qstat + ((static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0) * 4 + r;
+    const float neg_l = rec[0], gsv = rec[256], neg_d = rec[384];  // -L, g*sv, -D of this query
     const int row_limit = min(p.causal ? row + shift : p.Nk - 1, p.Nk - 1);
     bool ok = true;
 
@@ -632,20 +671,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tmem_ld32(s_tmem + cc * 32, sraw);
         tmem_ld32(dp_tmem + cc * 32, draw);
         tc_wait_ld();
-        float ds[32];
-        if (tile_masked) {
+        uint64_t ds[16];  // dS of this query for 32 keys, as packed pairs
+        const uint64_t beta2 = pack_f32x2(beta, beta), nl2 = pack_f32x2(neg_l, neg_l), z2 = pack_f32x2(gsv, gsv),
+                       nd2 = pack_f32x2(neg_d, neg_d);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float pr = ex2_approx(fmaf(__uint_as_float(sraw[i]), beta, -st.x));
-            if (c * 32 + i > limit) pr = 0.f;
-            ds[i] = pr * fmaf(__uint_as_float(draw[i]), st.z, -st.w);
+        for (int i = 0; i < 16; ++i) {
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[2 * i]), __uint_as_float(sraw[2 * i + 1])), beta2, nl2),
+                       x0, x1);
+          float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+          if (tile_masked) {
+            if (c * 32 + 2 * i > limit) p0 = 0.f;
+            if (c * 32 + 2 * i + 1 > limit) p1 = 0.f;
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float pr = ex2_approx(fmaf(__uint_as_float(sraw[i]), beta, -st.x));
-            ds[i] = pr * fmaf(__uint_as_float(draw[i]), st.z, -st.w);
-          }
+          ds[i] = mul_f32x2(pack_f32x2(p0, p1),
+                            fma_f32x2(pack_f32x2(__uint_as_float(draw[2 * i]), __uint_as_float(draw[2 * i + 1])), z2, nd2));
         }
         float inv_d;
         const uint32_t bd = block_scale(absmax_bits(ds), inv_d);
@@ -741,7 +781,7 @@ extern "C" int wk_attn_bwd_fp8(const wk_attn_bwd_args* a, void* stream) {
   const int nq_pad = (a->Nq + 127) / 128 * 128;
   uint8_t* do8 = static_cast<uint8_t*>(a->workspace);
   const int64_t do8_bytes = (static_cast<int64_t>(a->B) * a->Hq * a->Nq * D + 255) / 256 * 256;
-  float4* qstat = reinterpret_cast<float4*>(do8 + do8_bytes);
+  float* qstat = reinterpret_cast<float*>(do8 + do8_bytes);
 
   PrepParams pp;
   pp.dout = static_cast<const __nv_bfloat16*>(a->dout);
