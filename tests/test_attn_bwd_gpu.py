@@ -15,12 +15,14 @@ from tests.helpers import hard_inputs, load_golden, randn_qkv
 pytestmark = pytest.mark.gpu
 
 GOLDEN = ["attn_mha_causal", "attn_gqa_ragged_causal", "attn_gqa_noncausal", "attn_short_q_causal"]
-# d = 128 shapes of the reference's gradient test (tests/attn/test_grad.py) plus ragged / GQA / Nq != Nk cases
+# shapes of the reference's gradient test (tests/attn/test_grad.py) plus ragged / GQA / Nq != Nk cases
 SHAPES = [
     (1, 1, 1, 128, 128, 128),
     (2, 4, 2, 1000, 1000, 128),
+    (1, 2, 1, 300, 777, 64),
     (1, 2, 2, 512, 1024, 128),
     (1, 2, 1, 512, 128, 128),
+    (1, 2, 1, 512, 128, 64),
     (1, 8, 2, 384, 640, 128),
 ]
 

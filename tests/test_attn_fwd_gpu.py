@@ -15,12 +15,15 @@ from tests.helpers import fwd_errors, load_golden, randn_qkv, sink_qkv
 pytestmark = pytest.mark.gpu
 
 GOLDEN = ["attn_mha_causal", "attn_gqa_ragged_causal", "attn_gqa_noncausal", "attn_short_q_causal"]
-# the d = 128 shapes of the reference's forward test (tests/attn/test_fwd.py:23-31): (B, Hq, Hkv, Nq, Nk, d)
+# the shapes of the reference's forward test (tests/attn/test_fwd.py:23-31) plus one more: (B, Hq, Hkv, Nq, Nk, d)
 SHAPES = [
     (1, 1, 1, 128, 64, 128),
     (2, 4, 2, 1000, 1000, 128),
+    (1, 2, 1, 300, 777, 64),
     (1, 2, 2, 512, 1024, 128),
+    (1, 4, 4, 2048, 2048, 64),
     (1, 2, 1, 512, 128, 128),
+    (1, 2, 1, 512, 128, 64),
     (1, 8, 2, 384, 640, 128),
 ]
 

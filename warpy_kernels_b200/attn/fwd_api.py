@@ -41,6 +41,21 @@ def _kernel_view(x):
     return x if direct else x.contiguous()
 
 
+KERNEL_D = 128  # head dimension of the compiled kernels
+
+
+def _pad_head_dim(x):
+    """Zero-padded contiguous copy ``[..., 128]`` of a ``[..., 64]`` tensor.
+
+    Head dimension 64 runs through the head-dimension-128 kernels: zero columns add nothing to ``Q K^T`` and give
+    zero output columns, which the wrappers drop. Correct, at half the tensor-core efficiency of a native kernel.
+    """
+    padded = torch.zeros(*x.shape[:-1], KERNEL_D, dtype=torch.uint8 if x.element_size() == 1 else x.dtype, device=x.device)
+    src = x.view(torch.uint8) if x.element_size() == 1 else x
+    padded[..., : x.shape[-1]] = src
+    return padded.view(x.dtype) if x.element_size() == 1 else padded
+
+
 def _check_qkv(q, k, v):
     if not (q.dtype == k.dtype == v.dtype and q.dtype in (torch.float8_e4m3fn, torch.bfloat16)):
         raise ValueError("q, k and v must all be torch.float8_e4m3fn or all torch.bfloat16")
@@ -54,8 +69,6 @@ def _check_shapes(q, k, v):
             "need q [B, Hq, Nq, d] and k, v [B, Hkv, Nk, d] with d 64 or 128 and Hq a multiple of Hkv, "
             f"got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}"
         )
-    if d != 128:
-        raise NotImplementedError("warpy_kernels for SM100 has attention kernels for head dimension 128 only")
 
 
 def make_attn_fwd(
@@ -88,7 +101,8 @@ def make_attn_fwd(
     ``launch()`` may not see later in-place changes to the inputs. Call ``make_attn_fwd`` again for new values.
 
     Args:
-        q: ``[B, Hq, Nq, d]`` ``torch.float8_e4m3fn``, ``d`` = 128. Any strides work if the last one is 1, such as a
+        q: ``[B, Hq, Nq, d]`` ``torch.float8_e4m3fn``, ``d`` 64 or 128 (64 runs through the 128 kernels on
+            zero-padded copies). Any strides work if the last one is 1, such as a
             transposed ``[B, N, H, d]`` tensor. Inputs are copied if a stride or the base address is not a multiple
             of 16 bytes.
         k: ``[B, Hkv, Nk, d]``, same dtype and stride rules. ``Hq`` must be a multiple of ``Hkv``.
@@ -116,7 +130,7 @@ def make_attn_fwd(
         ValueError: If ``q``, ``k`` or ``v`` has the wrong dtype or shape, a descale is not ``[B, Hkv]`` or is given
             for bf16 inputs, ``out`` has the wrong shape, dtype or strides, or ``seqused_k`` is not an int32 CUDA
             tensor of shape ``[B]``.
-        NotImplementedError: If the GPU does not support the dtype of ``q``, or ``d`` is 64.
+        NotImplementedError: If the GPU does not support the dtype of ``q``.
     """
     _check_qkv(q, k, v)
     bf16 = q.dtype == torch.bfloat16
@@ -136,7 +150,7 @@ def make_attn_fwd(
     ones = cached_tensor(("ones", dev, B, Hkv), lambda: torch.ones(B, Hkv, dtype=torch.float32, device=dev))
     dq_, dk_, dv_ = [(x if x is not None else ones).float().contiguous() for x in (q_descale, k_descale, v_descale)]
 
-    qv, kv, vv = _kernel_view(q), _kernel_view(k), _kernel_view(v)
+    qv, kv, vv = (_pad_head_dim(x) for x in (q, k, v)) if d != KERNEL_D else (_kernel_view(x) for x in (q, k, v))
     if out is None:
         out = torch.empty_like(q, dtype=torch.bfloat16)
     elif (
@@ -149,8 +163,10 @@ def make_attn_fwd(
     ):
         raise ValueError("out must be a bf16 tensor shaped like q, with last stride 1 and even other strides")
     # the kernel stores 16-byte vectors; an output it cannot address that way is filled through a staging copy
-    out_direct = out.stride(3) == 1 and out.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in out.stride()[:3])
-    out_k = out if out_direct else torch.empty(q.shape, dtype=torch.bfloat16, device=dev)
+    out_direct = (
+        d == KERNEL_D and out.stride(3) == 1 and out.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in out.stride()[:3])
+    )
+    out_k = out if out_direct else torch.empty(B, Hq, Nq, KERNEL_D, dtype=torch.bfloat16, device=dev)
     if seqused_k is not None and (
         seqused_k.shape != (B,) or seqused_k.dtype != torch.int32 or seqused_k.device != dev
     ):
@@ -173,7 +189,7 @@ def make_attn_fwd(
     args.v_strides = (ctypes.c_int64 * 3)(*vv.stride()[:3])
     args.out_strides = (ctypes.c_int64 * 3)(*out_k.stride()[:3])
     args.lse_strides = (ctypes.c_int64 * 2)(Hq * nq_pad, nq_pad)
-    args.B, args.Hq, args.Hkv, args.Nq, args.Nk, args.d = B, Hq, Hkv, Nq, Nk, d
+    args.B, args.Hq, args.Hkv, args.Nq, args.Nk, args.d = B, Hq, Hkv, Nq, Nk, KERNEL_D
     args.causal, args.write_lse, args.lse_natural = int(bool(causal)), int(bool(return_lse)), int(bool(lse_natural))
     args.seqused_k = seq.data_ptr() if seq is not None else None
     args.softmax_scale = float(softmax_scale)
@@ -185,7 +201,7 @@ def make_attn_fwd(
             code = lib.wk_attn_fwd_fp8(ctypes.byref(args), _lib.stream_ptr(dev))
         _lib.check(code, "attn_fwd")
         if not out_direct:
-            out.copy_(out_k)
+            out.copy_(out_k[..., :d])
         return keep
 
     if return_lse:
