@@ -90,6 +90,8 @@ typedef struct {
   const void* pre_in;
   void* q_mx; /* optional [M, N] e4m3 copy of out, with s_mx [M, N/32]; N % 32 == 0 */
   void* s_mx;
+  int32_t a_trans; /* a is stored [K, M] (warpy_kernels/gemm/api.py:103-104, gemm/base.py:127-135) */
+  int32_t b_trans; /* b is stored [K, N] */
 } wk_gemm16_args;
 
 int wk_gemm_16bit(const wk_gemm16_args* args, void* stream);

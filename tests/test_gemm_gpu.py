@@ -328,3 +328,46 @@ def test_fp16_matches_fp32_product(cuda):
     o16 = gemm(a8, b8, out_dtype=torch.float16)
     assert o16.dtype == torch.float16
     assert R.rel_l2(o16.cpu(), R.gemm_reference(a8.cpu(), b8.cpu()).half()) <= 1e-3
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16"])
+@pytest.mark.parametrize("trans", [(True, False), (False, True), (True, True)])
+def test_transposed_operands(cuda, kind, trans):
+    """``a_trans`` / ``b_trans`` (``tests/gemm/test_gemm.py:83-91``): operands stored ``[K, M]`` / ``[K, N]``."""
+    from warpy_kernels import gemm
+
+    a_trans, b_trans = trans
+    m, n, k = 384, 640, 192
+    g = torch.Generator(device=cuda).manual_seed(0)
+    a, b, odt = _operands(cuda, kind, m, n, k, g)
+    at = a.T.contiguous() if a_trans else a
+    bt = b.T.contiguous() if b_trans else b
+    got = gemm(at, bt, a_trans=a_trans, b_trans=b_trans)
+    assert got.shape == (m, n) and got.dtype == odt
+    # same products in the same order as the plain layout: bit-identical
+    assert torch.equal(got, gemm(a, b))
+    assert R.rel_l2(got.float(), a.float() @ b.float().T) <= 1e-2
+
+
+def test_transposed_structured_operands(cuda):
+    """One distinct value per row and column, transposed storage: exposes MN-major tile indexing mistakes."""
+    from warpy_kernels import gemm
+
+    m, n, k = 256, 512, 256
+    a = torch.zeros(m, k, device=cuda)
+    b = torch.zeros(n, k, device=cuda)
+    a[torch.arange(m), torch.arange(m) % k] = (torch.arange(m, device=cuda) % 61 + 1).float()
+    b[torch.arange(n), (torch.arange(n) * 7) % k] = (torch.arange(n, device=cuda) % 53 + 1).float()
+    want = (a @ b.T).bfloat16()
+    a16, b16 = a.bfloat16(), b.bfloat16()
+    assert torch.equal(gemm(a16.T.contiguous(), b16, a_trans=True), want)
+    assert torch.equal(gemm(a16, b16.T.contiguous(), b_trans=True), want)
+    assert torch.equal(gemm(a16.T.contiguous(), b16.T.contiguous(), a_trans=True, b_trans=True), want)
+    # the reference's backward use: dgelu with a transposed weight (tests/gemm/test_gemm.py:88-91)
+    g = torch.Generator(device=cuda).manual_seed(2)
+    x = torch.randn(256, 128, device=cuda, generator=g).bfloat16()
+    w = torch.randn(512, 128, device=cuda, generator=g).bfloat16()
+    c0 = torch.randn(256, 512, device=cuda, generator=g).bfloat16()
+    post, pre = gemm(x, w, out=c0.clone(), accum=True, act="gelu", store_pre=True)
+    d = gemm(x, w.T.contiguous(), out=c0.clone(), act="dgelu", pre=pre, accum=True, b_trans=True)
+    assert torch.equal(d, gemm(x, w, out=c0.clone(), act="dgelu", pre=pre, accum=True))

@@ -26,6 +26,7 @@ constexpr int BK = 64;
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = BN * BK * 2;
+constexpr int CHUNK_BYTES = 64 * BK * 2;  // 64 rows x 64 K elements of a transposed operand
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 constexpr int THREADS = 192;
@@ -48,7 +49,7 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
 
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 void* __restrict__ out, int M, int N, int K, int group_m, int in_f16,
+                 void* __restrict__ out, int M, int N, int K, int group_m, int in_f16, int a_trans, int b_trans,
                  const __grid_constant__ Epilogue epi, int* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -104,8 +105,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
-          tma_load_2d(sa, &tmap_a, full_bar(stage), kb * BK, tc.m_blk * BM);
-          tma_load_2d(sa + A_BYTES, &tmap_b, full_bar(stage), kb * BK, tc.n_blk * BN);
+          // An operand stored [rows, K] arrives as one box of `rows` x 64 K elements (K-major tile).  A transposed
+          // operand, stored [K, rows], arrives as boxes of 64 K x 64 rows (128 bytes of rows per K line), one per
+          // 64 rows, 8 KiB apart: an MN-major tile.
+          if (a_trans) {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(sa + c * CHUNK_BYTES, &tmap_a, full_bar(stage), tc.m_blk * BM + 64 * c, kb * BK);
+          } else {
+            tma_load_2d(sa, &tmap_a, full_bar(stage), kb * BK, tc.m_blk * BM);
+          }
+          if (b_trans) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sa + A_BYTES + c * CHUNK_BYTES, &tmap_b, full_bar(stage), tc.n_blk * BN + 64 * c, kb * BK);
+          } else {
+            tma_load_2d(sa + A_BYTES, &tmap_b, full_bar(stage), kb * BK, tc.n_blk * BN);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -116,10 +132,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = in_f16 ? make_idesc(0, 0, 0, 0, BM, BN) : make_idesc(1, 1, 0, 0, BM, BN);
-      // descriptors of stage 0; a later stage only moves the 16-byte-granular start address field
-      const uint64_t a_desc0 = smem_desc_sw128(smem_base, 16, 1024);
-      const uint64_t b_desc0 = smem_desc_sw128(smem_base + A_BYTES, 16, 1024);
+      const uint32_t fmt = in_f16 ? 0 : 1;
+      const uint32_t idesc = make_idesc(fmt, fmt, a_trans ? 1 : 0, b_trans ? 1 : 0, BM, BN);
+      // descriptors of stage 0; a later stage only moves the 16-byte-granular start address field.
+      // K-major tile: 8-row groups 1024 bytes apart, 16 K elements = 32 bytes further along a row.
+      // MN-major tile: 64-row chunks 8 KiB apart (leading offset), groups of 8 K lines 1024 bytes apart,
+      // 16 K elements = 16 lines = 2048 bytes further on.
+      const uint64_t a_desc0 = smem_desc_sw128(smem_base, a_trans ? CHUNK_BYTES : 16, 1024);
+      const uint64_t b_desc0 = smem_desc_sw128(smem_base + A_BYTES, b_trans ? CHUNK_BYTES : 16, 1024);
+      const uint64_t a_kstep = a_trans ? 2048 / 16 : 32 / 16;
+      const uint64_t b_kstep = b_trans ? 2048 / 16 : 32 / 16;
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -141,8 +163,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint64_t b_desc = b_desc0 + step;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            // 16 bf16 = 32 bytes along K inside the 128-byte swizzle span
-            mma_f16_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+            mma_f16_ss(d_tmem, a_desc + a_kstep * k, b_desc + b_kstep * k, idesc, (kb | k) != 0);
           }
           tc_commit(empty_bar(stage));
           if (++stage == STAGES) {
@@ -207,20 +228,21 @@ extern "C" int wk_gemm_16bit(const wk_gemm16_args* g, void* stream) {
 
   const CUtensorMapDataType dt = g->f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap ta, tb;
-  {
-    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+  // [rows, K] operand: boxes of `tile_rows` x 64 K; transposed ([K, rows]): boxes of 64 K lines x 64 rows
+  auto encode_operand = [&](CUtensorMap* t, const void* ptr, int rows, int tile_rows, int trans) {
+    if (trans) {
+      const uint64_t dims[2] = {static_cast<uint64_t>(rows), static_cast<uint64_t>(k)};
+      const uint64_t strides[1] = {static_cast<uint64_t>(rows) * 2};
+      const uint32_t box[2] = {64, BK};
+      return encode_tmap(t, dt, 2, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    }
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(rows)};
     const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
-    const uint32_t box[2] = {BK, BM};
-    int r = encode_tmap(&ta, dt, 2, g->a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (r) return r;
-  }
-  {
-    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
-    const uint32_t box[2] = {BK, BN};
-    int r = encode_tmap(&tb, dt, 2, g->b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (r) return r;
-  }
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(tile_rows)};
+    return encode_tmap(t, dt, 2, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  };
+  if (int r = encode_operand(&ta, g->a, m, BM, g->a_trans)) return r;
+  if (int r = encode_operand(&tb, g->b, n, BN, g->b_trans)) return r;
   Epilogue e;
   e.scale_a = g->scale_a;
   e.scale_b = g->scale_b;
@@ -239,7 +261,7 @@ extern "C" int wk_gemm_16bit(const wk_gemm16_args* g, void* stream) {
   if (sms <= 0) return WK_E_CUDA;
   const int grid = num_tiles < sms ? num_tiles : sms;
   gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ta, tb, g->out, m, n, k, 8,
-                                                                                     g->f16, e, status);
+                                                                                     g->f16, g->a_trans, g->b_trans, e, status);
   return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
 }
 

@@ -45,6 +45,7 @@ class _Gemm16Args(ctypes.Structure):
         *_EPILOGUE_FIELDS,
         ("pre_out", ctypes.c_void_p), ("pre_in", ctypes.c_void_p),
         ("q_mx", ctypes.c_void_p), ("s_mx", ctypes.c_void_p),
+        ("a_trans", ctypes.c_int32), ("b_trans", ctypes.c_int32),
     ]
 
 
@@ -103,8 +104,8 @@ def make_gemm(
     """Prepare ``out = a @ b.T * scale_a * scale_b``.
 
     Args:
-        a: ``[M, K]`` bf16, fp16 or ``torch.float8_e4m3fn``, contiguous.
-        b: ``[N, K]`` with the dtype of ``a``, contiguous.
+        a: ``[M, K]`` bf16, fp16 or ``torch.float8_e4m3fn``, contiguous. ``[K, M]`` if ``a_trans``.
+        b: ``[N, K]`` with the dtype of ``a``, contiguous. ``[K, N]`` if ``b_trans``, so the product is ``a @ b``.
         out: Optional contiguous ``[M, N]`` bf16 output, 16-byte aligned. Allocated if ``None``.
         bk: K elements per pipeline stage in the reference; here only the divisibility rule ``K % bk == 0`` is
             kept. Defaults to 64 for bf16 and 128 for fp8.
@@ -120,7 +121,8 @@ def make_gemm(
         store_pre: Whether to also store the product before the activation. Needs ``act="gelu"``.
         pre: The pre-activation values the forward stored, ``[M, N]`` with the dtype of ``out``. Needed for
             ``act="dgelu"``.
-        a_trans, b_trans: Transposed operands; not implemented by this build (``NotImplementedError``).
+        a_trans: Whether ``a`` is stored ``[K, M]``. Needs bf16 or fp16 inputs.
+        b_trans: Whether ``b`` is stored ``[K, N]``. Same limits as ``a_trans``.
         accum: Whether to add the scaled product to the values ``out`` already holds, before the activation.
         a_scale_mx: ``[M, K / 32]`` uint8 ue8m0 scales of ``a``, one per row and block of 32 along K, as
             ``out_mx`` writes them. Needs fp8 inputs.
@@ -145,10 +147,8 @@ def make_gemm(
     _gemm_arch(a, fp8, act, accum, a_scale_mx is not None or b_scale_mx is not None, out_mx)
     if act not in _ACT:
         raise ValueError(f"act must be '', 'gelu' or 'dgelu', got {act!r}")
-    if a_trans or b_trans:
-        if fp8:
-            raise ValueError("transposed operands need bf16 or fp16 inputs")
-        raise NotImplementedError("warpy_kernels for SM100 has no transposed-operand gemm yet")
+    if (a_trans or b_trans) and fp8:
+        raise ValueError("transposed operands need bf16 or fp16 inputs")
     if store_pre and act != "gelu":
         raise ValueError("store_pre needs act='gelu'")
     odt = out_dtype if fp8 and out is None else out.dtype if out is not None else a.dtype
@@ -159,8 +159,8 @@ def make_gemm(
     bk = bk or (128 if fp8 else 64)
     if bn not in (128, 256):
         raise ValueError("bn must be 128 or 256")
-    m, k = a.shape
-    n, kb = b.shape
+    m, k = a.shape[::-1] if a_trans else a.shape
+    n, kb = b.shape[::-1] if b_trans else b.shape
     if kb != k:
         raise ValueError(f"inner dimensions differ: {k} vs {kb}")
     if not (a.is_contiguous() and b.is_contiguous()):
@@ -219,6 +219,7 @@ def make_gemm(
         args.a, args.b, args.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
         args.m, args.n, args.k = m, n, k
         args.f16 = int(a.dtype == torch.float16)
+        args.a_trans, args.b_trans = int(bool(a_trans)), int(bool(b_trans))
         fill_epilogue(args)
         keep = (a, b, scale_a, scale_b, pre_out, pre_in)
 
