@@ -210,6 +210,11 @@ typedef struct {
 
 int wk_attn_fwd_fp8(const wk_attn_fwd_args* args, void* stream);
 
+/* BF16 attention forward: q, k, v bf16 (element strides multiples of 8), the three descale
+ * pointers NULL, everything else as for wk_attn_fwd_fp8.  Replaces the same launch for 16-bit
+ * inputs (warpy_kernels/attn/fwd_api.py:383-390, kernel warpy_kernels/attn/fwd_base.py:374-416). */
+int wk_attn_fwd_bf16(const wk_attn_fwd_args* args, void* stream);
+
 /* FP8 attention backward.  Replaces the launches of warpy_kernels/attn/bwd_api.py:381-398
  * (BwdPrep warpy_kernels/attn/bwd_common.py:23-266, AttnBwdSm120 warpy_kernels/attn/bwd_sm120.py:38-1202,
  * BwdDqPost warpy_kernels/attn/bwd_common.py:307-403).

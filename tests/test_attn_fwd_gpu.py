@@ -144,7 +144,72 @@ def test_validation_errors(cuda):
         attn_fwd(q, kv, kv, q_descale=torch.ones(1, 2, device=cuda))
     with pytest.raises(ValueError):
         attn_fwd(q, kv, kv, seqused_k=torch.ones(1, device=cuda))
-    with pytest.raises(NotImplementedError):
-        attn_fwd(q.bfloat16(), kv.bfloat16(), kv.bfloat16())
+    with pytest.raises(ValueError):
+        attn_fwd(q.bfloat16(), kv.bfloat16(), kv.bfloat16(), q_descale=torch.ones(1, 1, device=cuda))  # bf16 has no descales
     with pytest.raises(ValueError):
         attn_fwd(q, kv, kv, out=torch.empty(1, 2, 128, 128, device=cuda))
+
+
+# ---- bf16 inputs ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_bf16_reference_shapes(cuda, shape, causal):
+    """The reference's ``fwd_bf16`` case (``tests/attn/test_fwd.py:117-144``): out rel-L2 and lse max-abs <= 1e-2."""
+    from warpy_kernels import attn_fwd
+
+    q, k, v = [x.bfloat16() for x in randn_qkv(*shape, device=cuda)]
+    out, lse, pmax = attn_fwd(q, k, v, causal=causal)
+    assert out.dtype == torch.bfloat16 and out.shape == q.shape
+    out_ref, lse_ref = R.attention_reference(q.float().cpu(), k.float().cpu(), v.float().cpu(), causal)
+    errs = fwd_errors(out, lse, out_ref, lse_ref, shape[3], shape[4], causal)
+    assert errs["out"] <= 1e-2 and errs["lse"] <= 1e-2 and errs["cos"] >= 0.999, errs
+    assert torch.equal(attn_fwd(q, k, v, causal=causal)[0], out), "repeated launches differ"
+
+
+def test_bf16_sink_and_late_peaks(cuda):
+    """A row reference fixed by the first tile must survive much larger scores later in the row, and a huge first
+    score (attention sink) with small ones after it."""
+    from warpy_kernels import attn_fwd
+
+    B, H, N, d = 1, 2, 1024, 128
+    g = torch.Generator(device=cuda).manual_seed(5)
+    q = torch.randn(B, H, N, d, device=cuda, generator=g)
+    k = torch.randn(B, H, N, d, device=cuda, generator=g)
+    v = torch.randn(B, H, N, d, device=cuda, generator=g)
+    for mode in ("late_peak", "sink"):
+        kk = k.clone()
+        if mode == "late_peak":
+            kk[:, :, 700:] *= 6.0  # logits grow by tens of bits after the first tile
+        else:
+            kk[:, :, 0] = q.mean(2) * 8.0  # key 0 dominates every row
+        qb, kb, vb = q.bfloat16(), kk.bfloat16(), v.bfloat16()
+        out, lse, _ = attn_fwd(qb, kb, vb, causal=False)
+        out_ref, lse_ref = R.attention_reference(qb.float().cpu(), kb.float().cpu(), vb.float().cpu(), False)
+        errs = fwd_errors(out, lse, out_ref, lse_ref, N, N, False)
+        assert errs["out"] <= 1e-2 and errs["lse"] <= 1e-2, (mode, errs)
+
+
+def test_bf16_layouts_and_options(cuda):
+    """``[B, N, H, d]`` views, GQA, ragged lengths, ``seqused_k``, natural-log lse, ``return_lse=False``, d = 64."""
+    from warpy_kernels import attn_fwd
+
+    B, Hq, Hkv, Nq, Nk, d = 2, 4, 2, 200, 333, 128
+    g = torch.Generator(device=cuda).manual_seed(9)
+    q = torch.randn(B, Nq, Hq, d, device=cuda, generator=g).bfloat16().transpose(1, 2)
+    k = torch.randn(B, Nk, Hkv, d, device=cuda, generator=g).bfloat16().transpose(1, 2)
+    v = torch.randn(B, Nk, Hkv, d, device=cuda, generator=g).bfloat16().transpose(1, 2)
+    out, lse, _ = attn_fwd(q, k, v, causal=True, lse_natural=True)
+    out_ref, lse_ref = R.attention_reference(q.float().cpu(), k.float().cpu(), v.float().cpu(), True)
+    errs = fwd_errors(out, lse / 0.6931471805599453, out_ref, lse_ref, Nq, Nk, True)
+    assert errs["out"] <= 1e-2 and errs["lse"] <= 1.5e-2, errs
+    out2, lse2, pmax2 = attn_fwd(q, k, v, causal=True, return_lse=False)
+    assert lse2 is None and pmax2 is None and torch.equal(out2, out)
+    used = torch.tensor([333, 100], dtype=torch.int32, device=cuda)
+    out3, lse3, _ = attn_fwd(q, k, v, causal=False, seqused_k=used)
+    ref3, _ = R.attention_reference(q[1:].float().cpu(), k[1:, :, :100].float().cpu(), v[1:, :, :100].float().cpu(), False)
+    assert R.rel_l2(out3[1:].float().cpu(), ref3) <= 1e-2
+    q64, k64, v64 = [x[..., :64].contiguous() for x in (q, k, v)]
+    out4, lse4, _ = attn_fwd(q64, k64, v64, causal=True)
+    ref4, lse_ref4 = R.attention_reference(q64.float().cpu(), k64.float().cpu(), v64.float().cpu(), True)
+    errs = fwd_errors(out4, lse4, ref4, lse_ref4, Nq, Nk, True)
+    assert out4.shape == q64.shape and errs["out"] <= 1e-2 and errs["lse"] <= 1e-2, errs

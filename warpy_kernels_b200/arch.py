@@ -21,7 +21,7 @@ _FEATURES = {
     "gemm_fp8": (100,),
     "gemm_mx": (100,),
     "gemm_mx_out": (100,),
-    "attn_fwd": (),
+    "attn_fwd": (100,),
     "attn_bwd": (),
     "attn_fwd_fp8": (100,),
     "attn_bwd_fp8": (100,),

@@ -101,7 +101,7 @@ def make_attn_fwd(
     ``launch()`` may not see later in-place changes to the inputs. Call ``make_attn_fwd`` again for new values.
 
     Args:
-        q: ``[B, Hq, Nq, d]`` ``torch.float8_e4m3fn``, ``d`` 64 or 128 (64 runs through the 128 kernels on
+        q: ``[B, Hq, Nq, d]`` ``torch.float8_e4m3fn`` or bf16, ``d`` 64 or 128 (64 runs through the 128 kernels on
             zero-padded copies). Any strides work if the last one is 1, such as a
             transposed ``[B, N, H, d]`` tensor. Inputs are copied if a stride or the base address is not a multiple
             of 16 bytes.
@@ -147,8 +147,11 @@ def make_attn_fwd(
     if not softmax_scale > 0:
         raise ValueError("softmax_scale must be positive")
     dev = q.device
-    ones = cached_tensor(("ones", dev, B, Hkv), lambda: torch.ones(B, Hkv, dtype=torch.float32, device=dev))
-    dq_, dk_, dv_ = [(x if x is not None else ones).float().contiguous() for x in (q_descale, k_descale, v_descale)]
+    if bf16:
+        dq_ = dk_ = dv_ = None
+    else:
+        ones = cached_tensor(("ones", dev, B, Hkv), lambda: torch.ones(B, Hkv, dtype=torch.float32, device=dev))
+        dq_, dk_, dv_ = [(x if x is not None else ones).float().contiguous() for x in (q_descale, k_descale, v_descale)]
 
     qv, kv, vv = (_pad_head_dim(x) for x in (q, k, v)) if d != KERNEL_D else (_kernel_view(x) for x in (q, k, v))
     if out is None:
@@ -183,7 +186,8 @@ def make_attn_fwd(
     args.q, args.k, args.v, args.out = qv.data_ptr(), kv.data_ptr(), vv.data_ptr(), out_k.data_ptr()
     args.lse = lse.data_ptr() if return_lse else None
     args.pmax = pmax.data_ptr() if return_lse else None
-    args.q_descale, args.k_descale, args.v_descale = dq_.data_ptr(), dk_.data_ptr(), dv_.data_ptr()
+    if not bf16:
+        args.q_descale, args.k_descale, args.v_descale = dq_.data_ptr(), dk_.data_ptr(), dv_.data_ptr()
     args.q_strides = (ctypes.c_int64 * 3)(*qv.stride()[:3])
     args.k_strides = (ctypes.c_int64 * 3)(*kv.stride()[:3])
     args.v_strides = (ctypes.c_int64 * 3)(*vv.stride()[:3])
@@ -195,10 +199,11 @@ def make_attn_fwd(
     args.softmax_scale = float(softmax_scale)
     keep = (qv, kv, vv, dq_, dk_, dv_, seq, out_k)  # the launch closure owns what the argument block points at
     lib = _lib.lib()
+    entry = lib.wk_attn_fwd_bf16 if bf16 else lib.wk_attn_fwd_fp8
 
     def launch():
         with torch.cuda.device(dev):
-            code = lib.wk_attn_fwd_fp8(ctypes.byref(args), _lib.stream_ptr(dev))
+            code = entry(ctypes.byref(args), _lib.stream_ptr(dev))
         _lib.check(code, "attn_fwd")
         if not out_direct:
             out.copy_(out_k[..., :d])

@@ -112,8 +112,8 @@ extern "C" {
 int wk_query(const char* feature) {
   if (!feature) return WK_E_ARG;
   static const char* const kYes[] = {"gemm",       "gemm_fp8",   "gemm_mx",      "gemm_mx_out", "gemm_gelu",
-                                     "gemm_dgelu", "gemm_accum", "attn_fwd_fp8", "attn_bwd_fp8"};
-  static const char* const kNo[] = {"attn_fwd", "attn_bwd"};
+                                     "gemm_dgelu", "gemm_accum", "attn_fwd_fp8", "attn_bwd_fp8", "attn_fwd"};
+  static const char* const kNo[] = {"attn_bwd"};
   for (const char* f : kYes)
     if (!strcmp(f, feature)) return 1;
   for (const char* f : kNo)
