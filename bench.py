@@ -146,6 +146,31 @@ def make_attn(dev, B, Hq, Hkv, N, d, causal, seed, backward=False):
                 check=lambda: None, tensors=(q8, k8, v8, dsq, dsk, dsv, out, lse))
 
 
+def make_attn_bf16(dev, B, Hq, Hkv, N, d, causal, seed):
+    """The attention forward on bf16 inputs (tcgen05 kind::f16): same shapes, no scales."""
+    import warpy_kernels as wk
+    from warpy_kernels.attn import make_attn_fwd
+
+    g = torch.Generator(device=dev).manual_seed(seed)
+    q, k, v = [torch.randn(B, h, N, d, device=dev, generator=g).bfloat16() for h in (Hq, Hkv, Hkv)]
+    flops = 4.0 * B * Hq * N * N * d * (0.5 if causal else 1.0)
+    launch, out, lse, pmax = make_attn_fwd(q, k, v, causal=causal)
+    hq, hk, hv = [x.cpu().pin_memory() for x in (q, k, v)]
+    dq, dk, dv = [torch.empty_like(x) for x in (q, k, v)]
+    hout = torch.empty(out.shape, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        o, _, _ = wk.attn_fwd(dq, dk, dv, causal=causal)
+        hout.copy_(o, non_blocking=True)
+
+    return dict(step=launch, e2e_step=e2e_step, work=flops, bound="tensor", dtype="bf16", launches=1,
+                h2d=2 * (hq.numel() + hk.numel() + hv.numel()), d2h=hout.numel() * 2,
+                resident_bytes=6 * q.numel() + out.numel() * 2, check=lambda: None, tensors=(q, k, v, out, lse))
+
+
 def make_attn_bwd(dev, B, Hq, Hkv, N, d, causal, seed):
     import warpy_kernels as wk
     from warpy_kernels.attn import make_attn_bwd as prepare
@@ -252,6 +277,8 @@ WORKLOADS = {
                      make=lambda dev: make_attn_bwd(dev, 4, 32, 32, 4096, 128, True, 0)),
     "attn_bwd_small": dict(desc="FP8 causal attention backward B2 H32 N4096 d128 (profiling size)", unit="TFLOP/s",
                            make=lambda dev: make_attn_bwd(dev, 2, 32, 32, 4096, 128, True, 0)),
+    "attn_fwd_bf16": dict(desc="BF16 causal attention forward B4 H32 N4096 d128", unit="TFLOP/s",
+                          make=lambda dev: make_attn_bf16(dev, 4, 32, 32, 4096, 128, True, 0)),
     "attn_gqa": dict(desc="FP8 GQA causal attention forward B1 Hq64 Hkv8 N32768 d128", unit="TFLOP/s",
                      make=lambda dev: make_attn(dev, 1, 64, 8, 32768, 128, True, 0)),
     "gemm_bf16": dict(desc="BF16 GEMM M=N=K=2048", unit="TFLOP/s",
