@@ -257,6 +257,13 @@ typedef struct {
 int64_t wk_attn_bwd_fp8_workspace_bytes(int B, int Hq, int Nq);
 int wk_attn_bwd_fp8(const wk_attn_bwd_args* args, void* stream);
 
+/* BF16 attention backward: q, k, v and dout bf16 read through TMA (16-byte aligned, element strides
+ * multiples of 8), the three descale pointers NULL, workspace of wk_attn_bwd_bf16_workspace_bytes
+ * (one 16-byte record per query row); everything else as for wk_attn_bwd_fp8.  Replaces the same
+ * launches for 16-bit inputs (warpy_kernels/attn/bwd_api.py:381-398, bwd_sm120.py:436-464). */
+int64_t wk_attn_bwd_bf16_workspace_bytes(int B, int Hq, int Nq);
+int wk_attn_bwd_bf16(const wk_attn_bwd_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -132,3 +132,52 @@ def test_validation_errors(cuda):
         attn_bwd(q, kv, kv, o, l[:, :, :64], l, o)
     with pytest.raises(ValueError):
         attn_bwd(q, kv.bfloat16(), kv, o, l, l, o)
+
+
+# ---- bf16 inputs ---------------------------------------------------------------------------------------------
+def _bf16_case(cuda, q, k, v, dout, causal):
+    """The reference's ``_bf16_grad`` (``tests/attn/test_grad.py:139-183``): rel-L2 <= 2e-2 for dq, dk, dv."""
+    from warpy_kernels import attn_bwd, attn_fwd
+
+    q, k, v, dout = [x.bfloat16() for x in (q, k, v, dout)]
+    out, lse, pmax = attn_fwd(q, k, v, causal=causal)
+    got = attn_bwd(q, k, v, out, lse, pmax, dout, causal=causal)
+    qf, kf, vf = [x.float().cpu().requires_grad_() for x in (q, k, v)]
+    out_ref, _ = R.attention_reference(qf, kf, vf, causal)
+    out_ref.backward(dout.float().cpu())
+    for name, g, w in zip(("dq", "dk", "dv"), got, (qf.grad, kf.grad, vf.grad)):
+        g = g.float().cpu()
+        assert g.shape == w.shape and not torch.isnan(g).any().item(), name
+        assert R.rel_l2(g, w) <= 2e-2, (name, R.rel_l2(g, w))
+        assert R.cosine(g, w) >= 0.995, (name, R.cosine(g, w))
+    return got
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_bf16_reference_shapes(cuda, shape, causal):
+    q, k, v = randn_qkv(*shape, device=cuda)
+    dout = torch.randn(q.shape, device=cuda, generator=torch.Generator(device=cuda).manual_seed(7))
+    _bf16_case(cuda, q, k, v, dout, causal)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_bf16_hard_inputs_and_repeat(cuda, causal):
+    """Peaky softmax and log-normal dO row norms (``grad_bf16_hard``); a second run gives the same bits."""
+    from warpy_kernels import attn_bwd, attn_fwd
+
+    q, k, v, dout = hard_inputs(1, 4, 2, 640, 640, 128, device=cuda)
+    first = _bf16_case(cuda, q, k, v, dout, causal)
+    qb, kb, vb, db = [x.bfloat16() for x in (q, k, v, dout)]
+    out, lse, pmax = attn_fwd(qb, kb, vb, causal=causal)
+    again = attn_bwd(qb, kb, vb, out, lse, pmax, db, causal=causal)
+    for a, b in zip(first, again):
+        assert torch.equal(a, b)
+
+
+def test_bf16_strided_views(cuda):
+    """``[B, N, H, d]`` storage for q, k, v and dout."""
+    B, Hq, Hkv, Nq, Nk, d = 2, 4, 2, 200, 333, 128
+    g = torch.Generator(device=cuda).manual_seed(11)
+    mk = lambda n, h: torch.randn(B, n, h, d, device=cuda, generator=g).transpose(1, 2)
+    _bf16_case(cuda, mk(Nq, Hq), mk(Nk, Hkv), mk(Nk, Hkv), mk(Nq, Hq), True)

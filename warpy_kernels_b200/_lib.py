@@ -29,6 +29,8 @@ SIGNATURES = {
     "wk_attn_fwd_bf16": (_i32, [_ptr, _ptr]),
     "wk_attn_bwd_fp8_workspace_bytes": (_i64, [_i32, _i32, _i32]),
     "wk_attn_bwd_fp8": (_i32, [_ptr, _ptr]),
+    "wk_attn_bwd_bf16_workspace_bytes": (_i64, [_i32, _i32, _i32]),
+    "wk_attn_bwd_bf16": (_i32, [_ptr, _ptr]),
     "wk_gemm_mxfp8_workspace_bytes": (_i64, [_i32, _i32, _i32]),
     "wk_gemm_mxfp8": (_i32, [_ptr, _ptr]),
     "wk_gemm_mxfp8_noalloc": (_i32, [_ptr, _ptr]),

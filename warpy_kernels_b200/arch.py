@@ -22,7 +22,7 @@ _FEATURES = {
     "gemm_mx": (100,),
     "gemm_mx_out": (100,),
     "attn_fwd": (100,),
-    "attn_bwd": (),
+    "attn_bwd": (100,),
     "attn_fwd_fp8": (100,),
     "attn_bwd_fp8": (100,),
 }

@@ -116,14 +116,19 @@ def make_attn_bwd(
     if not softmax_scale > 0:
         raise ValueError("softmax_scale must be positive")
     dev = q.device
-    ones = cached_tensor(("ones", dev, B, Hkv), lambda: torch.ones(B, Hkv, dtype=torch.float32, device=dev))
-    dq_, dk_, dv_ = [(x if x is not None else ones).float().contiguous() for x in (q_descale, k_descale, v_descale)]
+    if bf16:
+        dq_ = dk_ = dv_ = None
+    else:
+        ones = cached_tensor(("ones", dev, B, Hkv), lambda: torch.ones(B, Hkv, dtype=torch.float32, device=dev))
+        dq_, dk_, dv_ = [(x if x is not None else ones).float().contiguous() for x in (q_descale, k_descale, v_descale)]
     if d != KERNEL_D:
         # head dimension 64: the 128 kernels on zero-padded copies; the extra gradient columns are dropped
         qv, kv, vv, ov, dov = (_pad_head_dim(x) for x in (q, k, v, out, dout))
     else:
         qv, kv, vv = _kernel_view(q), _kernel_view(k), _kernel_view(v)
-        ov, dov = _bf16_view(out), _bf16_view(dout)
+        ov = _bf16_view(out)
+        # the bf16 kernels read dout through TMA like q: 16-byte aligned base and strides
+        dov = _kernel_view(dout if dout.dtype == torch.bfloat16 else dout.to(torch.bfloat16)) if bf16 else _bf16_view(dout)
     lsev = lse.float()
     if lsev.stride(2) != 1:
         lsev = lsev.contiguous()
@@ -131,13 +136,14 @@ def make_attn_bwd(
     dk = torch.empty(B, Hkv, Nk, KERNEL_D, dtype=torch.bfloat16, device=dev)
     dv = torch.empty(B, Hkv, Nk, KERNEL_D, dtype=torch.bfloat16, device=dev)
     lib = _lib.lib()
-    ws_bytes = lib.wk_attn_bwd_fp8_workspace_bytes(B, Hq, Nq)
+    ws_bytes = (lib.wk_attn_bwd_bf16_workspace_bytes if bf16 else lib.wk_attn_bwd_fp8_workspace_bytes)(B, Hq, Nq)
     workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
 
     args = _BwdArgs()
     args.q, args.k, args.v = qv.data_ptr(), kv.data_ptr(), vv.data_ptr()
     args.out, args.dout, args.lse = ov.data_ptr(), dov.data_ptr(), lsev.data_ptr()
-    args.q_descale, args.k_descale, args.v_descale = dq_.data_ptr(), dk_.data_ptr(), dv_.data_ptr()
+    if not bf16:
+        args.q_descale, args.k_descale, args.v_descale = dq_.data_ptr(), dk_.data_ptr(), dv_.data_ptr()
     args.dq, args.dk, args.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     args.workspace, args.workspace_bytes = workspace.data_ptr(), ws_bytes
     args.q_strides = (ctypes.c_int64 * 3)(*qv.stride()[:3])
@@ -150,9 +156,11 @@ def make_attn_bwd(
     args.causal, args.softmax_scale = int(bool(causal)), float(softmax_scale)
     keep = (qv, kv, vv, ov, dov, lsev, dq_, dk_, dv_, workspace)
 
+    entry = lib.wk_attn_bwd_bf16 if bf16 else lib.wk_attn_bwd_fp8
+
     def launch():
         with torch.cuda.device(dev):
-            code = lib.wk_attn_bwd_fp8(ctypes.byref(args), _lib.stream_ptr(dev))
+            code = entry(ctypes.byref(args), _lib.stream_ptr(dev))
         _lib.check(code, "attn_bwd")
         return keep
 
