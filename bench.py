@@ -203,6 +203,31 @@ def make_attn_bwd(dev, B, Hq, Hkv, N, d, causal, seed):
                 h2d=hdo.numel() * 2, d2h=sum(h.numel() * 2 for h in hg), tensors=(q8, k8, v8, out, lse, dout))
 
 
+def make_attn_bwd_bf16(dev, B, Hq, Hkv, N, d, causal, seed):
+    """The attention backward on bf16 inputs (tcgen05 kind::f16)."""
+    import warpy_kernels as wk
+    from warpy_kernels.attn import make_attn_bwd as prepare
+
+    g = torch.Generator(device=dev).manual_seed(seed)
+    q, k, v = [torch.randn(B, h, N, d, device=dev, generator=g).bfloat16() for h in (Hq, Hkv, Hkv)]
+    dout = torch.randn(B, Hq, N, d, device=dev, generator=torch.Generator(device=dev).manual_seed(7)).bfloat16()
+    out, lse, pmax = wk.attn_fwd(q, k, v, causal=causal)
+    launch, finish = prepare(q, k, v, out, lse, pmax, dout, causal=causal)
+    flops = 10.0 * B * Hq * N * N * d * (0.5 if causal else 1.0)
+    hdo = dout.cpu().pin_memory()
+    ddo = torch.empty_like(dout)
+    hg = [torch.empty(x.shape, dtype=torch.bfloat16).pin_memory() for x in (q, k, v)]
+
+    def e2e_step():
+        ddo.copy_(hdo, non_blocking=True)
+        grads = wk.attn_bwd(q, k, v, out, lse, pmax, ddo, causal=causal)
+        for h_, g_ in zip(hg, grads):
+            h_.copy_(g_, non_blocking=True)
+
+    return dict(step=launch, e2e_step=e2e_step, work=flops, bound="tensor", dtype="bf16", launches=3,
+                h2d=hdo.numel() * 2, d2h=sum(h.numel() * 2 for h in hg), tensors=(q, k, v, out, lse, dout))
+
+
 def make_gemm_bf16(dev, m, n, k, seed):
     import warpy_kernels as wk
 
@@ -279,6 +304,8 @@ WORKLOADS = {
                            make=lambda dev: make_attn_bwd(dev, 2, 32, 32, 4096, 128, True, 0)),
     "attn_fwd_bf16": dict(desc="BF16 causal attention forward B4 H32 N4096 d128", unit="TFLOP/s",
                           make=lambda dev: make_attn_bf16(dev, 4, 32, 32, 4096, 128, True, 0)),
+    "attn_bwd_bf16": dict(desc="BF16 causal attention backward B4 H32 N4096 d128", unit="TFLOP/s",
+                          make=lambda dev: make_attn_bwd_bf16(dev, 4, 32, 32, 4096, 128, True, 0)),
     "attn_gqa": dict(desc="FP8 GQA causal attention forward B1 Hq64 Hkv8 N32768 d128", unit="TFLOP/s",
                      make=lambda dev: make_attn(dev, 1, 64, 8, 32768, 128, True, 0)),
     "gemm_bf16": dict(desc="BF16 GEMM M=N=K=2048", unit="TFLOP/s",
