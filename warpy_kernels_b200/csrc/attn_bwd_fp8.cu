@@ -40,9 +40,8 @@ constexpr int BN = 128;  // keys per tile
 constexpr int D = 128;
 constexpr int TILE_BYTES = 128 * 128;
 constexpr int SF_BYTES = 512;
-constexpr int THREADS = 320;          // TMA warp, MMA warp, 8 element-wise warps (two threads per row)
-constexpr int ELEMWISE_THREADS = 256;
-constexpr int HALF_THREADS = 128;     // the element-wise threads of one 64-column half of a tile
+constexpr int THREADS = 576;          // TMA warp, MMA warp, 16 element-wise warps (four threads per row)
+constexpr int HALF_THREADS = 256;     // the element-wise threads of one 64-column half of a tile: two per row
 constexpr int HALF_COLS = 64;
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -209,7 +208,8 @@ constexpr int A_SMEM_NEED = 2 * TILE_BYTES + A_STAGES * A_STAGE_BYTES + 3 * SF_B
 constexpr int A_SMEM_BYTES = A_SMEM_NEED > 120 * 1024 ? A_SMEM_NEED : 120 * 1024;
 constexpr int A_ST_COL = 0, A_DPT_COL = 128, A_DV_COL = 256, A_DK_COL = 384;
 // scale-factor columns inside the consumed S^T columns; the two threads of a row own 4 columns each
-constexpr int A_SF_P = 16, A_SF_UNIT = 20, A_SF_DS = 24;
+// Inside the 32 S^T columns of a block, once its thread has read them: codes in 0..7, then the scale words
+constexpr int A_SF_P = 8, A_SF_UNIT = 12, A_SF_DS = 16;
 
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -325,16 +325,18 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       auto ts_half = [&](int it, int h) {
         const uint64_t q_desc = q_desc_of(it);
         const uint64_t do_desc = q_desc + (TILE_BYTES >> 4);
-        const uint32_t hb = st_tmem + HALF_COLS * h;
+        // block k of the half keeps its codes and scale words inside its own 32 columns
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
-          mma_mxf8_ts(tmem_base + A_DV_COL, hb + 8 * k, do_desc + 256 * (2 * h + k), make_idesc_mx_major(BN, D, k, 0, 0, 1),
-                      hb + A_SF_P, hb + A_SF_UNIT, (it | h | k) != 0);
+          const uint32_t bb = st_tmem + HALF_COLS * h + 32 * k;
+          mma_mxf8_ts(tmem_base + A_DV_COL, bb, do_desc + 256 * (2 * h + k), make_idesc_mx_major(BN, D, 0, 0, 0, 1),
+                      bb + A_SF_P, bb + A_SF_UNIT, (it | h | k) != 0);
         }
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
-          mma_mxf8_ts(tmem_base + A_DK_COL, dpt_tmem + HALF_COLS * h + 8 * k, q_desc + 256 * (2 * h + k),
-                      make_idesc_mx_major(BN, D, k, 0, 0, 1), hb + A_SF_DS, hb + A_SF_UNIT, (it | h | k) != 0);
+          const uint32_t bb = st_tmem + HALF_COLS * h + 32 * k;
+          mma_mxf8_ts(tmem_base + A_DK_COL, dpt_tmem + HALF_COLS * h + 32 * k, q_desc + 256 * (2 * h + k),
+                      make_idesc_mx_major(BN, D, 0, 0, 0, 1), bb + A_SF_DS, bb + A_SF_UNIT, (it | h | k) != 0);
         }
       };
       ok = ok && mbar_wait(q_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD);
@@ -365,13 +367,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     __syncwarp();
   } else {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;  // which 64 of the tile's 128 columns this thread handles
+    const int c = (warp - 2) >> 2;   // which block of 32 of the tile's 128 columns this thread handles
+    const int half = c >> 1;         // the half the block is handed over with
     const int r = quad * 32 + lane;  // key row of the tile == TMEM lane
     const int key = n0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    // this thread's half of the tile: scores in columns [64 half, 64 half + 64) of both buffers
-    const uint32_t st_tmem = tmem_base + lane_addr + A_ST_COL + HALF_COLS * half;
-    const uint32_t dpt_tmem = tmem_base + lane_addr + A_DPT_COL + HALF_COLS * half;
+    // this thread's block: scores in columns [32 c, 32 c + 32) of both buffers
+    const uint32_t st_tmem = tmem_base + lane_addr + A_ST_COL + 32 * c;
+    const uint32_t dpt_tmem = tmem_base + lane_addr + A_DPT_COL + 32 * c;
     const int sc = b * p.Hkv + hkv;
     const float sq = p.q_descale[sc], sk = p.k_descale[sc];
     const float beta = p.softmax_scale * sq * sk * LOG2E;
@@ -392,13 +395,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       const int first_col = key >= p.Nk ? BM : (p.causal ? max(0, key - shift - m0) : 0);
       // uniform over the CTA: does this (key block, query tile) pair contain any masked score?
       const bool tile_masked = (n0 + BN > p.Nk) || (p.causal && n0 + BN - 1 > m0 + shift);
-      uint32_t sf_p = 0, sf_d = 0;
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = 2 * half + cc;  // block of 32 queries within the tile
+      uint32_t sf_p, sf_d;
+      {
         uint32_t sraw[32], draw[32];
-        tmem_ld32(st_tmem + cc * 32, sraw);
-        tmem_ld32(dpt_tmem + cc * 32, draw);
+        tmem_ld32(st_tmem, sraw);
+        tmem_ld32(dpt_tmem, draw);
         tc_wait_ld();
         uint64_t pt[16], ds[16];  // (P g)^T and dS^T of this key for 32 queries, as packed pairs
         const uint64_t beta2 = pack_f32x2(beta, beta);
@@ -431,11 +432,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         float inv_p, inv_d;
         const uint32_t bp = block_scale(max_bits_nonneg(pt), inv_p);  // P >= 0 and g > 0
         const uint32_t bd = block_scale(absmax_bits(ds), inv_d);
-        // the codes go to the first columns of the half, which block 0's scores have left
-        quantize_block_to_tmem(pt, st_tmem + cc * 8, inv_p);
-        quantize_block_to_tmem(ds, dpt_tmem + cc * 8, inv_d);
-        sf_p |= bp << (8 * cc);
-        sf_d |= bd << (8 * cc);
+        // the codes go to the first columns of the block, which its scores have just left
+        quantize_block_to_tmem(pt, st_tmem, inv_p);
+        quantize_block_to_tmem(ds, dpt_tmem, inv_d);
+        sf_p = bp;
+        sf_d = bd;
       }
       // scale factors straight into TMEM: the MMA reads the scale of row r from lane r, column r / 32
       tmem_st1(st_tmem + A_SF_P + quad, sf_p);
@@ -457,7 +458,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         __nv_bfloat16* dst_row = (which == 0 ? p.dv : p.dk) + row_off;
         const float scale = which == 0 ? 1.f : dk_scale;
 #pragma unroll 1
-        for (int c = 2 * half; c < 2 * half + 2; ++c) {
+        {
           uint32_t v[32];
           if (n_iter > 0) {  // uniform: TMEM loads are warp-wide
             tmem_ld32(src + c * 32, v);
@@ -499,7 +500,7 @@ constexpr int B_STAGE_BYTES = 2 * TILE_BYTES;  // K tile, V tile
 constexpr int B_SMEM_NEED = 2 * TILE_BYTES + B_STAGES * B_STAGE_BYTES + 2 * SF_BYTES + 1024 + 256;
 constexpr int B_SMEM_BYTES = B_SMEM_NEED > 120 * 1024 ? B_SMEM_NEED : 120 * 1024;
 constexpr int B_S_COL = 0, B_DP_COL = 128, B_DQ_COL = 256;
-constexpr int B_SF_DS = 16, B_SF_UNIT = 20;
+constexpr int B_SF_DS = 8, B_SF_UNIT = 12;
 
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -604,11 +605,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       // dQ += dS K over the same 64 keys: A = dS codes in the dP columns, B = the K tile read MN-major
       auto ts_half = [&](int j, int h) {
         const uint64_t k_desc = k_desc_of(j);
-        const uint32_t hb = s_tmem + HALF_COLS * h;
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
-          mma_mxf8_ts(tmem_base + B_DQ_COL, dp_tmem + HALF_COLS * h + 8 * k, k_desc + 256 * (2 * h + k),
-                      make_idesc_mx_major(BM, D, k, 0, 0, 1), hb + B_SF_DS, hb + B_SF_UNIT, (j | h | k) != 0);
+          const uint32_t bb = s_tmem + HALF_COLS * h + 32 * k;  // the block's scale words sit in its own S columns
+          mma_mxf8_ts(tmem_base + B_DQ_COL, dp_tmem + HALF_COLS * h + 32 * k, k_desc + 256 * (2 * h + k),
+                      make_idesc_mx_major(BM, D, 0, 0, 0, 1), bb + B_SF_DS, bb + B_SF_UNIT, (j | h | k) != 0);
         }
       };
       ok = ok && mbar_wait(kv_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD);
@@ -639,13 +640,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     __syncwarp();
   } else {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;  // which 64 of the tile's 128 columns this thread handles
+    const int c = (warp - 2) >> 2;  // which block of 32 of the tile's 128 columns this thread handles
+    const int half = c >> 1;        // the half the block is handed over with
     const int r = quad * 32 + lane;
     const int row = m0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    // this thread's half of the tile: scores in columns [64 half, 64 half + 64) of both buffers
-    const uint32_t s_tmem = tmem_base + lane_addr + B_S_COL + HALF_COLS * half;
-    const uint32_t dp_tmem = tmem_base + lane_addr + B_DP_COL + HALF_COLS * half;
+    // this thread's block: scores in columns [32 c, 32 c + 32) of both buffers
+    const uint32_t s_tmem = tmem_base + lane_addr + B_S_COL + 32 * c;
+    const uint32_t dp_tmem = tmem_base + lane_addr + B_DP_COL + 32 * c;
     const int sc = b * p.Hkv + hkv;
     const float sq = p.q_descale[sc], sk = p.k_descale[sc];
     const float beta = p.softmax_scale * sq * sk * LOG2E;
@@ -663,13 +665,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const int limit = row_limit - j * BN;  // columns > limit are masked
       // uniform over the CTA: does this tile contain any masked score?
       const bool tile_masked = (j * BN + BN > p.Nk) || (p.causal && j * BN + BN - 1 > m0 + shift);
-      uint32_t sf_d = 0;
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = 2 * half + cc;  // block of 32 keys within the tile
+      uint32_t sf_d;
+      {
         uint32_t sraw[32], draw[32];
-        tmem_ld32(s_tmem + cc * 32, sraw);
-        tmem_ld32(dp_tmem + cc * 32, draw);
+        tmem_ld32(s_tmem, sraw);
+        tmem_ld32(dp_tmem, draw);
         tc_wait_ld();
         uint64_t ds[16];  // dS of this query for 32 keys, as packed pairs
         const uint64_t beta2 = pack_f32x2(beta, beta), nl2 = pack_f32x2(neg_l, neg_l), z2 = pack_f32x2(gsv, gsv),
@@ -689,8 +689,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
         float inv_d;
         const uint32_t bd = block_scale(absmax_bits(ds), inv_d);
-        quantize_block_to_tmem(ds, dp_tmem + cc * 8, inv_d);
-        sf_d |= bd << (8 * cc);
+        quantize_block_to_tmem(ds, dp_tmem, inv_d);
+        sf_d = bd;
       }
       tmem_st1(s_tmem + B_SF_DS + quad, sf_d);
       tmem_st4(s_tmem + B_SF_UNIT, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
@@ -705,7 +705,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const float scale = p.softmax_scale * sk;
       __nv_bfloat16* dst_row = p.dq + ((static_cast<int64_t>(b) * p.Hq + hq) * p.Nq + row) * D;
 #pragma unroll 1
-      for (int c = 2 * half; c < 2 * half + 2; ++c) {
+      {
         uint32_t v[32];
         if (n_tiles > 0) {
           tmem_ld32(tmem_base + lane_addr + B_DQ_COL + c * 32, v);
