@@ -7,7 +7,7 @@
 // kernels and the same pipeline as the FP8 backward (attn_bwd_fp8.cu), with tcgen05.mma kind::f16 and P^T, dS^T
 // rounded to bf16 instead of MXFP8:
 //
-//  1. attn_bwd_prep_kernel: per query row D = sum(dO . O) and the row record (-L, 1, 1, -D).
+//  1. attn_bwd_prep_kernel: per query row D = sum(dO . O) and the row record (-L, -D).
 //  2. attn_bwd_dkdv_kernel: CTA = 128 keys of one (batch, kv head), K and V resident in shared memory, loop over
 //     the group's query heads and query tiles; S^T = K Q^T and dP^T = V dO^T into TMEM, threads turn them into
 //     bf16 P^T and dS^T back in TMEM, dV += P^T dO and dK += dS^T Q (A from TMEM, B = the same Q / dO tiles read
@@ -33,9 +33,8 @@ constexpr int CHUNK = 64;                        // head-dim elements per 128-by
 constexpr int CHUNK_BYTES = 128 * CHUNK * 2;     // 16 KiB: 128 rows x 128 bytes
 constexpr int TILE_BYTES = 2 * CHUNK_BYTES;      // 32 KiB: 128 rows x 256 bytes
 constexpr int SF_BYTES = 512;
-constexpr int THREADS = 320;          // TMA warp, MMA warp, 8 element-wise warps (two threads per row)
-constexpr int ELEMWISE_THREADS = 256;
-constexpr int HALF_THREADS = 128;     // the element-wise threads of one 64-column half of a tile
+constexpr int THREADS = 576;          // TMA warp, MMA warp, 16 element-wise warps (four threads per row)
+constexpr int HALF_THREADS = 256;     // the element-wise threads of one 64-column half of a tile: two per row
 constexpr int HALF_COLS = 64;
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -47,7 +46,7 @@ struct PrepParams {
   const __nv_bfloat16* dout;  // [B,Hq,Nq,D] with element strides
   const __nv_bfloat16* out;
   const float* lse;           // [B,Hq,*] base 2
-  float* qstat;               // [B,Hq,Nq_pad/128][4][128]: per 128 rows the arrays -L, 1, 1, -D
+  float* qstat;               // [B,Hq,Nq_pad/128][2][128]: per 128 rows the arrays -L and -D
   int64_t do_sb, do_sh, do_sn;
   int64_t o_sb, o_sh, o_sn;
   int64_t lse_sb, lse_sh;
@@ -63,11 +62,11 @@ __global__ void __launch_bounds__(256) attn_bwd_bf16_prep_kernel(const PrepParam
   const int i = warp % p.nq_pad;
   const int h = (warp / p.nq_pad) % p.Hq;
   const int b = warp / (p.nq_pad * p.Hq);
-  // the four values of row i sit 128 floats apart inside the row's tile of 128
-  float* stat = p.qstat + ((static_cast<int64_t>(b) * p.Hq + h) * p.nq_pad + (i & ~127)) * 4 + (i & 127);
+  // the two values of row i sit 128 floats apart inside the row's tile of 128
+  float* stat = p.qstat + ((static_cast<int64_t>(b) * p.Hq + h) * p.nq_pad + (i & ~127)) * 2 + (i & 127);
   if (i >= p.Nq) {
     // padding rows: lse = +inf makes every probability zero
-    if (lane < 4) stat[lane * 128] = lane == 0 ? -INFINITY : 0.f;
+    if (lane < 2) stat[lane * 128] = lane == 0 ? -INFINITY : 0.f;
     return;
   }
   const __nv_bfloat16* dsrc = p.dout + b * p.do_sb + h * p.do_sh + static_cast<int64_t>(i) * p.do_sn + lane * 4;
@@ -82,15 +81,20 @@ __global__ void __launch_bounds__(256) attn_bwd_bf16_prep_kernel(const PrepParam
   for (int off = 16; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
   if (lane == 0) {
     stat[0] = -p.lse[b * p.lse_sb + h * p.lse_sh + i];
-    stat[128] = 1.f;
-    stat[256] = 1.f;
-    stat[384] = -dsum;
+    stat[128] = -dsum;
   }
 }
 
 // ---------------------------------------------------------------------------
 // helpers shared by the two main kernels
 // ---------------------------------------------------------------------------
+// Four consecutive floats from shared memory (the row records: every thread reads the same address, a broadcast).
+__device__ __forceinline__ float4 lds_f4(uint32_t saddr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
+  return v;
+}
+
 // The element-wise code keeps a block of 32 values as 16 packed fp32 pairs; they go to TMEM as 16 bf16 pairs.
 __device__ __forceinline__ void store_block_bf16(const uint64_t (&x)[16], uint32_t taddr) {
   uint32_t lo[8], hi[8];
@@ -107,7 +111,7 @@ __device__ __forceinline__ void store_block_bf16(const uint64_t (&x)[16], uint32
 }
 
 struct BwdParams {
-  const float* qstat;    // [B,Hq,nq_pad/128][4][128]: -L, g, g*sv, -D of 128 rows
+  const float* qstat;    // [B,Hq,nq_pad/128][2][128]: -L and -D of 128 rows
   __nv_bfloat16* dq;     // [B,Hq,Nq,D] contiguous
   __nv_bfloat16* dk;     // [B,Hkv,Nk,D] contiguous
   __nv_bfloat16* dv;
@@ -121,7 +125,7 @@ struct BwdParams {
 // 2. dK / dV
 // ---------------------------------------------------------------------------
 constexpr int A_STAGES = 2;
-constexpr int A_STAT_BYTES = BM * 16;
+constexpr int A_STAT_BYTES = BM * 8;
 constexpr int A_STAGE_BYTES = 2 * TILE_BYTES + A_STAT_BYTES;
 // Requested size is padded past half an SM's shared memory: each CTA allocates all 512 TMEM columns, so a second
 // resident CTA could only spin in tcgen05.alloc.
@@ -145,7 +149,6 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   auto p_full = [&](int h) { return bar_base + 8u * (3 + 2 * A_STAGES + h); };
   const uint32_t acc_full = bar_base + 8u * (5 + 2 * A_STAGES);
   const uint32_t tmem_slot = acc_full + 8;
-  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));  // generic pointer to the aligned base
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -207,7 +210,7 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           tma_load_4d(base + c * CHUNK_BYTES, &tmap_q, q_full(s), c * CHUNK, m0, hq, b);
           tma_load_4d(base + TILE_BYTES + c * CHUNK_BYTES, &tmap_do, q_full(s), c * CHUNK, m0, hq, b);
         }
-        bulk_load(base + 2 * TILE_BYTES, p.qstat + ((static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0) * 4,
+        bulk_load(base + 2 * TILE_BYTES, p.qstat + ((static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0) * 2,
                   A_STAT_BYTES, q_full(s));
       }
     }
@@ -252,13 +255,14 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         const uint64_t do_desc = q_desc + (TILE_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          mma_f16_ts(tmem_base + A_DV_COL, st_tmem + HALF_COLS * h + 8 * k, do_desc + 128 * (4 * h + k), idesc_ts,
-                     (it | h | k) != 0);
+          // 16 queries = 8 columns; a block of 32 queries keeps its pairs at the start of its own 32 columns
+          mma_f16_ts(tmem_base + A_DV_COL, st_tmem + HALF_COLS * h + 32 * (k >> 1) + 8 * (k & 1),
+                     do_desc + 128 * (4 * h + k), idesc_ts, (it | h | k) != 0);
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          mma_f16_ts(tmem_base + A_DK_COL, dpt_tmem + HALF_COLS * h + 8 * k, q_desc + 128 * (4 * h + k), idesc_ts,
-                     (it | h | k) != 0);
+          mma_f16_ts(tmem_base + A_DK_COL, dpt_tmem + HALF_COLS * h + 32 * (k >> 1) + 8 * (k & 1),
+                     q_desc + 128 * (4 * h + k), idesc_ts, (it | h | k) != 0);
         }
       };
       ok = ok && mbar_wait(q_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD);
@@ -289,13 +293,14 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
     __syncwarp();
   } else {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;  // which 64 of the tile's 128 columns this thread handles
+    const int c = (warp - 2) >> 2;   // which block of 32 of the tile's 128 columns this thread handles
+    const int half = c >> 1;         // the half the block is handed over with
     const int r = quad * 32 + lane;  // key row of the tile == TMEM lane
     const int key = n0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    // this thread's half of the tile: scores in columns [64 half, 64 half + 64) of both buffers
-    const uint32_t st_tmem = tmem_base + lane_addr + A_ST_COL + HALF_COLS * half;
-    const uint32_t dpt_tmem = tmem_base + lane_addr + A_DPT_COL + HALF_COLS * half;
+    // this thread's block: scores in columns [32 c, 32 c + 32) of both buffers
+    const uint32_t st_tmem = tmem_base + lane_addr + A_ST_COL + 32 * c;
+    const uint32_t dpt_tmem = tmem_base + lane_addr + A_DPT_COL + 32 * c;
     const float beta = p.softmax_scale * LOG2E;
     bool ok = true;
 
@@ -307,51 +312,55 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         break;
       }
       tc_fence_after();
-      // the tile's row records: arrays -L, g, g*sv, -D of 128 queries each, read four queries at a time
-      const float4* stat = reinterpret_cast<const float4*>(smem_gen + (stage_smem - smem_base) + s * A_STAGE_BYTES +
-                                                           2 * TILE_BYTES);
+      // the tile's row records: arrays -L and -D of 128 queries each, read four queries at a time
+      const uint32_t stat = stage_smem + s * A_STAGE_BYTES + 2 * TILE_BYTES;
       // query column c is visible to this key iff key < Nk and (not causal or key <= m0 + c + shift)
       const int first_col = key >= p.Nk ? BM : (p.causal ? max(0, key - shift - m0) : 0);
       // uniform over the CTA: does this (key block, query tile) pair contain any masked score?
       const bool tile_masked = (n0 + BN > p.Nk) || (p.causal && n0 + BN - 1 > m0 + shift);
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = 2 * half + cc;  // block of 32 queries within the tile
+      {
         uint32_t sraw[32], draw[32];
-        tmem_ld32(st_tmem + cc * 32, sraw);
-        tmem_ld32(dpt_tmem + cc * 32, draw);
+        tmem_ld32(st_tmem, sraw);
+        tmem_ld32(dpt_tmem, draw);
         tc_wait_ld();
-        uint64_t pt[16], ds[16];  // (P g)^T and dS^T of this key for 32 queries, as packed pairs
         const uint64_t beta2 = pack_f32x2(beta, beta);
+        // 16 queries at a time: their bf16 pairs go to the first columns of the block, which its scores have left
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          // the same addresses for every thread: shared-memory broadcasts
-          const float4 nl = stat[c * 8 + i], g4 = stat[32 + c * 8 + i], z4 = stat[64 + c * 8 + i],
-                       nd = stat[96 + c * 8 + i];
-          float x0, x1, x2, x3;
-          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[4 * i]), __uint_as_float(sraw[4 * i + 1])), beta2,
-                                 pack_f32x2(nl.x, nl.y)), x0, x1);
-          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[4 * i + 2]), __uint_as_float(sraw[4 * i + 3])), beta2,
-                                 pack_f32x2(nl.z, nl.w)), x2, x3);
-          float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
-          if (tile_masked) {
-            if (c * 32 + 4 * i + 0 < first_col) p0 = 0.f;
-            if (c * 32 + 4 * i + 1 < first_col) p1 = 0.f;
-            if (c * 32 + 4 * i + 2 < first_col) p2 = 0.f;
-            if (c * 32 + 4 * i + 3 < first_col) p3 = 0.f;
+        for (int hq16 = 0; hq16 < 2; ++hq16) {
+          uint32_t pw[8], dw[8];
+#pragma unroll
+          for (int ii = 0; ii < 4; ++ii) {
+            const int i = 4 * hq16 + ii;
+            // the same addresses for every thread: shared-memory broadcasts
+            const float4 nl = lds_f4(stat + 16 * (c * 8 + i)), nd = lds_f4(stat + 16 * (32 + c * 8 + i));
+            float x0, x1, x2, x3;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[4 * i]), __uint_as_float(sraw[4 * i + 1])), beta2,
+                                   pack_f32x2(nl.x, nl.y)), x0, x1);
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[4 * i + 2]), __uint_as_float(sraw[4 * i + 3])), beta2,
+                                   pack_f32x2(nl.z, nl.w)), x2, x3);
+            float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+            if (tile_masked) {
+              if (c * 32 + 4 * i + 0 < first_col) p0 = 0.f;
+              if (c * 32 + 4 * i + 1 < first_col) p1 = 0.f;
+              if (c * 32 + 4 * i + 2 < first_col) p2 = 0.f;
+              if (c * 32 + 4 * i + 3 < first_col) p3 = 0.f;
+            }
+            // dS = P (dP - D)
+            float d0, d1, d2, d3;
+            unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1),
+                                   add_f32x2(pack_f32x2(__uint_as_float(draw[4 * i]), __uint_as_float(draw[4 * i + 1])),
+                                             pack_f32x2(nd.x, nd.y))), d0, d1);
+            unpack_f32x2(mul_f32x2(pack_f32x2(p2, p3),
+                                   add_f32x2(pack_f32x2(__uint_as_float(draw[4 * i + 2]), __uint_as_float(draw[4 * i + 3])),
+                                             pack_f32x2(nd.z, nd.w))), d2, d3);
+            pw[2 * ii] = pack_bf16x2(p0, p1);
+            pw[2 * ii + 1] = pack_bf16x2(p2, p3);
+            dw[2 * ii] = pack_bf16x2(d0, d1);
+            dw[2 * ii + 1] = pack_bf16x2(d2, d3);
           }
-          const uint64_t p01 = pack_f32x2(p0, p1), p23 = pack_f32x2(p2, p3);
-          pt[2 * i] = mul_f32x2(p01, pack_f32x2(g4.x, g4.y));
-          pt[2 * i + 1] = mul_f32x2(p23, pack_f32x2(g4.z, g4.w));
-          ds[2 * i] = mul_f32x2(p01, fma_f32x2(pack_f32x2(__uint_as_float(draw[4 * i]), __uint_as_float(draw[4 * i + 1])),
-                                               pack_f32x2(z4.x, z4.y), pack_f32x2(nd.x, nd.y)));
-          ds[2 * i + 1] =
-              mul_f32x2(p23, fma_f32x2(pack_f32x2(__uint_as_float(draw[4 * i + 2]), __uint_as_float(draw[4 * i + 3])),
-                                       pack_f32x2(z4.z, z4.w), pack_f32x2(nd.z, nd.w)));
+          tmem_st8(st_tmem + 8 * hq16, pw);
+          tmem_st8(dpt_tmem + 8 * hq16, dw);
         }
-        // the bf16 pairs go to the first columns of the half, which block 0's scores have left
-        store_block_bf16(pt, st_tmem + cc * 16);
-        store_block_bf16(ds, dpt_tmem + cc * 16);
       }
       tc_wait_st();
       tc_fence_before();
@@ -369,7 +378,7 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         __nv_bfloat16* dst_row = (which == 0 ? p.dv : p.dk) + row_off;
         const float scale = which == 0 ? 1.f : dk_scale;
 #pragma unroll 1
-        for (int c = 2 * half; c < 2 * half + 2; ++c) {
+        {
           uint32_t v[32];
           if (n_iter > 0) {  // uniform: TMEM loads are warp-wide
             tmem_ld32(src + c * 32, v);
@@ -525,8 +534,9 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         const uint64_t k_desc = smem_desc_sw128(stage_base(j), CHUNK_BYTES, 1024);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          mma_f16_ts(tmem_base + B_DQ_COL, dp_tmem + HALF_COLS * h + 8 * k, k_desc + 128 * (4 * h + k), idesc_ts,
-                     (j | h | k) != 0);
+          // 16 keys = 8 columns; a block of 32 keys keeps its pairs at the start of its own 32 columns
+          mma_f16_ts(tmem_base + B_DQ_COL, dp_tmem + HALF_COLS * h + 32 * (k >> 1) + 8 * (k & 1),
+                     k_desc + 128 * (4 * h + k), idesc_ts, (j | h | k) != 0);
         }
       };
       ok = ok && mbar_wait(kv_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD);
@@ -557,16 +567,17 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     __syncwarp();
   } else {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;  // which 64 of the tile's 128 columns this thread handles
+    const int c = (warp - 2) >> 2;  // which block of 32 of the tile's 128 columns this thread handles
+    const int half = c >> 1;        // the half the block is handed over with
     const int r = quad * 32 + lane;
     const int row = m0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    // this thread's half of the tile: scores in columns [64 half, 64 half + 64) of both buffers
-    const uint32_t s_tmem = tmem_base + lane_addr + B_S_COL + HALF_COLS * half;
-    const uint32_t dp_tmem = tmem_base + lane_addr + B_DP_COL + HALF_COLS * half;
+    // this thread's block: scores in columns [32 c, 32 c + 32) of both buffers
+    const uint32_t s_tmem = tmem_base + lane_addr + B_S_COL + 32 * c;
+    const uint32_t dp_tmem = tmem_base + lane_addr + B_DP_COL + 32 * c;
     const float beta = p.softmax_scale * LOG2E;
-    const float* rec = p.qstat + ((static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0) * 4 + r;
-    const float neg_l = rec[0], gsv = rec[256], neg_d = rec[384];  // -L, g*sv, -D of this query
+    const float* rec = p.qstat + ((static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0) * 2 + r;
+    const float neg_l = rec[0], neg_d = rec[128];  // -L and -D of this query
     const int row_limit = min(p.causal ? row + shift : p.Nk - 1, p.Nk - 1);
     bool ok = true;
 
@@ -579,16 +590,13 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       const int limit = row_limit - j * BN;  // columns > limit are masked
       // uniform over the CTA: does this tile contain any masked score?
       const bool tile_masked = (j * BN + BN > p.Nk) || (p.causal && j * BN + BN - 1 > m0 + shift);
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = 2 * half + cc;  // block of 32 keys within the tile
+      {
         uint32_t sraw[32], draw[32];
-        tmem_ld32(s_tmem + cc * 32, sraw);
-        tmem_ld32(dp_tmem + cc * 32, draw);
+        tmem_ld32(s_tmem, sraw);
+        tmem_ld32(dp_tmem, draw);
         tc_wait_ld();
         uint64_t ds[16];  // dS of this query for 32 keys, as packed pairs
-        const uint64_t beta2 = pack_f32x2(beta, beta), nl2 = pack_f32x2(neg_l, neg_l), z2 = pack_f32x2(gsv, gsv),
-                       nd2 = pack_f32x2(neg_d, neg_d);
+        const uint64_t beta2 = pack_f32x2(beta, beta), nl2 = pack_f32x2(neg_l, neg_l), nd2 = pack_f32x2(neg_d, neg_d);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float x0, x1;
@@ -600,9 +608,9 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             if (c * 32 + 2 * i + 1 > limit) p1 = 0.f;
           }
           ds[i] = mul_f32x2(pack_f32x2(p0, p1),
-                            fma_f32x2(pack_f32x2(__uint_as_float(draw[2 * i]), __uint_as_float(draw[2 * i + 1])), z2, nd2));
+                            add_f32x2(pack_f32x2(__uint_as_float(draw[2 * i]), __uint_as_float(draw[2 * i + 1])), nd2));
         }
-        store_block_bf16(ds, dp_tmem + cc * 16);
+        store_block_bf16(ds, dp_tmem);
       }
       tc_wait_st();
       tc_fence_before();
@@ -615,7 +623,7 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       const float scale = p.softmax_scale;
       __nv_bfloat16* dst_row = p.dq + ((static_cast<int64_t>(b) * p.Hq + hq) * p.Nq + row) * D;
 #pragma unroll 1
-      for (int c = 2 * half; c < 2 * half + 2; ++c) {
+      {
         uint32_t v[32];
         if (n_tiles > 0) {
           tmem_ld32(tmem_base + lane_addr + B_DQ_COL + c * 32, v);

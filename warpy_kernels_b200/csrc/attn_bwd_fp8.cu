@@ -8,14 +8,14 @@
 // every product runs on the tensor core in e4m3.  Three kernels:
 //
 //  1. attn_bwd_prep_kernel (HBM-bound): per query row, dO -> e4m3 with a power-of-two row
-//     scale g (as the MXFP8 quantiser picks it), D = sum(dO8 . g . O), and the row record
-//     (L, g, g . v_descale, D) the main kernels read.  The reference scales dO per
+//     scale g (as the MXFP8 quantiser picks it) and the two numbers per row the main kernels
+//     read, log2(g) - L and -sum(dO8 . O).  The reference scales dO per
 //     (batch, kv head) and carries a second residual term (bwd_common.py:133-266); a scale per
 //     row keeps small rows precise without it.
 //  2. attn_bwd_dkdv_kernel: CTA = 128 keys of one (batch, kv head), K and V resident in shared
 //     memory, loop over the group's query heads and query tiles.  Per tile:
 //       S^T = K Q^T and dP^T = V dO8^T            (tcgen05.mma kind::f8f6f4, into TMEM)
-//       threads (one per key): P^T . g and dS^T as MXFP8 (e4m3 codes back into TMEM, one
+//       threads (four per key): P^T . g and dS^T as MXFP8 (e4m3 codes back into TMEM, one
 //                              power-of-two scale per key and 32 queries, also into TMEM)
 //       dV += (P g)^T dO8 and dK += dS^T Q8       (kind::mxf8f6f4, A from TMEM, B = the same
 //                                                  Q / dO8 tiles read MN-major)
@@ -55,7 +55,7 @@ struct PrepParams {
   const float* lse;           // [B,Hq,*] base 2
   const float* v_descale;     // [B,Hkv]
   uint8_t* do8;               // [B,Hq,Nq,D] contiguous
-  float* qstat;               // [B,Hq,Nq_pad/128][4][128]: per 128 rows the arrays -L, g, g*sv, -D
+  float* qstat;               // [B,Hq,Nq_pad/128][2][128]: per 128 rows the arrays log2(g) - L and -D / sv
   int64_t do_sb, do_sh, do_sn;
   int64_t o_sb, o_sh, o_sn;
   int64_t lse_sb, lse_sh;
@@ -71,11 +71,11 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const PrepParams p) 
   const int i = warp % p.nq_pad;
   const int h = (warp / p.nq_pad) % p.Hq;
   const int b = warp / (p.nq_pad * p.Hq);
-  // the four values of row i sit 128 floats apart inside the row's tile of 128
-  float* stat = p.qstat + ((static_cast<int64_t>(b) * p.Hq + h) * p.nq_pad + (i & ~127)) * 4 + (i & 127);
+  // the two values of row i sit 128 floats apart inside the row's tile of 128
+  float* stat = p.qstat + ((static_cast<int64_t>(b) * p.Hq + h) * p.nq_pad + (i & ~127)) * 2 + (i & 127);
   if (i >= p.Nq) {
     // padding rows: lse = +inf makes every probability zero
-    if (lane < 4) stat[lane * 128] = lane == 0 ? -INFINITY : 0.f;
+    if (lane < 2) stat[lane * 128] = lane == 0 ? -INFINITY : 0.f;
     return;
   }
   const __nv_bfloat16* dsrc = p.dout + b * p.do_sb + h * p.do_sh + static_cast<int64_t>(i) * p.do_sn + lane * 4;
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const PrepParams p) 
   int e = static_cast<int>((amax + 0x1fffffu) >> 23) - 8;
   e = min(max(e, 0), 254);
   const float inv = __uint_as_float(static_cast<uint32_t>(max(254 - e, 1)) << 23);
-  const float g = __uint_as_float(static_cast<uint32_t>(max(e, 1)) << 23) * (e == 0 ? 0.5f : 1.f);
+  const float log2_g = static_cast<float>(e - 127);  // g = 2^(e - 127) is the scale the e4m3 codes carry
   const uint16_t c01 = cvt_e4m3x2(dv[0] * inv, dv[1] * inv);
   const uint16_t c23 = cvt_e4m3x2(dv[2] * inv, dv[3] * inv);
   float q0, q1, q2, q3;
@@ -114,10 +114,10 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const PrepParams p) 
   if (lane == 0) {
     const float sv = p.v_descale[b * p.Hkv + h / (p.Hq / p.Hkv)];
     const float L = p.lse[b * p.lse_sb + h * p.lse_sh + i];
-    stat[0] = -L;
-    stat[128] = g;
-    stat[256] = g * sv;
-    stat[384] = -dsum * g;
+    // With dO = g . dO8:  P g = 2^(s . beta - L + log2 g),  dV += (P g) dO8,  dS = (P g) . (sv . dP8 - sum(dO8 . O)),
+    // so the main kernels need two numbers per query and no multiplication by g
+    stat[0] = log2_g - L;
+    stat[128] = -dsum;
   }
 }
 
@@ -131,6 +131,13 @@ __device__ __forceinline__ uint32_t block_scale(uint32_t amax_bits, float& inv) 
   const int sf = max(eb - 7, 0);
   inv = __uint_as_float(static_cast<uint32_t>(254 - sf) << 23);
   return static_cast<uint32_t>(sf);
+}
+
+// Four consecutive floats from shared memory (the row records: every thread reads the same address, a broadcast).
+__device__ __forceinline__ float4 lds_f4(uint32_t saddr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
+  return v;
 }
 
 // The element-wise code keeps a block of 32 values as 16 packed fp32 pairs (fma/mul.f32x2 work on two at once).
@@ -184,9 +191,10 @@ __device__ __forceinline__ uint32_t max_bits_nonneg(const uint64_t (&x)[16]) {
 }
 
 struct BwdParams {
-  const float* qstat;    // [B,Hq,nq_pad/128][4][128]: -L, g, g*sv, -D of 128 rows
+  const float* qstat;    // [B,Hq,nq_pad/128][2][128]: log2(g) - L and -sum(dO8 . O) of 128 rows
   const float* q_descale;
   const float* k_descale;
+  const float* v_descale;
   __nv_bfloat16* dq;     // [B,Hq,Nq,D] contiguous
   __nv_bfloat16* dk;     // [B,Hkv,Nk,D] contiguous
   __nv_bfloat16* dv;
@@ -200,7 +208,7 @@ struct BwdParams {
 // 2. dK / dV
 // ---------------------------------------------------------------------------
 constexpr int A_STAGES = 2;
-constexpr int A_STAT_BYTES = BM * 16;
+constexpr int A_STAT_BYTES = BM * 8;
 constexpr int A_STAGE_BYTES = 2 * TILE_BYTES + A_STAT_BYTES;
 // Requested size is padded past half an SM's shared memory: each CTA allocates all 512 TMEM columns, so a second
 // resident CTA could only spin in tcgen05.alloc.
@@ -232,7 +240,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   auto p_full = [&](int h) { return bar_base + 8u * (3 + 2 * A_STAGES + h); };
   const uint32_t acc_full = bar_base + 8u * (5 + 2 * A_STAGES);
   const uint32_t tmem_slot = acc_full + 8;
-  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));  // generic pointer to the aligned base
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -290,7 +297,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         mbar_expect_tx(q_full(s), A_STAGE_BYTES);
         tma_load_4d(base, &tmap_q, q_full(s), 0, m0, hq, b);
         tma_load_4d(base + TILE_BYTES, &tmap_do, q_full(s), 0, m0, hq, b);
-        bulk_load(base + 2 * TILE_BYTES, p.qstat + ((static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0) * 4,
+        bulk_load(base + 2 * TILE_BYTES, p.qstat + ((static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0) * 2,
                   A_STAT_BYTES, q_full(s));
       }
     }
@@ -378,6 +385,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const int sc = b * p.Hkv + hkv;
     const float sq = p.q_descale[sc], sk = p.k_descale[sc];
     const float beta = p.softmax_scale * sq * sk * LOG2E;
+    const uint64_t sv2 = pack_f32x2(p.v_descale[sc], p.v_descale[sc]);
     bool ok = true;
 
     for (int it = 0; it < n_iter; ++it) {
@@ -388,9 +396,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         break;
       }
       tc_fence_after();
-      // the tile's row records: arrays -L, g, g*sv, -D of 128 queries each, read four queries at a time
-      const float4* stat = reinterpret_cast<const float4*>(smem_gen + (stage_smem - smem_base) + s * A_STAGE_BYTES +
-                                                           2 * TILE_BYTES);
+      // the tile's row records: arrays log2(g) - L and -sum(dO8 . O) of 128 queries each, read four at a time
+      const uint32_t stat = stage_smem + s * A_STAGE_BYTES + 2 * TILE_BYTES;
       // query column c is visible to this key iff key < Nk and (not causal or key <= m0 + c + shift)
       const int first_col = key >= p.Nk ? BM : (p.causal ? max(0, key - shift - m0) : 0);
       // uniform over the CTA: does this (key block, query tile) pair contain any masked score?
@@ -406,13 +413,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           // the same addresses for every thread: shared-memory broadcasts
-          const float4 nl = stat[c * 8 + i], g4 = stat[32 + c * 8 + i], z4 = stat[64 + c * 8 + i],
-                       nd = stat[96 + c * 8 + i];
+          const float4 el = lds_f4(stat + 16 * (c * 8 + i)), nd = lds_f4(stat + 16 * (32 + c * 8 + i));
           float x0, x1, x2, x3;
           unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[4 * i]), __uint_as_float(sraw[4 * i + 1])), beta2,
-                                 pack_f32x2(nl.x, nl.y)), x0, x1);
+                                 pack_f32x2(el.x, el.y)), x0, x1);
           unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[4 * i + 2]), __uint_as_float(sraw[4 * i + 3])), beta2,
-                                 pack_f32x2(nl.z, nl.w)), x2, x3);
+                                 pack_f32x2(el.z, el.w)), x2, x3);
           float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
           if (tile_masked) {
             if (c * 32 + 4 * i + 0 < first_col) p0 = 0.f;
@@ -420,14 +426,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             if (c * 32 + 4 * i + 2 < first_col) p2 = 0.f;
             if (c * 32 + 4 * i + 3 < first_col) p3 = 0.f;
           }
-          const uint64_t p01 = pack_f32x2(p0, p1), p23 = pack_f32x2(p2, p3);
-          pt[2 * i] = mul_f32x2(p01, pack_f32x2(g4.x, g4.y));
-          pt[2 * i + 1] = mul_f32x2(p23, pack_f32x2(g4.z, g4.w));
-          ds[2 * i] = mul_f32x2(p01, fma_f32x2(pack_f32x2(__uint_as_float(draw[4 * i]), __uint_as_float(draw[4 * i + 1])),
-                                               pack_f32x2(z4.x, z4.y), pack_f32x2(nd.x, nd.y)));
+          pt[2 * i] = pack_f32x2(p0, p1);
+          pt[2 * i + 1] = pack_f32x2(p2, p3);
+          ds[2 * i] = mul_f32x2(pt[2 * i], fma_f32x2(pack_f32x2(__uint_as_float(draw[4 * i]), __uint_as_float(draw[4 * i + 1])),
+                                                     sv2, pack_f32x2(nd.x, nd.y)));
           ds[2 * i + 1] =
-              mul_f32x2(p23, fma_f32x2(pack_f32x2(__uint_as_float(draw[4 * i + 2]), __uint_as_float(draw[4 * i + 3])),
-                                       pack_f32x2(z4.z, z4.w), pack_f32x2(nd.z, nd.w)));
+              mul_f32x2(pt[2 * i + 1], fma_f32x2(pack_f32x2(__uint_as_float(draw[4 * i + 2]), __uint_as_float(draw[4 * i + 3])),
+                                                 sv2, pack_f32x2(nd.z, nd.w)));
         }
         float inv_p, inv_d;
         const uint32_t bp = block_scale(max_bits_nonneg(pt), inv_p);  // P >= 0 and g > 0
@@ -651,8 +656,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int sc = b * p.Hkv + hkv;
     const float sq = p.q_descale[sc], sk = p.k_descale[sc];
     const float beta = p.softmax_scale * sq * sk * LOG2E;
-    const float* rec = p.qstat + ((static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0) * 4 + r;
-    const float neg_l = rec[0], gsv = rec[256], neg_d = rec[384];  // -L, g*sv, -D of this query
+    const float* rec = p.qstat + ((static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0) * 2 + r;
+    const float neg_l = rec[0], neg_d = rec[128];  // log2(g) - L and -sum(dO8 . O) of this query
+    const float gsv = p.v_descale[sc];  // dP = sv . dP8 in units of g
     const int row_limit = min(p.causal ? row + shift : p.Nk - 1, p.Nk - 1);
     bool ok = true;
 
@@ -825,6 +831,7 @@ extern "C" int wk_attn_bwd_fp8(const wk_attn_bwd_args* a, void* stream) {
   p.qstat = qstat;
   p.q_descale = a->q_descale;
   p.k_descale = a->k_descale;
+  p.v_descale = a->v_descale;
   p.dq = static_cast<__nv_bfloat16*>(a->dq);
   p.dk = static_cast<__nv_bfloat16*>(a->dk);
   p.dv = static_cast<__nv_bfloat16*>(a->dv);
