@@ -164,10 +164,10 @@ __device__ __forceinline__ uint32_t absmax_bits(const uint64_t (&x)[16]) {
     unpack_f32x2(x[i + 1], v2, v3);
     unpack_f32x2(x[i + 2], v4, v5);
     unpack_f32x2(x[i + 3], v6, v7);
-    a0 = fmaxf(fmaxf(a0, fabsf(v0)), fabsf(v1));
-    a1 = fmaxf(fmaxf(a1, fabsf(v2)), fabsf(v3));
-    a2 = fmaxf(fmaxf(a2, fabsf(v4)), fabsf(v5));
-    a3 = fmaxf(fmaxf(a3, fabsf(v6)), fabsf(v7));
+    a0 = max3_abs(a0, v0, v1);
+    a1 = max3_abs(a1, v2, v3);
+    a2 = max3_abs(a2, v4, v5);
+    a3 = max3_abs(a3, v6, v7);
   }
   return __float_as_uint(fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)));
 }
