@@ -35,8 +35,8 @@ NOMINAL = {"fp8": 4500.0, "bf16": 2250.0}  # dense TFLOP/s, B200 data sheet
 DRAM_TRAFFIC_BYTES = {
     "attn_fwd": 2 * (96.5e6 + 30.3e6 + 12.6e6),
     "attn_fwd_small": 96.5e6 + 30.3e6 + 12.6e6,
-    "attn_bwd": 2 * (157.6e6 + 229.0e6 + 179.2e6),
-    "attn_bwd_small": 157.6e6 + 229.0e6 + 179.2e6,
+    "attn_bwd": 2 * (156.5e6 + 226.4e6 + 177.7e6),
+    "attn_bwd_small": 156.5e6 + 226.4e6 + 177.7e6,
     "gemm_mx": 292.8e6 + 201.3e6,
     "gemm_bf16_8k": 1399.6e6 + 127.8e6,
     "quant": 234.9e6 + 82.3e6,
