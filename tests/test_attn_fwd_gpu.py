@@ -213,3 +213,20 @@ def test_bf16_layouts_and_options(cuda):
     ref4, lse_ref4 = R.attention_reference(q64.float().cpu(), k64.float().cpu(), v64.float().cpu(), True)
     errs = fwd_errors(out4, lse4, ref4, lse_ref4, Nq, Nk, True)
     assert out4.shape == q64.shape and errs["out"] <= 1e-2 and errs["lse"] <= 1e-2, errs
+
+
+def test_autotune_stores_the_winner(cuda, tmp_path, monkeypatch):
+    """``autotune_attn_fwd`` times its candidates and writes the reference's cache entry for the shape."""
+    import json
+
+    from warpy_kernels.attn import autotune_attn_fwd
+    from warpy_kernels_b200 import utils
+
+    monkeypatch.setattr(utils, "TUNE_CACHE_PATH", str(tmp_path / "tune.json"))
+    monkeypatch.setattr(utils, "_tune_cache", None)
+    q, k, v = randn_qkv(1, 4, 2, 256, 384, 128, device=cuda)
+    q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+    best, results = autotune_attn_fwd(q8, k8, v8, iters=2, verbose=False, q_descale=sq, k_descale=sk, v_descale=sv,
+                                      causal=True)
+    assert best == {} and len(results) == 1 and isinstance(results[0][1], float)
+    assert json.load(open(tmp_path / "tune.json")) == {"fwd|d=128|causal=1|nq=1024|nk=1024|rep=2|sm100": {}}

@@ -93,3 +93,25 @@ def test_product_never_imports_the_oracle():
                 if f.endswith((".py", ".cu", ".cuh", ".h")):
                     text = open(os.path.join(dirpath, f)).read()
                     assert "oracle" not in text.replace("oracle for", ""), f"{pkg}/{f} mentions the oracle"
+
+
+def test_tune_cache_uses_the_reference_file_format(tmp_path, monkeypatch):
+    """Keys and file layout of the reference's tune cache (``warpy_kernels/utils/__init__.py:229-273``)."""
+    import json
+
+    from warpy_kernels_b200 import utils
+
+    path = tmp_path / "cache" / "tune.json"
+    monkeypatch.setattr(utils, "TUNE_CACHE_PATH", str(path))
+    monkeypatch.setattr(utils, "_tune_cache", None)
+    key = utils.tune_key("fwd", 128, True, 4096, 4000, 4)
+    assert key == "fwd|d=128|causal=1|nq=4096|nk=4096|rep=4|sm100"
+    assert utils.tune_key("bwd_bf16", 64, False, 5, 1025, 1, arch=120) == "bwd_bf16|d=64|causal=0|nq=1024|nk=2048|rep=1"
+    assert utils.tune_lookup(key) is None
+    utils.tune_store(key, {"num_stages": 3})
+    assert json.load(open(path)) == {key: {"num_stages": 3}}
+    monkeypatch.setattr(utils, "_tune_cache", None)  # a new process reads the file back
+    assert utils.tune_lookup(key) == {"num_stages": 3}
+    best, results = utils.autotune("fwd", 128, False, 10, 10, 1, [{"a": 1}], lambda cfg: (lambda: None), 1, False) \
+        if torch.cuda.is_available() else ({"a": 1}, [])
+    assert best == {"a": 1}

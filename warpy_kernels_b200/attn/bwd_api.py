@@ -12,7 +12,7 @@ import torch
 
 from .. import _lib
 from ..arch import require
-from ..utils import cached_tensor, check_descale, time_candidates
+from ..utils import autotune, cached_tensor, check_descale
 from .fwd_api import KERNEL_D, _check_qkv, _check_shapes, _kernel_view, _pad_head_dim
 
 
@@ -189,15 +189,19 @@ def attn_bwd(
 
 
 def autotune_attn_bwd(q, k, v, out, lse, pmax, dout, candidates=None, iters=20, verbose=True, **kwargs):
-    """Time candidate configs (a single fixed configuration on SM100); kept for callers of the reference's tuner.
+    """Time candidate configs and store the fastest in the tune cache, as the reference's tuner does.
+
+    The SM100 kernels have a single configuration, so the default candidate list is ``[{}]``.
 
     Returns:
         ``(best_config, results)``.
     """
     _check_qkv(q, k, v)
-    require("attn_bwd_fp8", q)
-    candidates = candidates or [{}]
-    return time_candidates(
-        candidates, lambda cfg: make_attn_bwd(q, k, v, out, lse, pmax, dout, **cfg, **kwargs)[0], iters, verbose,
-        "attn_bwd",
+    bf16 = q.dtype == torch.bfloat16
+    require("attn_bwd" if bf16 else "attn_bwd_fp8", q)
+    _check_shapes(q, k, v)
+    return autotune(
+        "bwd_bf16" if bf16 else "bwd", q.shape[3], bool(kwargs.get("causal", False)), q.shape[2], k.shape[2],
+        q.shape[1] // k.shape[1], candidates or [{}],
+        lambda cfg: make_attn_bwd(q, k, v, out, lse, pmax, dout, **cfg, **kwargs)[0], iters, verbose,
     )

@@ -12,7 +12,7 @@ import torch
 
 from .. import _lib
 from ..arch import require
-from ..utils import cached_tensor, check_descale, round_up, time_candidates
+from ..utils import autotune, cached_tensor, check_descale, round_up
 
 BM = 128
 
@@ -226,14 +226,20 @@ def attn_fwd(q, k, v, q_descale=None, k_descale=None, v_descale=None, causal=Fal
 
 
 def autotune_attn_fwd(q, k, v, candidates=None, iters=20, verbose=True, **kwargs):
-    """Time candidate configs (a single fixed configuration on SM100); kept for callers of the reference's tuner.
+    """Time candidate configs and store the fastest in the tune cache, as the reference's tuner does.
+
+    The SM100 kernels have a single configuration, so the default candidate list is ``[{}]``; the cache entry keeps
+    the reference's key format (``fwd`` / ``fwd_bf16``, head dimension, mask, length buckets, GQA ratio, ``sm100``).
 
     Returns:
         ``(best_config, results)``.
     """
     _check_qkv(q, k, v)
-    require("attn_fwd_fp8", q)
-    candidates = candidates or [{}]
-    return time_candidates(
-        candidates, lambda cfg: make_attn_fwd(q, k, v, **cfg, **kwargs)[0], iters, verbose, "attn_fwd"
+    bf16 = q.dtype == torch.bfloat16
+    require("attn_fwd" if bf16 else "attn_fwd_fp8", q)
+    _check_shapes(q, k, v)
+    return autotune(
+        "fwd_bf16" if bf16 else "fwd", q.shape[3], bool(kwargs.get("causal", False)), q.shape[2], k.shape[2],
+        q.shape[1] // k.shape[1], candidates or [{}], lambda cfg: make_attn_fwd(q, k, v, **cfg, **kwargs)[0], iters,
+        verbose,
     )

@@ -1,9 +1,13 @@
 """Host-side helpers with the semantics of the reference's ``warpy_kernels/utils/__init__.py``.
 
 Only the pieces the hot path uses are here: ``round_up``/``pad_rows`` (``:170-179``), ``check_descale``
-(``:151-167``), ``cached_tensor`` (``:113-126``), and ``time_launch_ms``/``time_candidates`` (``:182-226``).  The
-reference's JIT compile cache and JSON tune cache have no counterpart: kernels here are compiled ahead of time.
+(``:151-167``), ``cached_tensor`` (``:113-126``), ``time_launch_ms``/``time_candidates`` (``:182-226``) and the JSON
+tune cache (``:229-273``: same file, same keys with an ``|sm100`` suffix, so one cache file can serve both
+libraries).  The reference's JIT compile cache has no counterpart: kernels here are compiled ahead of time.
 """
+
+import json
+import os
 
 import torch
 import torch.nn.functional as F
@@ -80,3 +84,46 @@ def time_candidates(candidates, build, iters, verbose, what):
     if not timed:
         raise RuntimeError(f"no {what} config ran: {results}")
     return min(timed, key=lambda ct: ct[1])[0], results
+
+
+# ---- tune cache: best config per (kernel, head dim, causal, length bucket, GQA ratio), one JSON object on disk ----
+TUNE_CACHE_PATH = os.environ.get("WARPY_KERNELS_TUNE_CACHE", os.path.expanduser("~/.cache/warpy_kernels_tune.json"))
+_tune_cache = None
+
+
+def tune_key(kind, d, causal, nq, nk, rep, arch=100):
+    """Cache key in the reference's format; lengths fall into power-of-two buckets of at least 1024."""
+    bucket = lambda n: 1 << max(10, (int(n) - 1).bit_length())
+    key = f"{kind}|d={d}|causal={int(causal)}|nq={bucket(nq)}|nk={bucket(nk)}|rep={rep}"
+    return key if arch == 120 else f"{key}|sm{arch}"
+
+
+def tune_lookup(key):
+    """The stored config for ``key``, or ``None``. An unreadable cache file counts as empty."""
+    global _tune_cache
+    if _tune_cache is None:
+        try:
+            with open(TUNE_CACHE_PATH) as f:
+                _tune_cache = json.load(f)
+        except (OSError, ValueError):
+            _tune_cache = {}
+    return _tune_cache.get(key)
+
+
+def tune_store(key, cfg):
+    """Remember ``cfg`` for ``key`` and rewrite the cache file (silently skipped if the file cannot be written)."""
+    tune_lookup(key)
+    _tune_cache[key] = cfg
+    try:
+        os.makedirs(os.path.dirname(TUNE_CACHE_PATH) or ".", exist_ok=True)
+        with open(TUNE_CACHE_PATH, "w") as f:
+            json.dump(_tune_cache, f, indent=1, sort_keys=True)
+    except OSError:
+        pass
+
+
+def autotune(kind, d, causal, nq, nk, rep, candidates, build, iters, verbose, arch=100):
+    """Time the candidates, store the winner under the shape's key, and return ``(best_config, results)``."""
+    best, results = time_candidates(candidates, build, iters, verbose, kind)
+    tune_store(tune_key(kind, d, causal, nq, nk, rep, arch), best)
+    return best, results
