@@ -206,6 +206,9 @@ typedef struct {
   int32_t lse_natural;      /* 1: lse is written in natural log units instead of base 2 */
   const int32_t* seqused_k; /* optional [B] int32: keys each batch item attends to (<= Nk) */
   float softmax_scale;
+  int32_t ctas_per_sm; /* fp8 forward: 2 = two CTAs per SM with 64-key tiles, 1 = one CTA per SM with 128-key
+                          rounds and four softmax groups (long sequences), 0 = pick by Nk.  The reference's
+                          tuning option of the same name (warpy_kernels/attn/fwd_api.py:196-208) */
 } wk_attn_fwd_args;
 
 int wk_attn_fwd_fp8(const wk_attn_fwd_args* args, void* stream);

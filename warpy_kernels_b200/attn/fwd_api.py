@@ -12,7 +12,7 @@ import torch
 
 from .. import _lib
 from ..arch import require
-from ..utils import autotune, cached_tensor, check_descale, round_up
+from ..utils import autotune, cached_tensor, check_descale, round_up, tune_key, tune_lookup
 
 BM = 128
 
@@ -27,7 +27,7 @@ class _FwdArgs(ctypes.Structure):
         ("B", ctypes.c_int32), ("Hq", ctypes.c_int32), ("Hkv", ctypes.c_int32), ("Nq", ctypes.c_int32),
         ("Nk", ctypes.c_int32), ("d", ctypes.c_int32),
         ("causal", ctypes.c_int32), ("write_lse", ctypes.c_int32), ("lse_natural", ctypes.c_int32),
-        ("seqused_k", ctypes.c_void_p), ("softmax_scale", ctypes.c_float),
+        ("seqused_k", ctypes.c_void_p), ("softmax_scale", ctypes.c_float), ("ctas_per_sm", ctypes.c_int32),
     ]
 
 
@@ -112,8 +112,11 @@ def make_attn_fwd(
         v_descale: Same as ``q_descale``, for ``v``.
         causal: Whether to apply a bottom-right aligned causal mask.
         softmax_scale: Scale on the logits, positive. Defaults to ``1 / sqrt(d)``.
-        num_stages, pipelined, block_n, block_m, warp_rows, ctas_per_sm, tile_local, lpt, tma, warp_spec, split_kv:
-            Tuning options of the reference's SM80-SM120 kernels; accepted and ignored.
+        ctas_per_sm: FP8 inputs: 2 runs the kernel with two CTAs per SM and 64-key tiles, 1 the one with a single
+            CTA per SM, 128-key rounds and four softmax groups, which is the faster one on long sequences. ``None``
+            takes the tuned value for the shape (``autotune_attn_fwd``), else 1 from 16384 keys on and 2 below.
+        num_stages, pipelined, block_n, block_m, warp_rows, tile_local, lpt, tma, warp_spec, split_kv:
+            Other tuning options of the reference's SM80-SM120 kernels; accepted and ignored.
         out: Output buffer, ``[B, Hq, Nq, d]`` bf16 with last stride 1 and even other strides. ``None`` allocates one
             with the memory layout of ``q``.
         return_lse: Whether to compute ``lse`` and ``pmax``. The backward pass needs them.
@@ -197,6 +200,12 @@ def make_attn_fwd(
     args.causal, args.write_lse, args.lse_natural = int(bool(causal)), int(bool(return_lse)), int(bool(lse_natural))
     args.seqused_k = seq.data_ptr() if seq is not None else None
     args.softmax_scale = float(softmax_scale)
+    if ctas_per_sm is None and not bf16:
+        tuned = tune_lookup(tune_key("fwd", d, causal, Nq, Nk, Hq // Hkv))
+        ctas_per_sm = (tuned or {}).get("ctas_per_sm")
+    if ctas_per_sm not in (None, 1, 2):
+        raise ValueError("ctas_per_sm must be 1 or 2")
+    args.ctas_per_sm = int(ctas_per_sm or 0)
     keep = (qv, kv, vv, dq_, dk_, dv_, seq, out_k)  # the launch closure owns what the argument block points at
     lib = _lib.lib()
     entry = lib.wk_attn_fwd_bf16 if bf16 else lib.wk_attn_fwd_fp8
@@ -228,8 +237,9 @@ def attn_fwd(q, k, v, q_descale=None, k_descale=None, v_descale=None, causal=Fal
 def autotune_attn_fwd(q, k, v, candidates=None, iters=20, verbose=True, **kwargs):
     """Time candidate configs and store the fastest in the tune cache, as the reference's tuner does.
 
-    The SM100 kernels have a single configuration, so the default candidate list is ``[{}]``; the cache entry keeps
-    the reference's key format (``fwd`` / ``fwd_bf16``, head dimension, mask, length buckets, GQA ratio, ``sm100``).
+    The FP8 forward has two kernels to choose from (``ctas_per_sm`` 1 and 2, the default candidates); ``make_attn_fwd``
+    looks the winner up when ``ctas_per_sm`` is not given. The cache entry keeps the reference's key format (``fwd`` /
+    ``fwd_bf16``, head dimension, mask, length buckets, GQA ratio, ``sm100``).
 
     Returns:
         ``(best_config, results)``.
@@ -240,6 +250,6 @@ def autotune_attn_fwd(q, k, v, candidates=None, iters=20, verbose=True, **kwargs
     _check_shapes(q, k, v)
     return autotune(
         "fwd_bf16" if bf16 else "fwd", q.shape[3], bool(kwargs.get("causal", False)), q.shape[2], k.shape[2],
-        q.shape[1] // k.shape[1], candidates or [{}], lambda cfg: make_attn_fwd(q, k, v, **cfg, **kwargs)[0], iters,
-        verbose,
+        q.shape[1] // k.shape[1], candidates or ([{}] if bf16 else [{"ctas_per_sm": 2}, {"ctas_per_sm": 1}]),
+        lambda cfg: make_attn_fwd(q, k, v, **cfg, **kwargs)[0], iters, verbose,
     )

@@ -449,6 +449,354 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Wide variant for long sequences (query blocks that see more than RESID_MAX_TILES key tiles): one CTA per SM,
+// 608 threads.  Measured against the kernel above: 4 % faster at 32768 keys per head, 8 % slower at 4096, where a
+// single CTA per SM leaves the prologue and epilogue of every query block uncovered.
+//
+//   warp 0       TMA producer: Q once, then K and V tiles of 128 keys into four-stage rings
+//   warp 1       S = Q.K^T for 128 keys at a time (four tcgen05.mma with N = 128: what a thread can issue per unit
+//                of time is limited, and a shared-memory operand pair for N = 64 is bandwidth-bound) into one of
+//                two 128-column S buffers
+//   warp 2       O += P.V, 64 keys at a time as the groups deliver their P
+//   warps 3-18   softmax in four groups of four warps: rounds of 128 keys alternate between the two S buffers,
+//                the two groups of a buffer take 64 keys each.  A thread reads the 64 scores of its row into
+//                registers and the buffer goes straight back to warp 1, so the next S is computed while the
+//                exponentials run; P goes to a small TMEM region per group.  (With P written over S, a group
+//                waited 1500-2500 cycles after every tile for the round trip P -> P.V -> next S.)
+//   TMEM (512 columns): S buffers 0..255 | group g: P codes 256 + 24 g .. + 15, scale word column + 16 + quad |
+//                       unit scales for V 352..355 | O 384..511
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int M_BN = 128;          // keys per round
+constexpr int M_KV_BYTES = M_BN * D;
+constexpr int M_GROUPS = 4;
+constexpr int M_THREADS = 96 + M_GROUPS * GROUP_THREADS;
+constexpr int M_TMEM_COLS = 512;
+constexpr int M_P_COL = 256;       // group g: 256 + 24 g
+constexpr int M_P_STRIDE = 24;
+constexpr int M_SFA_OFF = 16;      // inside a group's P region
+constexpr int M_SFB_COL = 352;
+constexpr int M_O_COL = 384;
+constexpr int M_XCH_BYTES = (1 + 2 * M_GROUPS) * BM * 4;  // row reference plus (l, m_true) of each group
+constexpr int M_SMEM_BYTES = Q_BYTES + 2 * KV_STAGES * M_KV_BYTES + M_XCH_BYTES + 1024 + 512;
+
+__global__ void __launch_bounds__(M_THREADS, 1)
+attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                         const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_smem = smem_base;
+  const uint32_t k_smem = q_smem + Q_BYTES;
+  const uint32_t v_smem = k_smem + KV_STAGES * M_KV_BYTES;
+  const uint32_t xch_smem = v_smem + KV_STAGES * M_KV_BYTES;  // exchange between the softmax groups
+  const uint32_t bar_base = xch_smem + M_XCH_BYTES;
+  const uint32_t q_full = bar_base;
+  auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar_base + 8u * (1 + KV_STAGES + s); };
+  auto v_full = [&](int s) { return bar_base + 8u * (1 + 2 * KV_STAGES + s); };
+  auto v_empty = [&](int s) { return bar_base + 8u * (1 + 3 * KV_STAGES + s); };
+  const uint32_t misc_bar = bar_base + 8u * (1 + 4 * KV_STAGES);
+  auto s_full = [&](int buf) { return misc_bar + 8u * buf; };        // S buffer `buf` holds a round's scores
+  auto s_free = [&](int buf) { return misc_bar + 8u * (2 + buf); };  // both of its groups have read them
+  auto p_full = [&](int g) { return misc_bar + 8u * (4 + g); };      // group g has written P
+  auto p_empty = [&](int g) { return misc_bar + 8u * (8 + g); };     // the P.V product has read group g's P
+  const uint32_t o_full = misc_bar + 8u * 12;
+  const uint32_t tmem_slot = misc_bar + 8u * 13;
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const int m_blk = p.m_first + gridDim.x - 1 - blockIdx.x;  // longest (latest) causal blocks first
+  const int hq = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hkv = hq / (p.Hq / p.Hkv);
+  const int m0 = m_blk * BM;
+  const int nk = p.seqused_k ? max(0, min(p.Nk, p.seqused_k[b])) : p.Nk;
+  const int shift = nk - p.Nq;  // key j is visible to query i iff j <= i + shift (causal)
+  int n_tiles = (nk + BN - 1) / BN;
+  if (p.causal) {
+    const int last_row = min(m0 + BM, p.Nq) - 1;
+    const int last_key = last_row + shift;  // may be negative
+    n_tiles = last_key < 0 ? 0 : min(n_tiles, last_key / BN + 1);
+  }
+  if (n_tiles <= RESID_MAX_TILES) return;  // the two-term variant's block
+  const int n_rounds = (n_tiles + 1) / 2;  // 128 keys each; the second half of the last one may be all masked
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(k_full(s), 1);
+      mbar_init(k_empty(s), 1);
+      mbar_init(v_full(s), 1);
+      mbar_init(v_empty(s), 1);
+    }
+    for (int buf = 0; buf < 2; ++buf) {
+      mbar_init(s_full(buf), 1);
+      mbar_init(s_free(buf), 2 * GROUP_THREADS);
+    }
+    for (int g = 0; g < M_GROUPS; ++g) {
+      mbar_init(p_full(g), GROUP_THREADS);
+      mbar_init(p_empty(g), 1);
+    }
+    mbar_init(o_full, 1);
+    mbar_fence_init();
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, M_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, Q_BYTES);
+      tma_load_4d(q_smem, &tmap_q, q_full, 0, m0, hq, b);
+      for (int R = 0; R < n_rounds; ++R) {
+        const int s = R % KV_STAGES;
+        const uint32_t ph = (R / KV_STAGES) & 1;
+        if (!mbar_wait(k_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(k_full(s), M_KV_BYTES);
+        tma_load_4d(k_smem + s * M_KV_BYTES, &tmap_k, k_full(s), 0, R * M_BN, hkv, b);
+        if (!mbar_wait(v_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(v_full(s), M_KV_BYTES);
+        tma_load_4d(v_smem + s * M_KV_BYTES, &tmap_v, v_full(s), 0, R * M_BN, hkv, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---- S = Q.K^T, a round of 128 keys at a time ---------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc(0, 0, 0, 0, BM, M_BN);
+      const uint64_t q_desc = smem_desc_sw128(q_smem, 16, 1024);
+      bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
+      for (int R = 0; ok && R < n_rounds; ++R) {
+        const int s = R % KV_STAGES;
+        const int buf = R & 1;
+        // the buffer is free when both groups have the scores of round R - 2 in registers
+        if (R >= 2 && !mbar_wait(s_free(buf), ((R >> 1) - 1) & 1, p.status, WK_ERR_TIMEOUT_P)) break;
+        if (!mbar_wait(k_full(s), (R / KV_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        tc_fence_after();
+        const uint64_t k_desc = smem_desc_sw128(k_smem + s * M_KV_BYTES, 16, 1024);
+        const uint32_t s_tmem = tmem_base + 128 * buf;
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) {
+          // 32 e4m3 = 32 bytes along the head dimension inside the 128-byte swizzle span
+          mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k != 0);
+        }
+        tc_commit(k_empty(s));
+        tc_commit(s_full(buf));
+      }
+    }
+    __syncwarp();
+  } else if (warp == 2) {
+    // ---- O += P.V, 64 keys at a time ------------------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t o_tmem = tmem_base + M_O_COL;
+      bool ok = true;
+      for (int R = 0; ok && R < n_rounds; ++R) {
+        const int s = R % KV_STAGES;
+        const uint32_t it_par = (R >> 1) & 1;
+        // V tile: 128 keys (the MMA's K) x 128 bytes of head dim (the MMA's N): MN-major,
+        // one 128-byte span wide, 8-key groups 1024 bytes apart, 32 keys per MMA = 4096 bytes
+        const uint64_t v_desc = smem_desc_sw128(v_smem + s * M_KV_BYTES, 16, 1024);
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          const int g = 2 * (R & 1) + h;
+          const uint32_t p_tmem = tmem_base + M_P_COL + M_P_STRIDE * g;
+          if (!mbar_wait(p_full(g), it_par, p.status, WK_ERR_TIMEOUT_P)) {
+            ok = false;
+            break;
+          }
+          if (h == 0 && !mbar_wait(v_full(s), (R / KV_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            // P: 32 e4m3 per K step = 8 TMEM columns; scale byte k of the row's scale word
+            mma_mxf8_ts(o_tmem, p_tmem + 8 * k, v_desc + 256 * (2 * h + k), make_idesc_mx_major(BM, D, k, 0, 0, 1),
+                        p_tmem + M_SFA_OFF, tmem_base + M_SFB_COL, (R | h | k) != 0);
+          }
+          tc_commit(p_empty(g));
+          if (h == 1) tc_commit(v_empty(s));
+        }
+      }
+      if (ok) tc_commit(o_full);
+    }
+    __syncwarp();
+  } else {
+    // Group g works on S buffer g >> 1 (rounds g >> 1, (g >> 1) + 2, ...) and there on keys [64 (g & 1), + 64).
+    // Inside a group one thread owns one query row.
+    const int quad = warp & 3;  // TMEM lanes [32 quad, 32 quad + 32) are the ones this warp may touch
+    const int grp = (warp - 3) >> 2;
+    const int buf = grp >> 1, half = grp & 1;
+    const int r = quad * 32 + lane;  // row of the tile == TMEM lane
+    const int row = m0 + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_addr + 128 * buf + 64 * half;
+    const uint32_t p_tmem = tmem_base + lane_addr + M_P_COL + M_P_STRIDE * grp;
+    const uint32_t o_tmem = tmem_base + lane_addr + M_O_COL;
+    const uint32_t x_ref = xch_smem + r * 4;
+    const int sc = b * p.Hkv + hkv;
+    const float beta = p.softmax_scale * p.q_descale[sc] * p.k_descale[sc] * 1.4426950408889634f;
+    const float sv = p.v_descale[sc];
+    const int row_limit = p.causal ? row + shift : nk - 1;  // last visible key of this row
+    // m_ref: reference exponent of the row, fixed by the first tile (O and the sums are in units of 2^-m_ref)
+    // l: sum of the exact probabilities over this group's tiles (normaliser of O, lse, pmax)
+    float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
+    bool ok = true;
+    bool met = false;  // the one-time meeting of the two groups has taken place
+
+    for (int R = buf; R < n_rounds; R += 2) {
+      const int it = R >> 1;
+      const int j = 2 * R + half;  // the 64-key tile
+      if (!mbar_wait_warp(s_full(buf), it & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      // the whole row of the tile into registers, then the S buffer goes back to the MMA thread
+      uint32_t sraw[2][32];
+      tmem_ld32(s_tmem, sraw[0]);
+      tmem_ld32(s_tmem + 32, sraw[1]);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(s_free(buf));
+
+      const int key0 = j * BN;
+      const bool tile_masked = (key0 + BN > nk) || (p.causal && key0 + BN - 1 > m0 + shift);
+      const int limit = min(row_limit, nk - 1) - key0;  // columns > limit are masked
+      if (tile_masked) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i > limit) sraw[c][i] = 0xff800000u;  // -inf
+      }
+      float cm[2];
+      cm[0] = block_max(sraw[0]) * beta;  // beta > 0 (checked on the host)
+      cm[1] = block_max(sraw[1]) * beta;
+      if (j == 0) {
+        // the row reference: maximum of the first tile (every row that sees any key sees one here)
+        m_ref = fmaxf(cm[0], cm[1]);
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_ref), "f"(m_ref) : "memory");
+      }
+      if (it == 0) {
+        // the groups meet once: the others pick up the reference the first one has just published
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+        met = true;
+        if (grp != 0) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(m_ref) : "r"(x_ref) : "memory");
+      } else {
+        // this group's P region is free once the P.V product of its previous tile has completed
+        if (!mbar_wait_warp(p_empty(grp), (it - 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+      }
+
+      uint32_t sf_word = 0;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        m_true = fmaxf(m_true, cm[c]);
+        const bool live = cm[c] > -INFINITY;
+        float kf = live ? ceilf(cm[c] - m_ref) : 0.f;  // block exponent relative to the row reference
+        if (kf > MAX_BLOCK_EXP) {
+          // the scores have outgrown the first tile's maximum by more than 2^100: not representable here
+          atomicCAS(p.status, 0, WK_ERR_RANGE);
+          kf = MAX_BLOCK_EXP;
+        }
+        const float bias = live ? (static_cast<float>(P_OFFSET) - kf) - m_ref : 0.f;
+        uint32_t w[8], wl[8];
+        float sum_exact;
+        softmax_block<false>(sraw[c], beta, bias, w, wl, sum_exact);
+        tmem_st8(p_tmem + c * 8, w);
+        int sf = live ? 127 + static_cast<int>(kf) - P_OFFSET : 0;
+        sf = min(max(sf, 0), 254);
+        const float blk_scale = __uint_as_float(static_cast<uint32_t>(sf) << 23);
+        if (live) l = fmaf(sum_exact, blk_scale, l);
+        sf_word |= static_cast<uint32_t>(sf) << (8 * c);
+      }
+      // scale factors straight into TMEM: the MMA reads the scale of row r from lane r, column r / 32
+      tmem_st1(p_tmem + M_SFA_OFF + quad, sf_word);
+      if (it == 0) {
+        tmem_st4(tmem_base + lane_addr + M_SFB_COL, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full(grp));
+    }
+    if (!met) {
+      // this group had no round (or gave up on a wait): it still owes the others the meeting above
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+    }
+
+    // epilogue: the groups add up their sums; group g stores head-dim columns [32 g, 32 g + 32)
+    if (ok) ok = mbar_wait_warp(o_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch_smem + (1 + 2 * grp) * BM * 4 + r * 4), "f"(l) : "memory");
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch_smem + (2 + 2 * grp) * BM * 4 + r * 4), "f"(m_true) : "memory");
+    asm volatile("bar.sync 1, 512;" ::: "memory");
+    {
+      l = 0.f;
+      m_true = -INFINITY;
+#pragma unroll
+      for (int g = 0; g < M_GROUPS; ++g) {  // same order in every group: identical sums
+        float l_g, mt_g;
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_g) : "r"(xch_smem + (1 + 2 * g) * BM * 4 + r * 4) : "memory");
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(mt_g) : "r"(xch_smem + (2 + 2 * g) * BM * 4 + r * 4) : "memory");
+        l += l_g;
+        m_true = fmaxf(m_true, mt_g);
+      }
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(m_ref) : "r"(x_ref) : "memory");
+    }
+    if (ok) {
+      tc_fence_after();
+      const bool empty = !(l > 0.f);
+      const float inv = empty ? 0.f : sv / l;
+      const int col0 = 32 * grp;
+      __nv_bfloat16* out_row = p.out + b * p.out_stride_b + hq * p.out_stride_h +
+                               static_cast<int64_t>(row) * p.out_stride_n + col0;
+      {
+        uint32_t v[32];
+        tmem_ld32(o_tmem + col0, v);
+        tc_wait_ld();
+        if (row < p.Nq) {
+          uint4* dst = reinterpret_cast<uint4*>(out_row);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(v[8 * i + 0]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+            dst[i] = w;
+          }
+        }
+      }
+      if (p.write_lse && grp == 0 && row < p.Nq) {
+        const int64_t off = b * p.lse_stride_b + hq * p.lse_stride_h + row;
+        const float lse = empty ? INFINITY : m_ref + log2f(l);
+        p.lse[off] = p.lse_natural ? lse * 0.6931471805599453f : lse;
+        p.pmax[off] = empty ? 0.f : exp2f(m_true - lse);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, M_TMEM_COLS);
+  }
+}
+
 }  // namespace
 }  // namespace wk
 
@@ -472,7 +820,7 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
   int* status = status_word();
   if (!status) return WK_E_CUDA;
 
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, tk128, tv128;  // K and V in tiles of 64 keys and, for the wide variant, of 128
   const uint32_t box[4] = {D, BM, 1, 1};
   const uint32_t box_kv[4] = {D, BN, 1, 1};
   {
@@ -493,6 +841,11 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
     int r = encode_tmap(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, a->k, dims, strk, box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
     if (r) return r;
     r = encode_tmap(&tv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, a->v, dims, strv, box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r) return r;
+    const uint32_t box_kv128[4] = {D, M_BN, 1, 1};
+    r = encode_tmap(&tk128, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, a->k, dims, strk, box_kv128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r) return r;
+    r = encode_tmap(&tv128, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, a->v, dims, strv, box_kv128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (r) return r;
   }
   FwdParams p;
@@ -520,6 +873,10 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
   p.status = status;
 
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<false>), SMEM_BYTES)) return WK_E_CUDA;
+  if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_wide_kernel), M_SMEM_BYTES)) return WK_E_CUDA;
+  // ctas_per_sm: 0 picks by the number of keys (the wide kernel pays off on long sequences)
+  if (a->ctas_per_sm < 0 || a->ctas_per_sm > 2) return WK_E_ARG;
+  const bool wide = a->ctas_per_sm == 1 || (a->ctas_per_sm == 0 && a->Nk >= 16384);
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<true>), SMEM_BYTES)) return WK_E_CUDA;
   const int num_m = (a->Nq + BM - 1) / BM;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -544,7 +901,11 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
   if (num_m - main_first > 0) {
     p.m_first = main_first;
     dim3 grid(num_m - main_first, a->Hq, a->B);
-    attn_fwd_fp8_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
+    if (wide) {
+      attn_fwd_fp8_wide_kernel<<<grid, M_THREADS, M_SMEM_BYTES, st>>>(tq, tk128, tv128, p);
+    } else {
+      attn_fwd_fp8_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
+    }
     if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
   }
   if (resid_count > 0) {
