@@ -35,6 +35,8 @@ NOMINAL = {"fp8": 4500.0, "bf16": 2250.0}  # dense TFLOP/s, B200 data sheet
 DRAM_TRAFFIC_BYTES = {
     "attn_fwd": 2 * (96.5e6 + 30.3e6 + 12.6e6),
     "attn_fwd_small": 96.5e6 + 30.3e6 + 12.6e6,
+    "attn_gqa": 4 * (83.1e6 + 84.5e6),
+    "attn_gqa_small": 83.1e6 + 84.5e6,
     "attn_bwd": 2 * (156.5e6 + 226.4e6 + 177.7e6),
     "attn_bwd_small": 156.5e6 + 226.4e6 + 177.7e6,
     "gemm_mx": 292.8e6 + 201.3e6,
@@ -308,6 +310,8 @@ WORKLOADS = {
                           make=lambda dev: make_attn_bwd_bf16(dev, 4, 32, 32, 4096, 128, True, 0)),
     "attn_gqa": dict(desc="FP8 GQA causal attention forward B1 Hq64 Hkv8 N32768 d128", unit="TFLOP/s",
                      make=lambda dev: make_attn(dev, 1, 64, 8, 32768, 128, True, 0)),
+    "attn_gqa_small": dict(desc="FP8 GQA causal attention forward B1 Hq16 Hkv2 N32768 d128 (profiling size)",
+                           unit="TFLOP/s", make=lambda dev: make_attn(dev, 1, 16, 2, 32768, 128, True, 0)),
     "gemm_bf16": dict(desc="BF16 GEMM M=N=K=2048", unit="TFLOP/s",
                       make=lambda dev: make_gemm_bf16(dev, 2048, 2048, 2048, 0)),
     "gemm_bf16_8k": dict(desc="BF16 GEMM M=N=K=8192", unit="TFLOP/s",
@@ -329,7 +333,7 @@ def cpu_baseline(workload, budget_s=15.0):
     from oracle import reference_math as R
 
     threads = torch.get_num_threads()
-    if workload in ("attn_fwd", "attn_gqa"):
+    if workload in ("attn_fwd", "attn_gqa", "attn_gqa_small"):
         N = 4096 if workload == "attn_fwd" else 32768
         d, heads, done, t_used = 128, 0, 0.0, 0.0
         g = torch.Generator().manual_seed(0)
