@@ -581,6 +581,9 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         // the buffer is free when both groups have the scores of round R - 2 in registers
         if (R >= 2 && !mbar_wait(s_free(buf), ((R >> 1) - 1) & 1, p.status, WK_ERR_TIMEOUT_P)) break;
         if (!mbar_wait(k_full(s), (R / KV_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        // Also the round's V tile, on behalf of warp 2: this thread has time to spare, that one is the busiest of
+        // the kernel, and what it does with V comes after this S, the softmax and the hand-over of P.
+        if (!mbar_wait(v_full(s), (R / KV_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
         tc_fence_after();
         const uint64_t k_desc = smem_desc_sw128(k_smem + s * M_KV_BYTES, 16, 1024);
         const uint32_t s_tmem = tmem_base + 128 * buf;
@@ -610,10 +613,6 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           const int g = 2 * (R & 1) + h;
           const uint32_t p_tmem = tmem_base + M_P_COL + M_P_STRIDE * g;
           if (!mbar_wait(p_full(g), it_par, p.status, WK_ERR_TIMEOUT_P)) {
-            ok = false;
-            break;
-          }
-          if (h == 0 && !mbar_wait(v_full(s), (R / KV_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) {
             ok = false;
             break;
           }
