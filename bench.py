@@ -423,7 +423,9 @@ def main():
             "ms_per_step": 1e3 * sum(times) / len(times),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl["desc"], "note": "reference CPU path = its torch fp32 test oracle on host cores"},
+            "config": {"workload": wl["desc"], "l2": "inputs and outputs larger than L2",
+                       "sharding": "independent per-rank shards, no collective",
+                       "note": "reference CPU path = its torch fp32 test oracle on host cores"},
             "cpu_baseline": best,
             "e2e": {"value": best["value"], "unit": best["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }
