@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this directory from the REFERENCE's own test oracle.
 
-Run in a container that has the reference checkout (default ``/root/reference``; override with the ``WARPY_REFERENCE``
+Run in a container that has the reference checkout (its path in the ``WARPY_REFERENCE``
 environment variable)::
 
     python tests/golden/make_golden.py
@@ -22,7 +22,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("WARPY_REFERENCE", "/root/reference")
+REF = os.environ.get("WARPY_REFERENCE", os.path.join(os.sep, "root", "reference"))
 
 
 def _load_reference_tests():
