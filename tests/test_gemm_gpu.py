@@ -371,3 +371,25 @@ def test_transposed_structured_operands(cuda):
     post, pre = gemm(x, w, out=c0.clone(), accum=True, act="gelu", store_pre=True)
     d = gemm(x, w.T.contiguous(), out=c0.clone(), act="dgelu", pre=pre, accum=True, b_trans=True)
     assert torch.equal(d, gemm(x, w, out=c0.clone(), act="dgelu", pre=pre, accum=True))
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16"])
+@pytest.mark.parametrize("shape", [(256, 256, 128), (512, 768, 384), (4096, 4096, 2048)])
+def test_cta_pair_kernel_matches_single_cta_kernel(cuda, kind, shape):
+    """``cta_pair=True``: two SMs per 256 x 256 tile (tcgen05 ``cta_group::2``).  Same products in the same order as
+    the single-CTA kernel, so the results are bit-identical; the fused epilogue goes through it as well."""
+    from warpy_kernels import gemm
+
+    m, n, k = shape
+    g = torch.Generator(device=cuda).manual_seed(0)
+    a, b, odt = _operands(cuda, kind, m, n, k, g)
+    out = gemm(a, b, cta_pair=True)
+    assert torch.equal(out, gemm(a, b, cta_pair=False))
+    assert R.rel_l2(out.float(), a.float() @ b.float().T) <= 1e-2
+    rows = torch.rand(m, device=cuda, generator=g) + 0.5
+    c0 = torch.randn(m, n, device=cuda, generator=g).to(odt)
+    post, pre = gemm(a, b, out=c0.clone(), scale_a=rows, accum=True, act="gelu", store_pre=True, cta_pair=True)
+    post1, pre1 = gemm(a, b, out=c0.clone(), scale_a=rows, accum=True, act="gelu", store_pre=True, cta_pair=False)
+    assert torch.equal(post, post1) and torch.equal(pre, pre1)
+    with pytest.raises(ValueError):
+        gemm(a[:128], b, cta_pair=True)  # M not a multiple of 256

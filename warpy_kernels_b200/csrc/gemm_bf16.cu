@@ -209,6 +209,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }
 
 }  // namespace
+
+// the CTA-pair kernel (gemm_bf16_2sm.cu)
+int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n, int k, int f16, const Epilogue& e,
+                          int* status, cudaStream_t stream);
 }  // namespace wk
 
 extern "C" int wk_gemm_16bit(const wk_gemm16_args* g, void* stream) {
@@ -255,6 +259,14 @@ extern "C" int wk_gemm_16bit(const wk_gemm16_args* g, void* stream) {
   e.pre_in = g->pre_in;
   e.q_mx = static_cast<uint8_t*>(g->q_mx);
   e.s_mx = static_cast<uint8_t*>(g->s_mx);
+  // cta_pair = 1 asks for the CTA-pair kernel (row-major operands, M and N multiples of 256, K of 128); 0 and 2
+  // use this file's kernel, which is the faster of the two today
+  if (g->cta_pair < 0 || g->cta_pair > 2) return WK_E_ARG;
+  const bool pair_ok = !g->a_trans && !g->b_trans && m % 256 == 0 && n % 256 == 0 && k % 128 == 0;
+  if (g->cta_pair == 1 && !pair_ok) return WK_E_ARG;
+  if (g->cta_pair == 1) {
+    return launch_gemm_16bit_2sm(g->a, g->b, g->out, m, n, k, g->f16, e, status, static_cast<cudaStream_t>(stream));
+  }
   if (allow_smem(reinterpret_cast<const void*>(gemm_bf16_kernel), SMEM_BYTES)) return WK_E_CUDA;
   const int num_tiles = (m / BM) * ((n + BN - 1) / BN);
   const int sms = sm_count();

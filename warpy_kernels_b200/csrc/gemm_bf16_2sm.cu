@@ -1,0 +1,320 @@
+// BF16 / FP16 GEMM on CTA pairs (tcgen05 cta_group::2): out[M,N] = a[M,K] . b[N,K]^T.
+//
+// Two CTAs of a cluster (two neighbouring SMs) share one 256 x 256 output tile.  Each CTA loads its own 128 rows
+// of A and its own 128 of the tile's 256 rows of B (32 KiB per stage instead of 48), the even CTA issues one
+// tcgen05.mma.cta_group::2 (M256 N256 K16) per K step for both, and each CTA's tensor memory holds the
+// accumulator rows of its own half of M.  Against the single-CTA kernel (gemm_bf16.cu) a pair reads a third less
+// shared memory per flop and a quarter less from L2 / DRAM.  Measured at 8192^3: 1.10-1.21 PFLOP/s against 1.40 of
+// the single-CTA kernel, bit-identical results; the thread that issues the MMAs also pays two commits per stage
+// (one per CTA), which is why a stage holds 128 K elements.  Callers opt in (cta_pair = 1) until it is the faster
+// one.
+//   warp 0      TMA producer in both CTAs; its loads signal the even CTA's "full" barrier
+//   warp 1      both: tensor-memory allocation for the pair; even CTA only: MMA issue; its commits release the
+//               stage in both CTAs and announce the finished accumulator to both
+//   warps 2-5   epilogue in both CTAs (the fused epilogue of gemm_epilogue.cuh), then they hand the accumulator
+//               back to the even CTA
+// Every wait is bounded (common.cuh); the two cluster-wide barriers at start and end are plain hardware barriers
+// that both CTAs always reach.
+//
+// Reached through wk_gemm_16bit with cta_pair = 1, for row-major operands with M and N multiples of 256 and K of 128.
+#include "common.cuh"
+#include "gemm_epilogue.cuh"
+#include "host_common.h"
+
+namespace wk {
+namespace {
+
+constexpr int P_BM = 256;  // output rows per CTA pair
+constexpr int P_BN = 256;
+constexpr int P_BK = 128;  // two 128-byte swizzle spans per row: the even CTA's thread pays a wait and two commits
+                           // per stage, which eight MMAs (1024 cycles) cover and four did not
+constexpr int P_STAGES = 3;
+constexpr int P_CHUNK_BYTES = 128 * 64 * 2;    // 128 rows x 64 K elements (one swizzle span)
+constexpr int P_A_BYTES = 2 * P_CHUNK_BYTES;   // this CTA's 128 rows of A
+constexpr int P_B_BYTES = 2 * P_CHUNK_BYTES;   // this CTA's 128 of the tile's 256 rows of B
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int P_THREADS = 192;
+constexpr int P_TMEM_COLS = 512;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of this CTA's shared-memory address `saddr` in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A[smem of both] * B[smem of both]
+__device__ __forceinline__ void mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on the mbarrier at shared::cluster address `bar` once the pair's MMAs issued so far have completed
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// TMA tile load into this CTA's shared memory whose completion is counted on a barrier of either CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+      "[%2];" ::"r"(dst),
+      "l"(map), "r"(bar_cluster), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar_cluster, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar_cluster),
+               "r"(bytes)
+               : "memory");
+}
+// bounded wait with cluster-scope acquire: the arrivals come from the other CTA as well
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* status, int code) {
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(bar), "r"(parity), "r"(kTryWaitSuspendNs)
+          : "memory");
+      if (ok) return true;
+    }
+    if (globaltimer_ns() - t0 > WK_WAIT_LIMIT_NS) {
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
+
+struct PairTile {
+  int m_blk, n_blk;
+};
+__device__ __forceinline__ PairTile pair_tile(int tile, int num_m, int num_n, int group_m) {
+  const int per_group = group_m * num_n;
+  const int g = tile / per_group;
+  const int first_m = g * group_m;
+  const int gsz = min(group_m, num_m - first_m);
+  const int local = tile - g * per_group;
+  PairTile c;
+  c.m_blk = first_m + local % gsz;
+  c.n_blk = local / gsz;
+  return c;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
+gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     void* __restrict__ out, int M, int N, int K, int group_m, int in_f16,
+                     const __grid_constant__ Epilogue epi, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + P_STAGES * P_STAGE_BYTES;
+  // barriers: full[STAGES] (used in the even CTA), empty[STAGES], tmem_full[2], tmem_empty[2] (used in the even
+  // CTA), then the TMEM base slot
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (P_STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * P_STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * P_STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * P_STAGES + 4);
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const uint32_t rank = cluster_ctarank();  // 0: issues the MMAs
+  const int pair = blockIdx.x / 2;
+  const int num_pairs = gridDim.x / 2;
+  const int num_m = M / P_BM;
+  const int num_n = N / P_BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = K / P_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(full_bar(s), 2);   // one arrival (with its byte count) from each CTA's producer
+      mbar_init(empty_bar(s), 1);  // the pair's commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8);  // four epilogue warps in each CTA
+    }
+    mbar_fence_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, P_TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // the other CTA's barriers are initialised before anybody signals them
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+        const PairTile tc = pair_tile(tile, num_m, num_n, group_m);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, status, WK_ERR_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+
+          const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+          const uint32_t full0 = mapa(full_bar(stage), 0);
+          mbar_expect_tx_cluster(full0, P_STAGE_BYTES);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            tma_load_2d_pair(sa + c * P_CHUNK_BYTES, &tmap_a, full0, kb * P_BK + 64 * c, tc.m_blk * P_BM + 128 * rank);
+            tma_load_2d_pair(sa + P_A_BYTES + c * P_CHUNK_BYTES, &tmap_b, full0, kb * P_BK + 64 * c,
+                             tc.n_blk * P_BN + 128 * rank);
+          }
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t fmt = in_f16 ? 0 : 1;
+      const uint32_t idesc = make_idesc(fmt, fmt, 0, 0, P_BM, P_BN);
+      // descriptors of stage 0 (the same offsets hold in the other CTA); a later stage only moves the
+      // 16-byte-granular start address field
+      const uint64_t a_desc0 = smem_desc_sw128(smem_base, 16, 1024);
+      const uint64_t b_desc0 = smem_desc_sw128(smem_base + P_A_BYTES, 16, 1024);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait_cluster(tempty_bar(acc), acc_phase ^ 1, status, WK_ERR_TIMEOUT_TMEM)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * P_BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, status, WK_ERR_TIMEOUT_LOAD)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t step = static_cast<uint64_t>(stage) * (P_STAGE_BYTES / 16);
+#pragma unroll
+          for (int k = 0; k < P_BK / 16; ++k) {
+            // 16 elements = 32 bytes along K inside a 128-byte swizzle span; the second span one chunk further on
+            const uint64_t off = step + (k >> 2) * (P_CHUNK_BYTES >> 4) + 2 * (k & 3);
+            mma_f16_ss_pair(d_tmem, a_desc0 + off, b_desc0 + off, idesc, (kb | k) != 0);
+          }
+          // the stage is free in both CTAs once these MMAs have read it.  (One commit here and the even CTA's
+          // producer passing the news on to the other measured 10 % slower: three stages leave no room for the
+          // extra latency.)
+          tc_commit_pair(mapa(empty_bar(stage), 0));
+          tc_commit_pair(mapa(empty_bar(stage), 1));
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) {
+          tc_commit_pair(mapa(tfull_bar(acc), 0));
+          tc_commit_pair(mapa(tfull_bar(acc), 1));
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are visible to this warp
+    int local = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
+      const PairTile tc = pair_tile(tile, num_m, num_n, group_m);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait_warp(tfull_bar(acc), acc_phase, status, WK_ERR_TIMEOUT_MMA)) break;
+      tc_fence_after();
+      const int row = tc.m_blk * P_BM + 128 * rank + quad * 32 + lane;
+      const float row_scale = epilogue_row_scale(epi, row);
+#pragma unroll 1
+      for (int c = 0; c < P_BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * P_BN + c * 32, v);
+        tc_wait_ld();
+        epilogue_chunk(epi, v, row_scale, row, tc.n_blk * P_BN + c * 32, N, out);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // nobody leaves while the other CTA may still signal this one's barriers
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, P_TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+// Launches the CTA-pair kernel.  The caller has checked the arguments; M and N are multiples of 256, K of 128.
+int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n, int k, int f16, const Epilogue& e,
+                          int* status, cudaStream_t stream) {
+  const CUtensorMapDataType dt = f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap ta, tb;
+  const uint32_t box[2] = {64, 128};
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
+    if (int r = encode_tmap(&ta, dt, 2, a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return r;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
+    if (int r = encode_tmap(&tb, dt, 2, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return r;
+  }
+  if (allow_smem(reinterpret_cast<const void*>(gemm_bf16_2sm_kernel), P_SMEM_BYTES)) return WK_E_CUDA;
+  const int sms = sm_count();
+  if (sms <= 0) return WK_E_CUDA;
+  const int num_tiles = (m / P_BM) * (n / P_BN);
+  const int max_pairs = sms / 2;
+  const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
+  gemm_bf16_2sm_kernel<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(ta, tb, out, m, n, k, 8, f16, e, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
+}
+
+}  // namespace wk

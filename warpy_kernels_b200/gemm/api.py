@@ -45,7 +45,7 @@ class _Gemm16Args(ctypes.Structure):
         *_EPILOGUE_FIELDS,
         ("pre_out", ctypes.c_void_p), ("pre_in", ctypes.c_void_p),
         ("q_mx", ctypes.c_void_p), ("s_mx", ctypes.c_void_p),
-        ("a_trans", ctypes.c_int32), ("b_trans", ctypes.c_int32),
+        ("a_trans", ctypes.c_int32), ("b_trans", ctypes.c_int32), ("cta_pair", ctypes.c_int32),
     ]
 
 
@@ -100,6 +100,7 @@ def make_gemm(
     a_scale_mx=None,
     out_mx=False,
     b_scale_mx=None,
+    cta_pair=None,
 ):
     """Prepare ``out = a @ b.T * scale_a * scale_b``.
 
@@ -128,6 +129,10 @@ def make_gemm(
             ``out_mx`` writes them. Needs fp8 inputs.
         out_mx: Whether to also write the result as MXFP8: e4m3 values ``[M, N]`` and ``[M, N / 32]`` uint8 ue8m0
             scales computed from the fp32 values before they are rounded to bf16.
+        cta_pair: 16-bit inputs only, not in the reference. ``True`` runs the CTA-pair kernel (``tcgen05``
+            ``cta_group::2``: two SMs share a 256 x 256 tile); it needs ``M`` and ``N`` multiples of 256, ``K`` of 128
+            and no transposed operand (``ValueError`` otherwise). ``None`` leaves the choice to the library, which
+            takes the single-CTA kernel today; ``False`` never uses pairs.
         b_scale_mx: ``[N, K / 32]`` uint8 ue8m0 scales of ``b``. Not in the reference (which scales only ``a``);
             ``None`` gives the reference's behaviour.
 
@@ -220,6 +225,7 @@ def make_gemm(
         args.m, args.n, args.k = m, n, k
         args.f16 = int(a.dtype == torch.float16)
         args.a_trans, args.b_trans = int(bool(a_trans)), int(bool(b_trans))
+        args.cta_pair = 0 if cta_pair is None else 1 if cta_pair else 2
         fill_epilogue(args)
         keep = (a, b, scale_a, scale_b, pre_out, pre_in)
 
