@@ -26,12 +26,14 @@ namespace {
 
 constexpr int P_BM = 256;  // output rows per CTA pair
 constexpr int P_BN = 256;
-constexpr int P_BK = 128;  // two 128-byte swizzle spans per row: the even CTA's thread pays a wait and two commits
-                           // per stage, which eight MMAs (1024 cycles) cover and four did not
+constexpr int P_BK = 128;  // two 128-byte swizzle spans per row.  Per stage the even CTA's thread pays a wait and two
+                           // commits; eight MMAs cover that, four did not (seven stages of 64: 0.75 PFLOP/s at 8192^3,
+                           // three of 128: 1.2)
 constexpr int P_STAGES = 3;
 constexpr int P_CHUNK_BYTES = 128 * 64 * 2;    // 128 rows x 64 K elements (one swizzle span)
-constexpr int P_A_BYTES = 2 * P_CHUNK_BYTES;   // this CTA's 128 rows of A
-constexpr int P_B_BYTES = 2 * P_CHUNK_BYTES;   // this CTA's 128 of the tile's 256 rows of B
+constexpr int P_CHUNKS = P_BK / 64;            // swizzle spans per row of a stage
+constexpr int P_A_BYTES = P_CHUNKS * P_CHUNK_BYTES;   // this CTA's 128 rows of A
+constexpr int P_B_BYTES = P_CHUNKS * P_CHUNK_BYTES;   // this CTA's 128 of the tile's 256 rows of B
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 constexpr int P_THREADS = 192;
@@ -195,7 +197,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           const uint32_t full0 = mapa(full_bar(stage), 0);
           mbar_expect_tx_cluster(full0, P_STAGE_BYTES);
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < P_CHUNKS; ++c) {
             tma_load_2d_pair(sa + c * P_CHUNK_BYTES, &tmap_a, full0, kb * P_BK + 64 * c, tc.m_blk * P_BM + 128 * rank);
             tma_load_2d_pair(sa + P_A_BYTES + c * P_CHUNK_BYTES, &tmap_b, full0, kb * P_BK + 64 * c,
                              tc.n_blk * P_BN + 128 * rank);
