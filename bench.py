@@ -230,13 +230,13 @@ def make_attn_bwd_bf16(dev, B, Hq, Hkv, N, d, causal, seed):
                 h2d=hdo.numel() * 2, d2h=sum(h.numel() * 2 for h in hg), tensors=(q, k, v, out, lse, dout))
 
 
-def make_gemm_bf16(dev, m, n, k, seed):
+def make_gemm_bf16(dev, m, n, k, seed, cta_pair=None):
     import warpy_kernels as wk
 
     g = torch.Generator(device=dev).manual_seed(seed)
     a = torch.randn(m, k, device=dev, generator=g).bfloat16()
     b = torch.randn(n, k, device=dev, generator=g).bfloat16()
-    launch, out = wk.make_gemm(a, b)
+    launch, out = wk.make_gemm(a, b, cta_pair=cta_pair)
     ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
     da, db = torch.empty_like(a), torch.empty_like(b)
     hout = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
@@ -244,7 +244,7 @@ def make_gemm_bf16(dev, m, n, k, seed):
     def e2e_step():
         da.copy_(ha, non_blocking=True)
         db.copy_(hb, non_blocking=True)
-        hout.copy_(wk.gemm(da, db), non_blocking=True)
+        hout.copy_(wk.gemm(da, db, cta_pair=cta_pair), non_blocking=True)
 
     return dict(step=launch, e2e_step=e2e_step, work=2.0 * m * n * k, bound="tensor", dtype="bf16", launches=1,
                 h2d=(ha.numel() + hb.numel()) * 2, d2h=hout.numel() * 2, tensors=(a, b, out))
@@ -316,6 +316,8 @@ WORKLOADS = {
                       make=lambda dev: make_gemm_bf16(dev, 2048, 2048, 2048, 0)),
     "gemm_bf16_8k": dict(desc="BF16 GEMM M=N=K=8192", unit="TFLOP/s",
                          make=lambda dev: make_gemm_bf16(dev, 8192, 8192, 8192, 0)),
+    "gemm_bf16_8k_pair": dict(desc="BF16 GEMM M=N=K=8192 on CTA pairs (cta_group::2)", unit="TFLOP/s",
+                              make=lambda dev: make_gemm_bf16(dev, 8192, 8192, 8192, 0, cta_pair=True)),
     "gemm_mx": dict(desc="MXFP8 GEMM M8192 N14336 K4096 (E8M0 scales on A and B)", unit="TFLOP/s",
                     make=lambda dev: make_gemm_mx(dev, 8192, 14336, 4096, 0)),
     "gemm_mx_b": dict(desc="MXFP8 GEMM M8192 N4096 K14336 (E8M0 scales on A and B)", unit="TFLOP/s",
