@@ -40,7 +40,9 @@ DRAM_TRAFFIC_BYTES = {
     "attn_bwd": 2 * (156.5e6 + 226.4e6 + 177.7e6),
     "attn_bwd_small": 156.5e6 + 226.4e6 + 177.7e6,
     "gemm_mx": 292.8e6 + 201.3e6,
-    "gemm_bf16_8k": 1399.6e6 + 127.8e6,
+    "gemm_bf16_8k": 1083.5e6 + 127.0e6,
+    "gemm_bf16_8k_pair": 1083.5e6 + 127.0e6,
+    "gemm_bf16_8k_single": 1377.2e6 + 128.6e6,
     "quant": 234.9e6 + 82.3e6,
 }
 
@@ -316,6 +318,8 @@ WORKLOADS = {
                       make=lambda dev: make_gemm_bf16(dev, 2048, 2048, 2048, 0)),
     "gemm_bf16_8k": dict(desc="BF16 GEMM M=N=K=8192", unit="TFLOP/s",
                          make=lambda dev: make_gemm_bf16(dev, 8192, 8192, 8192, 0)),
+    "gemm_bf16_8k_single": dict(desc="BF16 GEMM M=N=K=8192 on single CTAs (128 x 256 tiles)", unit="TFLOP/s",
+                                make=lambda dev: make_gemm_bf16(dev, 8192, 8192, 8192, 0, cta_pair=False)),
     "gemm_bf16_8k_pair": dict(desc="BF16 GEMM M=N=K=8192 on CTA pairs (cta_group::2)", unit="TFLOP/s",
                               make=lambda dev: make_gemm_bf16(dev, 8192, 8192, 8192, 0, cta_pair=True)),
     "gemm_mx": dict(desc="MXFP8 GEMM M8192 N14336 K4096 (E8M0 scales on A and B)", unit="TFLOP/s",

@@ -374,17 +374,22 @@ def test_transposed_structured_operands(cuda):
 
 
 @pytest.mark.parametrize("kind", ["bf16", "fp16"])
-@pytest.mark.parametrize("shape", [(256, 256, 128), (512, 768, 384), (4096, 4096, 2048)])
+@pytest.mark.parametrize("shape", [(256, 256, 128), (128, 128, 64), (384, 640, 192), (512, 768, 384),
+                                   (4096, 4096, 2048), (2176, 4224, 576)])
 def test_cta_pair_kernel_matches_single_cta_kernel(cuda, kind, shape):
     """``cta_pair=True``: two SMs per 256 x 256 tile (tcgen05 ``cta_group::2``).  Same products in the same order as
-    the single-CTA kernel, so the results are bit-identical; the fused epilogue goes through it as well."""
+    the single-CTA kernel, so the results are bit-identical; the fused epilogue goes through it as well.  Tiles that
+    hang over the edge of M or N by 128 (one CTA of the pair, or half the columns of both) store nothing there."""
     from warpy_kernels import gemm
 
     m, n, k = shape
     g = torch.Generator(device=cuda).manual_seed(0)
     a, b, odt = _operands(cuda, kind, m, n, k, g)
-    out = gemm(a, b, cta_pair=True)
+    guard = torch.full((m + 128, n), 7.0, device=cuda, dtype=odt)  # rows past M must stay untouched
+    out = gemm(a, b, out=guard[:m], cta_pair=True)
     assert torch.equal(out, gemm(a, b, cta_pair=False))
+    assert torch.equal(out, gemm(a, b))  # the library's own choice
+    assert bool((guard[m:] == 7.0).all())
     assert R.rel_l2(out.float(), a.float() @ b.float().T) <= 1e-2
     rows = torch.rand(m, device=cuda, generator=g) + 0.5
     c0 = torch.randn(m, n, device=cuda, generator=g).to(odt)
@@ -392,4 +397,4 @@ def test_cta_pair_kernel_matches_single_cta_kernel(cuda, kind, shape):
     post1, pre1 = gemm(a, b, out=c0.clone(), scale_a=rows, accum=True, act="gelu", store_pre=True, cta_pair=False)
     assert torch.equal(post, post1) and torch.equal(pre, pre1)
     with pytest.raises(ValueError):
-        gemm(a[:128], b, cta_pair=True)  # M not a multiple of 256
+        gemm(a.T.contiguous(), b, a_trans=True, cta_pair=True)  # row-major operands only

@@ -4,10 +4,12 @@
 // of A and its own 128 of the tile's 256 rows of B (32 KiB per stage instead of 48), the even CTA issues one
 // tcgen05.mma.cta_group::2 (M256 N256 K16) per K step for both, and each CTA's tensor memory holds the
 // accumulator rows of its own half of M.  Against the single-CTA kernel (gemm_bf16.cu) a pair reads a third less
-// shared memory per flop and a quarter less from L2 / DRAM.  Measured at 8192^3: 1.10-1.21 PFLOP/s against 1.40 of
-// the single-CTA kernel, bit-identical results; the thread that issues the MMAs also pays two commits per stage
-// (one per CTA), which is why a stage holds 128 K elements.  Callers opt in (cta_pair = 1) until it is the faster
-// one.
+// shared memory per flop and a quarter less from L2 / DRAM.  Measured at 8192^3: 1.50-1.54 PFLOP/s against 1.40 of
+// the single-CTA kernel, bit-identical results.
+// The "full" barrier of a stage lives in the even CTA and takes ONE arrival: the even CTA's producer announces the
+// bytes of both CTAs, and the odd CTA's loads just complete against it (its bytes may land first; the count goes
+// negative meanwhile).  An announcement sent from the odd CTA instead (a remote mbarrier.arrive.expect_tx) held
+// its producer for about a thousand cycles per stage and capped the kernel at 0.76-1.2 PFLOP/s.
 //   warp 0      TMA producer in both CTAs; its loads signal the even CTA's "full" barrier
 //   warp 1      both: tensor-memory allocation for the pair; even CTA only: MMA issue; its commits release the
 //               stage in both CTAs and announce the finished accumulator to both
@@ -16,7 +18,8 @@
 // Every wait is bounded (common.cuh); the two cluster-wide barriers at start and end are plain hardware barriers
 // that both CTAs always reach.
 //
-// Reached through wk_gemm_16bit with cta_pair = 1, for row-major operands with M and N multiples of 256 and K of 128.
+// Reached through wk_gemm_16bit for row-major operands (cta_pair = 1, or 0 when the pairs fill the GPU better); M
+// and N multiples of 128 and K of 64 as there.
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 #include "host_common.h"
@@ -26,10 +29,8 @@ namespace {
 
 constexpr int P_BM = 256;  // output rows per CTA pair
 constexpr int P_BN = 256;
-constexpr int P_BK = 128;  // two 128-byte swizzle spans per row.  Per stage the even CTA's thread pays a wait and two
-                           // commits; eight MMAs cover that, four did not (seven stages of 64: 0.75 PFLOP/s at 8192^3,
-                           // three of 128: 1.2)
-constexpr int P_STAGES = 3;
+constexpr int P_BK = 64;  // one 128-byte swizzle span per row
+constexpr int P_STAGES = 7;
 constexpr int P_CHUNK_BYTES = 128 * 64 * 2;    // 128 rows x 64 K elements (one swizzle span)
 constexpr int P_CHUNKS = P_BK / 64;            // swizzle spans per row of a stage
 constexpr int P_A_BYTES = P_CHUNKS * P_CHUNK_BYTES;   // this CTA's 128 rows of A
@@ -151,14 +152,14 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const uint32_t rank = cluster_ctarank();  // 0: issues the MMAs
   const int pair = blockIdx.x / 2;
   const int num_pairs = gridDim.x / 2;
-  const int num_m = M / P_BM;
-  const int num_n = N / P_BN;
+  const int num_m = (M + P_BM - 1) / P_BM;  // M and N are multiples of 128: the last tile may be half outside,
+  const int num_n = (N + P_BN - 1) / P_BN;  // where the loads read zeros and the epilogue stores nothing
   const int num_tiles = num_m * num_n;
   const int num_kb = K / P_BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
-      mbar_init(full_bar(s), 2);   // one arrival (with its byte count) from each CTA's producer
+      mbar_init(full_bar(s), 1);   // the even CTA's producer, which announces the bytes of both CTAs
       mbar_init(empty_bar(s), 1);  // the pair's commit
     }
     for (int a = 0; a < 2; ++a) {
@@ -195,7 +196,8 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
           const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
           const uint32_t full0 = mapa(full_bar(stage), 0);
-          mbar_expect_tx_cluster(full0, P_STAGE_BYTES);
+          // the other CTA's bytes may land before this announcement: the count just goes negative meanwhile
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * P_STAGE_BYTES);
 #pragma unroll
           for (int c = 0; c < P_CHUNKS; ++c) {
             tma_load_2d_pair(sa + c * P_CHUNK_BYTES, &tmap_a, full0, kb * P_BK + 64 * c, tc.m_blk * P_BM + 128 * rank);
@@ -241,9 +243,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             const uint64_t off = step + (k >> 2) * (P_CHUNK_BYTES >> 4) + 2 * (k & 3);
             mma_f16_ss_pair(d_tmem, a_desc0 + off, b_desc0 + off, idesc, (kb | k) != 0);
           }
-          // the stage is free in both CTAs once these MMAs have read it.  (One commit here and the even CTA's
-          // producer passing the news on to the other measured 10 % slower: three stages leave no room for the
-          // extra latency.)
+          // the stage is free in both CTAs once these MMAs have read it: one commit per CTA
           tc_commit_pair(mapa(empty_bar(stage), 0));
           tc_commit_pair(mapa(empty_bar(stage), 1));
           if (++stage == P_STAGES) {
@@ -268,13 +268,16 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       if (!mbar_wait_warp(tfull_bar(acc), acc_phase, status, WK_ERR_TIMEOUT_MMA)) break;
       tc_fence_after();
       const int row = tc.m_blk * P_BM + 128 * rank + quad * 32 + lane;
-      const float row_scale = epilogue_row_scale(epi, row);
+      const bool row_ok = row < M;  // the same for the whole CTA
+      const float row_scale = row_ok ? epilogue_row_scale(epi, row) : 0.f;
 #pragma unroll 1
       for (int c = 0; c < P_BN / 32; ++c) {
+        const int col = tc.n_blk * P_BN + c * 32;
+        if (!row_ok || col >= N) break;
         uint32_t v[32];
         tmem_ld32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * P_BN + c * 32, v);
         tc_wait_ld();
-        epilogue_chunk(epi, v, row_scale, row, tc.n_blk * P_BN + c * 32, N, out);
+        epilogue_chunk(epi, v, row_scale, row, col, N, out);
       }
       tc_fence_before();
       __syncwarp();
@@ -293,7 +296,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
 }  // namespace
 
-// Launches the CTA-pair kernel.  The caller has checked the arguments; M and N are multiples of 256, K of 128.
+// Launches the CTA-pair kernel.  The caller has checked the arguments; M and N are multiples of 128, K of 64.
 int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n, int k, int f16, const Epilogue& e,
                           int* status, cudaStream_t stream) {
   const CUtensorMapDataType dt = f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -312,7 +315,7 @@ int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n,
   if (allow_smem(reinterpret_cast<const void*>(gemm_bf16_2sm_kernel), P_SMEM_BYTES)) return WK_E_CUDA;
   const int sms = sm_count();
   if (sms <= 0) return WK_E_CUDA;
-  const int num_tiles = (m / P_BM) * (n / P_BN);
+  const int num_tiles = ((m + P_BM - 1) / P_BM) * ((n + P_BN - 1) / P_BN);
   const int max_pairs = sms / 2;
   const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
   gemm_bf16_2sm_kernel<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(ta, tb, out, m, n, k, 8, f16, e, status);

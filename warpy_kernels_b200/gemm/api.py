@@ -130,9 +130,10 @@ def make_gemm(
         out_mx: Whether to also write the result as MXFP8: e4m3 values ``[M, N]`` and ``[M, N / 32]`` uint8 ue8m0
             scales computed from the fp32 values before they are rounded to bf16.
         cta_pair: 16-bit inputs only, not in the reference. ``True`` runs the CTA-pair kernel (``tcgen05``
-            ``cta_group::2``: two SMs share a 256 x 256 tile); it needs ``M`` and ``N`` multiples of 256, ``K`` of 128
-            and no transposed operand (``ValueError`` otherwise). ``None`` leaves the choice to the library, which
-            takes the single-CTA kernel today; ``False`` never uses pairs.
+            ``cta_group::2``: two SMs share a 256 x 256 tile); it needs row-major operands (``ValueError`` with
+            ``a_trans`` / ``b_trans``). ``False`` never uses pairs. ``None`` leaves the choice to the library: pairs
+            when the 256 x 256 tiles fill the GPU about as well as 128 x 256 ones. The results are bit-identical
+            either way.
         b_scale_mx: ``[N, K / 32]`` uint8 ue8m0 scales of ``b``. Not in the reference (which scales only ``a``);
             ``None`` gives the reference's behaviour.
 
