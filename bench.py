@@ -252,13 +252,13 @@ def make_gemm_bf16(dev, m, n, k, seed, cta_pair=None):
                 h2d=(ha.numel() + hb.numel()) * 2, d2h=hout.numel() * 2, tensors=(a, b, out))
 
 
-def make_gemm_mx(dev, m, n, k, seed):
+def make_gemm_mx(dev, m, n, k, seed, cta_pair=None):
     import warpy_kernels as wk
 
     g = torch.Generator(device=dev).manual_seed(seed)
     a8, sa = wk.quantize_mx(torch.randn(m, k, device=dev, generator=g).bfloat16())
     b8, sb = wk.quantize_mx(torch.randn(n, k, device=dev, generator=g).bfloat16())
-    launch, out = wk.make_gemm(a8, b8, a_scale_mx=sa, b_scale_mx=sb)
+    launch, out = wk.make_gemm(a8, b8, a_scale_mx=sa, b_scale_mx=sb, cta_pair=cta_pair)
     host = [x.view(torch.uint8).cpu().pin_memory() for x in (a8, b8, sa, sb)]
     devb = [torch.empty_like(x.view(torch.uint8)) for x in (a8, b8, sa, sb)]
     hout = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
@@ -267,7 +267,7 @@ def make_gemm_mx(dev, m, n, k, seed):
         for d_, h_ in zip(devb, host):
             d_.copy_(h_, non_blocking=True)
         o = wk.gemm(devb[0].view(torch.float8_e4m3fn), devb[1].view(torch.float8_e4m3fn), a_scale_mx=devb[2],
-                    b_scale_mx=devb[3])
+                    b_scale_mx=devb[3], cta_pair=cta_pair)
         hout.copy_(o, non_blocking=True)
 
     return dict(step=launch, e2e_step=e2e_step, work=2.0 * m * n * k, bound="tensor", dtype="fp8", launches=3,
@@ -324,6 +324,8 @@ WORKLOADS = {
                               make=lambda dev: make_gemm_bf16(dev, 8192, 8192, 8192, 0, cta_pair=True)),
     "gemm_mx": dict(desc="MXFP8 GEMM M8192 N14336 K4096 (E8M0 scales on A and B)", unit="TFLOP/s",
                     make=lambda dev: make_gemm_mx(dev, 8192, 14336, 4096, 0)),
+    "gemm_mx_pair": dict(desc="MXFP8 GEMM M8192 N14336 K4096 on CTA pairs (cta_group::2)", unit="TFLOP/s",
+                         make=lambda dev: make_gemm_mx(dev, 8192, 14336, 4096, 0, cta_pair=True)),
     "gemm_mx_b": dict(desc="MXFP8 GEMM M8192 N4096 K14336 (E8M0 scales on A and B)", unit="TFLOP/s",
                       make=lambda dev: make_gemm_mx(dev, 8192, 4096, 14336, 0)),
     "quant": dict(desc="MXFP8 quantiser [8192, 14336] bf16", unit="GB/s",

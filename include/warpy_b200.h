@@ -137,6 +137,9 @@ typedef struct {
   int32_t out_f16;      /* 0: out / pre buffers are bf16, 1: fp16 */
   void* pre_out;        /* optional [M,N]: the value before the activation (act = 1) */
   const void* pre_in;   /* [M,N] pre-activation values, required for act = 2 */
+  int32_t cta_pair;     /* kernel choice as in wk_gemm16_args: 0 the library's, 1 CTA pairs (tcgen05 cta_group::2, one
+                           256 x 256 tile per two SMs), 2 single CTAs; bit-identical results.  wk_gemm_mxfp8_noalloc
+                           always runs single CTAs. */
 } wk_gemm_mx_args;
 
 int64_t wk_gemm_mxfp8_workspace_bytes(int m, int n, int k);

@@ -398,3 +398,29 @@ def test_cta_pair_kernel_matches_single_cta_kernel(cuda, kind, shape):
     assert torch.equal(post, post1) and torch.equal(pre, pre1)
     with pytest.raises(ValueError):
         gemm(a.T.contiguous(), b, a_trans=True, cta_pair=True)  # row-major operands only
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 128), (128, 128, 128), (384, 640, 384), (4096, 4096, 2048),
+                                   (2176, 4224, 640)])
+def test_mx_cta_pair_kernel_matches_single_cta_kernel(cuda, shape):
+    """MXFP8 on CTA pairs (``cta_pair=True``): each CTA of a pair holds the scale factors of its own rows of ``a`` and
+    of all 256 columns of the tile.  Bit-identical to the single-CTA kernel, fused epilogue and MX output included;
+    tiles that hang over the edge of M or N by 128 store nothing there."""
+    from warpy_kernels import gemm, quantize_mx
+
+    m, n, k = shape
+    g = torch.Generator(device=cuda).manual_seed(0)
+    a8, sa = quantize_mx(torch.randn(m, k, device=cuda, generator=g).bfloat16() * 3)
+    b8, sb = quantize_mx(torch.randn(n, k, device=cuda, generator=g).bfloat16() * 0.2)
+    guard = torch.full((m + 128, n), 7.0, device=cuda, dtype=torch.bfloat16)
+    out = gemm(a8, b8, a_scale_mx=sa, b_scale_mx=sb, out=guard[:m], cta_pair=True)
+    assert torch.equal(out, gemm(a8, b8, a_scale_mx=sa, b_scale_mx=sb, cta_pair=False))
+    assert torch.equal(out, gemm(a8, b8, a_scale_mx=sa, b_scale_mx=sb))
+    assert bool((guard[m:] == 7.0).all())
+    assert R.rel_l2(out.float(), R.mx_dequant(a8, sa) @ R.mx_dequant(b8, sb).T) <= 1e-2
+    rows = torch.rand(m, device=cuda, generator=g) + 0.5
+    c0 = torch.randn(m, n, device=cuda, generator=g).bfloat16()
+    kw = dict(a_scale_mx=sa, scale_a=rows, accum=True, act="gelu", store_pre=True, out_mx=True)
+    got = gemm(a8, b8, out=c0.clone(), cta_pair=True, **kw)
+    want = gemm(a8, b8, out=c0.clone(), cta_pair=False, **kw)
+    assert len(got) == len(want) and all(torch.equal(x.view(torch.uint8), y.view(torch.uint8)) for x, y in zip(got, want))

@@ -27,6 +27,7 @@
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 #include "host_common.h"
+#include "gemm_mxfp8.h"
 
 namespace wk {
 namespace {
@@ -67,31 +68,6 @@ __global__ void swizzle_scales_kernel(const uint8_t* __restrict__ s, uint32_t* _
   const int64_t atom = static_cast<int64_t>(rb) * kblocks128 + kb;
   out[atom * (SF_ATOM / 4) + (r % 32) * 4 + (r / 32)] = w;
 }
-
-struct TileCoord {
-  int m_blk, n_blk;
-};
-__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int group_m) {
-  const int per_group = group_m * num_n;
-  const int g = tile / per_group;
-  const int first_m = g * group_m;
-  const int gsz = min(group_m, num_m - first_m);
-  const int local = tile - g * per_group;
-  TileCoord c;
-  c.m_blk = first_m + local % gsz;
-  c.n_blk = local / gsz;
-  return c;
-}
-
-struct GemmParams {
-  void* out;
-  const uint8_t* sfa;   // swizzled atoms [M/128][K/128][512]
-  const uint8_t* sfb;   // swizzled atoms [N/128][K/128][512]
-  Epilogue epi;         // scales, accumulate, activation, MXFP8 copy
-  int M, N, K;
-  int group_m;
-  int* status;
-};
 
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -318,6 +294,7 @@ extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
   if ((a->q_mx == nullptr) != (a->s_mx == nullptr)) return WK_E_ARG;
   if (a->q_mx && !aligned16(a->q_mx)) return WK_E_ARG;
   if (!epilogue_args_ok(a)) return WK_E_ARG;
+  if (a->cta_pair < 0 || a->cta_pair > 2) return WK_E_ARG;
   if (a->workspace_bytes < wk_gemm_mxfp8_workspace_bytes(m, n, k)) return WK_E_ARG;
   int* status = status_word();
   if (!status) return WK_E_CUDA;
@@ -329,6 +306,18 @@ extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
   if (r) return r;
   r = swizzle(a->b_scale_mx, sfb, n, k, st);
   if (r) return r;
+
+  GemmParams p;
+  p.out = a->out;
+  p.sfa = sfa;
+  p.sfb = sfb;
+  p.epi = epilogue_of(a);
+  p.M = m;
+  p.N = n;
+  p.K = k;
+  p.group_m = 8;
+  p.status = status;
+  if (a->cta_pair == 1) return launch_gemm_mxfp8_2sm(a->a, a->b, p, st);
 
   CUtensorMap ta, tb;
   {
@@ -345,16 +334,6 @@ extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
     r = encode_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (r) return r;
   }
-  GemmParams p;
-  p.out = a->out;
-  p.sfa = sfa;
-  p.sfb = sfb;
-  p.epi = epilogue_of(a);
-  p.M = m;
-  p.N = n;
-  p.K = k;
-  p.group_m = 8;
-  p.status = status;
   if (allow_smem(reinterpret_cast<const void*>(gemm_mxfp8_kernel), SMEM_BYTES)) return WK_E_CUDA;
   const int num_tiles = (m / BM) * ((n + BN - 1) / BN);
   const int sms = sm_count();

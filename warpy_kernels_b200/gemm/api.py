@@ -33,7 +33,7 @@ class _MxArgs(ctypes.Structure):
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64),
         ("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32),
         *_EPILOGUE_FIELDS, ("out_f16", ctypes.c_int32),
-        ("pre_out", ctypes.c_void_p), ("pre_in", ctypes.c_void_p),
+        ("pre_out", ctypes.c_void_p), ("pre_in", ctypes.c_void_p), ("cta_pair", ctypes.c_int32),
     ]
 
 
@@ -129,11 +129,11 @@ def make_gemm(
             ``out_mx`` writes them. Needs fp8 inputs.
         out_mx: Whether to also write the result as MXFP8: e4m3 values ``[M, N]`` and ``[M, N / 32]`` uint8 ue8m0
             scales computed from the fp32 values before they are rounded to bf16.
-        cta_pair: 16-bit inputs only, not in the reference. ``True`` runs the CTA-pair kernel (``tcgen05``
-            ``cta_group::2``: two SMs share a 256 x 256 tile); it needs row-major operands (``ValueError`` with
-            ``a_trans`` / ``b_trans``). ``False`` never uses pairs. ``None`` leaves the choice to the library: pairs
-            when the 256 x 256 tiles fill the GPU about as well as 128 x 256 ones. The results are bit-identical
-            either way.
+        cta_pair: Not in the reference. ``True`` runs the CTA-pair kernel (``tcgen05`` ``cta_group::2``: two SMs
+            share a 256 x 256 tile); it needs row-major operands (``ValueError`` with ``a_trans`` / ``b_trans``).
+            ``False`` never uses pairs. ``None`` leaves the choice to the library: for 16-bit inputs pairs when the
+            256 x 256 tiles fill the GPU about as well as 128 x 256 ones, for fp8 inputs single CTAs. The results
+            are bit-identical either way.
         b_scale_mx: ``[N, K / 32]`` uint8 ue8m0 scales of ``b``. Not in the reference (which scales only ``a``);
             ``None`` gives the reference's behaviour.
 
@@ -246,6 +246,7 @@ def make_gemm(
         args.workspace, args.workspace_bytes = workspace.data_ptr(), ws_bytes
         args.m, args.n, args.k = m, n, k
         args.out_f16 = int(odt == torch.float16)
+        args.cta_pair = 0 if cta_pair is None else 1 if cta_pair else 2
         fill_epilogue(args)
         keep = (a, b, a_scale_mx, b_scale_mx, scale_a, scale_b, workspace, pre_out, pre_in)
 
