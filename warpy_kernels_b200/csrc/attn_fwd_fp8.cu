@@ -873,9 +873,11 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
 
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<false>), SMEM_BYTES)) return WK_E_CUDA;
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_wide_kernel), M_SMEM_BYTES)) return WK_E_CUDA;
-  // ctas_per_sm: 0 picks by the number of keys (the wide kernel pays off on long sequences)
+  // ctas_per_sm: 0 picks by the number of keys.  The wide kernel pays off on long sequences; measured with equal
+  // work (causal / full, TFLOP/s): 2048 keys 818 / 1088 against 975 / 1258 of the two-CTA kernel, 4096 keys
+  // 1047 / 1304 against 1132 / 1344, 8192 keys 1220 / 1457 against 1174 / 1353, 16384 keys (causal) 1384 against 1118
   if (a->ctas_per_sm < 0 || a->ctas_per_sm > 2) return WK_E_ARG;
-  const bool wide = a->ctas_per_sm == 1 || (a->ctas_per_sm == 0 && a->Nk >= 16384);
+  const bool wide = a->ctas_per_sm == 1 || (a->ctas_per_sm == 0 && a->Nk >= 8192);
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<true>), SMEM_BYTES)) return WK_E_CUDA;
   const int num_m = (a->Nq + BM - 1) / BM;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
