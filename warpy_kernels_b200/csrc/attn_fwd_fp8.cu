@@ -450,11 +450,10 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Wide variant for long sequences (query blocks that see more than RESID_MAX_TILES key tiles): one CTA per SM,
-// 608 threads.  Measured against the kernel above: 4 % faster at 32768 keys per head, 8 % slower at 4096, where a
-// single CTA per SM leaves the prologue and epilogue of every query block uncovered.
+// Wide variant (query blocks that see more than RESID_MAX_TILES key tiles): one persistent CTA per SM, 608 threads,
+// each working through a list of query blocks.
 //
-//   warp 0       TMA producer: Q once, then K and V tiles of 128 keys into four-stage rings
+//   warp 0       TMA producer: Q of a block (two buffers), then its K and V tiles of 128 keys into four-stage rings
 //   warp 1       S = Q.K^T for 128 keys at a time (four tcgen05.mma with N = 128: what a thread can issue per unit
 //                of time is limited, and a shared-memory operand pair for N = 64 is bandwidth-bound) into one of
 //                two 128-column S buffers
@@ -463,66 +462,126 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 //                the two groups of a buffer take 64 keys each.  A thread reads the 64 scores of its row into
 //                registers and the buffer goes straight back to warp 1, so the next S is computed while the
 //                exponentials run; P goes to a small TMEM region per group.  (With P written over S, a group
-//                waited 1500-2500 cycles after every tile for the round trip P -> P.V -> next S.)
+//                waited 1500-2500 cycles after every tile for the round trip P -> P.V -> next S.)  The groups also
+//                store a block's output; meanwhile warps 0 and 1 are already at work on the next block.
 //   TMEM (512 columns): S buffers 0..255 | group g: P codes 256 + 24 g .. + 15, scale word column + 16 + quad |
 //                       unit scales for V 352..355 | O 384..511
+//
+// Work list: the grid has one CTA per query block (longest blocks of a head first), but a CTA that has finished
+// issuing the loads of its block asks the hardware for the index of a CTA that has not started yet
+// (clusterlaunchcontrol.try_cancel) and works on that block as well, and so on until none is left: the blocks are
+// handed out one by one in launch order, as they would be to fresh CTAs, without the start-up and the drain of a
+// CTA in between.  Rounds and blocks are counted through the CTA's whole life: every barrier parity below derives
+// from those running counts.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int M_BN = 128;          // keys per round
 constexpr int M_KV_BYTES = M_BN * D;
 constexpr int M_GROUPS = 4;
-constexpr int M_THREADS = 96 + M_GROUPS * GROUP_THREADS;
+constexpr int M_SOFTMAX_THREADS = M_GROUPS * GROUP_THREADS;
+constexpr int M_THREADS = 96 + M_SOFTMAX_THREADS;
 constexpr int M_TMEM_COLS = 512;
 constexpr int M_P_COL = 256;       // group g: 256 + 24 g
 constexpr int M_P_STRIDE = 24;
 constexpr int M_SFA_OFF = 16;      // inside a group's P region
 constexpr int M_SFB_COL = 352;
 constexpr int M_O_COL = 384;
-constexpr int M_XCH_BYTES = (1 + 2 * M_GROUPS) * BM * 4;  // row reference plus (l, m_true) of each group
-constexpr int M_SMEM_BYTES = Q_BYTES + 2 * KV_STAGES * M_KV_BYTES + M_XCH_BYTES + 1024 + 512;
+constexpr int M_XCH_HALF = (1 + 2 * M_GROUPS) * BM * 4;  // row reference plus (l, m_true) of each group
+constexpr int M_XCH_BYTES = 2 * M_XCH_HALF;              // blocks alternate between the halves
+constexpr int M_SMEM_BYTES = 2 * Q_BYTES + 2 * KV_STAGES * M_KV_BYTES + M_XCH_BYTES + 1024 + 512;
+
+struct WideItem {
+  int hq, b, hkv, m0, nk, shift, n_tiles, n_rounds;
+};
+
+constexpr int M_SCHED_SLOTS = 4;  // answers of the launch control in flight
+constexpr int M_CONSUMERS = 3 + M_SOFTMAX_THREADS;  // threads that read every answer
+
+// The query block of grid index (x, y, z); false if it belongs to the two-term variant's launch.
+__device__ __forceinline__ bool wide_item(const FwdParams& p, uint32_t x, uint32_t y, uint32_t z, WideItem& it) {
+  const int m_blk = p.m_first + gridDim.x - 1 - x;  // longest (latest) causal blocks first
+  it.hq = y;
+  it.b = z;
+  it.hkv = it.hq / (p.Hq / p.Hkv);
+  it.m0 = m_blk * BM;
+  it.nk = p.seqused_k ? max(0, min(p.Nk, p.seqused_k[it.b])) : p.Nk;
+  it.shift = it.nk - p.Nq;  // key j is visible to query i iff j <= i + shift (causal)
+  int n_tiles = (it.nk + BN - 1) / BN;
+  if (p.causal) {
+    const int last_row = min(it.m0 + BM, p.Nq) - 1;
+    const int last_key = last_row + it.shift;  // may be negative
+    n_tiles = last_key < 0 ? 0 : min(n_tiles, last_key / BN + 1);
+  }
+  it.n_tiles = n_tiles;
+  it.n_rounds = (n_tiles + 1) / 2;  // 128 keys each; the second half of the last one may be all masked
+  return n_tiles > RESID_MAX_TILES;
+}
+
+// Asks the hardware to cancel the launch of a CTA of this grid that has not started; the 16-byte answer lands at
+// `resp` and its bytes are counted on `bar`.
+__device__ __forceinline__ void launch_control_try_cancel(uint32_t resp, uint32_t bar) {
+  asm volatile(
+      "clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];" ::"r"(resp),
+      "r"(bar)
+      : "memory");
+}
+// Decodes an answer: true and the cancelled CTA's index if one was cancelled, false if none was left.
+__device__ __forceinline__ bool launch_control_answer(uint32_t resp, uint32_t& x, uint32_t& y, uint32_t& z) {
+  uint32_t got;
+  asm volatile(
+      "{\n\t.reg .b128 ans;\n\t.reg .pred pc;\n\t.reg .b32 t;\n\t"
+      "ld.shared.b128 ans, [%4];\n\t"
+      "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 pc, ans;\n\t"
+      "selp.u32 %0, 1, 0, pc;\n\t"
+      "mov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
+      "@pc clusterlaunchcontrol.query_cancel.get_first_ctaid.v4.b32.b128 {%1, %2, %3, t}, ans;\n\t}"
+      : "=r"(got), "=r"(x), "=r"(y), "=r"(z)
+      : "r"(resp)
+      : "memory");
+  return got != 0;
+}
 
 __global__ void __launch_bounds__(M_THREADS, 1)
 attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t q_smem = smem_base;
-  const uint32_t k_smem = q_smem + Q_BYTES;
+  const uint32_t q_smem = smem_base;  // two buffers
+  const uint32_t k_smem = q_smem + 2 * Q_BYTES;
   const uint32_t v_smem = k_smem + KV_STAGES * M_KV_BYTES;
   const uint32_t xch_smem = v_smem + KV_STAGES * M_KV_BYTES;  // exchange between the softmax groups
   const uint32_t bar_base = xch_smem + M_XCH_BYTES;
-  const uint32_t q_full = bar_base;
-  auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
-  auto k_empty = [&](int s) { return bar_base + 8u * (1 + KV_STAGES + s); };
-  auto v_full = [&](int s) { return bar_base + 8u * (1 + 2 * KV_STAGES + s); };
-  auto v_empty = [&](int s) { return bar_base + 8u * (1 + 3 * KV_STAGES + s); };
-  const uint32_t misc_bar = bar_base + 8u * (1 + 4 * KV_STAGES);
+  auto q_full = [&](int i) { return bar_base + 8u * i; };
+  auto q_empty = [&](int i) { return bar_base + 8u * (2 + i); };
+  auto k_full = [&](int s) { return bar_base + 8u * (4 + s); };
+  auto k_empty = [&](int s) { return bar_base + 8u * (4 + KV_STAGES + s); };
+  auto v_full = [&](int s) { return bar_base + 8u * (4 + 2 * KV_STAGES + s); };
+  auto v_empty = [&](int s) { return bar_base + 8u * (4 + 3 * KV_STAGES + s); };
+  const uint32_t misc_bar = bar_base + 8u * (4 + 4 * KV_STAGES);
   auto s_full = [&](int buf) { return misc_bar + 8u * buf; };        // S buffer `buf` holds a round's scores
   auto s_free = [&](int buf) { return misc_bar + 8u * (2 + buf); };  // both of its groups have read them
   auto p_full = [&](int g) { return misc_bar + 8u * (4 + g); };      // group g has written P
   auto p_empty = [&](int g) { return misc_bar + 8u * (8 + g); };     // the P.V product has read group g's P
-  const uint32_t o_full = misc_bar + 8u * 12;
-  const uint32_t tmem_slot = misc_bar + 8u * 13;
+  const uint32_t o_full = misc_bar + 8u * 12;    // the block's last P.V product has completed
+  const uint32_t o_free = misc_bar + 8u * 13;    // every softmax thread has read its part of O
+  const uint32_t ref_full = misc_bar + 8u * 14;  // the block's row references are published
+  const uint32_t sum_meet = misc_bar + 8u * 15;  // every group has published its sums
+  auto sched_full = [&](int i) { return misc_bar + 8u * (16 + i); };                   // answer i has landed
+  auto sched_empty = [&](int i) { return misc_bar + 8u * (16 + M_SCHED_SLOTS + i); };  // and everybody has read it
+  const uint32_t tmem_slot = misc_bar + 8u * (16 + 2 * M_SCHED_SLOTS);
+  auto sched_resp = [&](int i) { return misc_bar + 8u * (18 + 2 * M_SCHED_SLOTS) + 16u * i; };  // 16-byte answers
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
-  const int m_blk = p.m_first + gridDim.x - 1 - blockIdx.x;  // longest (latest) causal blocks first
-  const int hq = blockIdx.y;
-  const int b = blockIdx.z;
-  const int hkv = hq / (p.Hq / p.Hkv);
-  const int m0 = m_blk * BM;
-  const int nk = p.seqused_k ? max(0, min(p.Nk, p.seqused_k[b])) : p.Nk;
-  const int shift = nk - p.Nq;  // key j is visible to query i iff j <= i + shift (causal)
-  int n_tiles = (nk + BN - 1) / BN;
-  if (p.causal) {
-    const int last_row = min(m0 + BM, p.Nq) - 1;
-    const int last_key = last_row + shift;  // may be negative
-    n_tiles = last_key < 0 ? 0 : min(n_tiles, last_key / BN + 1);
-  }
-  if (n_tiles <= RESID_MAX_TILES) return;  // the two-term variant's block
-  const int n_rounds = (n_tiles + 1) / 2;  // 128 keys each; the second half of the last one may be all masked
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(q_full(i), 1);
+      mbar_init(q_empty(i), 1);
+    }
+    for (int i = 0; i < M_SCHED_SLOTS; ++i) {
+      mbar_init(sched_full(i), 1);
+      mbar_init(sched_empty(i), M_CONSUMERS);
+    }
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(k_full(s), 1);
       mbar_init(k_empty(s), 1);
@@ -538,6 +597,9 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       mbar_init(p_empty(g), 1);
     }
     mbar_init(o_full, 1);
+    mbar_init(o_free, M_SOFTMAX_THREADS);
+    mbar_init(ref_full, GROUP_THREADS);
+    mbar_init(sum_meet, M_SOFTMAX_THREADS);
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
     prefetch_tmap(&tmap_k);
@@ -553,19 +615,64 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
+  WideItem it;
+  bool ok = true;
+  bool valid = wide_item(p, blockIdx.x, blockIdx.y, blockIdx.z, it);  // false: nothing to do for this block here
+  uint32_t n_blocks = 0;  // answers read so far
+  // Reads the next answer of the launch control: false if no block was left (or the wait gave up: ok is false then).
+  auto next_block = [&]() {
+    const int slot = n_blocks % M_SCHED_SLOTS;
+    if (!mbar_wait(sched_full(slot), (n_blocks / M_SCHED_SLOTS) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) {
+      ok = false;
+      return false;
+    }
+    uint32_t x, y, z;
+    const bool got = launch_control_answer(sched_resp(slot), x, y, z);
+    // the slot's next answer is written through the async proxy: order this read before it
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_arrive(sched_empty(slot));
+    ++n_blocks;
+    if (got) valid = wide_item(p, x, y, z, it);
+    return got;
+  };
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, Q_BYTES);
-      tma_load_4d(q_smem, &tmap_q, q_full, 0, m0, hq, b);
-      for (int R = 0; R < n_rounds; ++R) {
-        const int s = R % KV_STAGES;
-        const uint32_t ph = (R / KV_STAGES) & 1;
-        if (!mbar_wait(k_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
-        mbar_expect_tx(k_full(s), M_KV_BYTES);
-        tma_load_4d(k_smem + s * M_KV_BYTES, &tmap_k, k_full(s), 0, R * M_BN, hkv, b);
-        if (!mbar_wait(v_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
-        mbar_expect_tx(v_full(s), M_KV_BYTES);
-        tma_load_4d(v_smem + s * M_KV_BYTES, &tmap_v, v_full(s), 0, R * M_BN, hkv, b);
+      int ci = -1;
+      uint32_t gr = 0;  // rounds so far
+      for (;;) {
+        if (valid) {
+        ++ci;
+        const int qb = ci & 1;
+        // the S products of the block before the previous one have read this Q buffer
+        if (ci >= 2 && !mbar_wait(q_empty(qb), ((ci >> 1) - 1) & 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(q_full(qb), Q_BYTES);
+        tma_load_4d(q_smem + qb * Q_BYTES, &tmap_q, q_full(qb), 0, it.m0, it.hq, it.b);
+        for (int R = 0; R < it.n_rounds; ++R, ++gr) {
+          const int s = gr % KV_STAGES;
+          const uint32_t ph = (gr / KV_STAGES) & 1;
+          if (!mbar_wait(k_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(k_full(s), M_KV_BYTES);
+          tma_load_4d(k_smem + s * M_KV_BYTES, &tmap_k, k_full(s), 0, R * M_BN, it.hkv, it.b);
+          if (!mbar_wait(v_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(v_full(s), M_KV_BYTES);
+          tma_load_4d(v_smem + s * M_KV_BYTES, &tmap_v, v_full(s), 0, R * M_BN, it.hkv, it.b);
+        }
+        }
+        if (!ok) break;
+        // this block's loads are on their way: ask for another block (the MMAs have rounds in hand meanwhile)
+        const int slot = n_blocks % M_SCHED_SLOTS;
+        if (n_blocks >= M_SCHED_SLOTS &&
+            !mbar_wait(sched_empty(slot), ((n_blocks / M_SCHED_SLOTS) - 1) & 1, p.status, WK_ERR_TIMEOUT_EMPTY))
+          break;
+        mbar_expect_tx(sched_full(slot), 16);
+        launch_control_try_cancel(sched_resp(slot), sched_full(slot));
+        if (!next_block()) break;
       }
     }
     __syncwarp();
@@ -573,27 +680,47 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     // ---- S = Q.K^T, a round of 128 keys at a time ---------------------------------------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(0, 0, 0, 0, BM, M_BN);
-      const uint64_t q_desc = smem_desc_sw128(q_smem, 16, 1024);
-      bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
-      for (int R = 0; ok && R < n_rounds; ++R) {
-        const int s = R % KV_STAGES;
-        const int buf = R & 1;
-        // the buffer is free when both groups have the scores of round R - 2 in registers
-        if (R >= 2 && !mbar_wait(s_free(buf), ((R >> 1) - 1) & 1, p.status, WK_ERR_TIMEOUT_P)) break;
-        if (!mbar_wait(k_full(s), (R / KV_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
-        // Also the round's V tile, on behalf of warp 2: this thread has time to spare, that one is the busiest of
-        // the kernel, and what it does with V comes after this S, the softmax and the hand-over of P.
-        if (!mbar_wait(v_full(s), (R / KV_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
-        tc_fence_after();
-        const uint64_t k_desc = smem_desc_sw128(k_smem + s * M_KV_BYTES, 16, 1024);
-        const uint32_t s_tmem = tmem_base + 128 * buf;
+      int ci = -1;
+      uint32_t gr = 0;
+      for (;;) {
+        if (valid) {
+        ++ci;
+        const int qb = ci & 1;
+        const uint64_t q_desc = smem_desc_sw128(q_smem + qb * Q_BYTES, 16, 1024);
+        if (!mbar_wait(q_full(qb), (ci >> 1) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        for (int R = 0; R < it.n_rounds; ++R, ++gr) {
+          const int s = gr % KV_STAGES;
+          const uint32_t ph = (gr / KV_STAGES) & 1;
+          const int buf = gr & 1;
+          // the buffer is free when both groups have the scores of the round before the previous one in registers
+          if (gr >= 2 && !mbar_wait(s_free(buf), ((gr >> 1) - 1) & 1, p.status, WK_ERR_TIMEOUT_P)) {
+            ok = false;
+            break;
+          }
+          if (!mbar_wait(k_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) {
+            ok = false;
+            break;
+          }
+          // Also the round's V tile, on behalf of warp 2: this thread has time to spare, that one is the busiest of
+          // the kernel, and what it does with V comes after this S, the softmax and the hand-over of P.
+          if (!mbar_wait(v_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t k_desc = smem_desc_sw128(k_smem + s * M_KV_BYTES, 16, 1024);
+          const uint32_t s_tmem = tmem_base + 128 * buf;
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k) {
-          // 32 e4m3 = 32 bytes along the head dimension inside the 128-byte swizzle span
-          mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k != 0);
+          for (int k = 0; k < D / 32; ++k) {
+            // 32 e4m3 = 32 bytes along the head dimension inside the 128-byte swizzle span
+            mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k != 0);
+          }
+          tc_commit(k_empty(s));
+          tc_commit(s_full(buf));
         }
-        tc_commit(k_empty(s));
-        tc_commit(s_full(buf));
+        if (ok) tc_commit(q_empty(qb));
+        }
+        if (!ok || !next_block()) break;
       }
     }
     __syncwarp();
@@ -601,171 +728,191 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     // ---- O += P.V, 64 keys at a time ------------------------------------------------------------------------------
     if (lane == 0) {
       const uint32_t o_tmem = tmem_base + M_O_COL;
-      bool ok = true;
-      for (int R = 0; ok && R < n_rounds; ++R) {
-        const int s = R % KV_STAGES;
-        const uint32_t it_par = (R >> 1) & 1;
-        // V tile: 128 keys (the MMA's K) x 128 bytes of head dim (the MMA's N): MN-major,
-        // one 128-byte span wide, 8-key groups 1024 bytes apart, 32 keys per MMA = 4096 bytes
-        const uint64_t v_desc = smem_desc_sw128(v_smem + s * M_KV_BYTES, 16, 1024);
+      int ci = -1;
+      uint32_t gr = 0;
+      for (;;) {
+        if (valid) {
+        ++ci;
+        // the softmax threads have read the previous block's O
+        if (ci >= 1 && !mbar_wait(o_free, (ci - 1) & 1, p.status, WK_ERR_TIMEOUT_TMEM)) break;
+        tc_fence_after();
+        for (int R = 0; ok && R < it.n_rounds; ++R, ++gr) {
+          const int s = gr % KV_STAGES;
+          const uint32_t it_par = (gr >> 1) & 1;
+          // V tile: 128 keys (the MMA's K) x 128 bytes of head dim (the MMA's N): MN-major,
+          // one 128-byte span wide, 8-key groups 1024 bytes apart, 32 keys per MMA = 4096 bytes
+          const uint64_t v_desc = smem_desc_sw128(v_smem + s * M_KV_BYTES, 16, 1024);
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-          const int g = 2 * (R & 1) + h;
-          const uint32_t p_tmem = tmem_base + M_P_COL + M_P_STRIDE * g;
-          if (!mbar_wait(p_full(g), it_par, p.status, WK_ERR_TIMEOUT_P)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
+          for (int h = 0; h < 2; ++h) {
+            const int g = 2 * (gr & 1) + h;
+            const uint32_t p_tmem = tmem_base + M_P_COL + M_P_STRIDE * g;
+            if (!mbar_wait(p_full(g), it_par, p.status, WK_ERR_TIMEOUT_P)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 2; ++k) {
-            // P: 32 e4m3 per K step = 8 TMEM columns; scale byte k of the row's scale word
-            mma_mxf8_ts(o_tmem, p_tmem + 8 * k, v_desc + 256 * (2 * h + k), make_idesc_mx_major(BM, D, k, 0, 0, 1),
-                        p_tmem + M_SFA_OFF, tmem_base + M_SFB_COL, (R | h | k) != 0);
+            for (int k = 0; k < 2; ++k) {
+              // P: 32 e4m3 per K step = 8 TMEM columns; scale byte k of the row's scale word
+              mma_mxf8_ts(o_tmem, p_tmem + 8 * k, v_desc + 256 * (2 * h + k), make_idesc_mx_major(BM, D, k, 0, 0, 1),
+                          p_tmem + M_SFA_OFF, tmem_base + M_SFB_COL, (R | h | k) != 0);
+            }
+            tc_commit(p_empty(g));
+            if (h == 1) tc_commit(v_empty(s));
           }
-          tc_commit(p_empty(g));
-          if (h == 1) tc_commit(v_empty(s));
         }
+        if (ok) tc_commit(o_full);
+        }
+        if (!ok || !next_block()) break;
       }
-      if (ok) tc_commit(o_full);
     }
     __syncwarp();
   } else {
-    // Group g works on S buffer g >> 1 (rounds g >> 1, (g >> 1) + 2, ...) and there on keys [64 (g & 1), + 64).
+    // Group g works on S buffer g >> 1 (every second round) and there on keys [64 (g & 1), + 64).
     // Inside a group one thread owns one query row.
     const int quad = warp & 3;  // TMEM lanes [32 quad, 32 quad + 32) are the ones this warp may touch
     const int grp = (warp - 3) >> 2;
     const int buf = grp >> 1, half = grp & 1;
     const int r = quad * 32 + lane;  // row of the tile == TMEM lane
-    const int row = m0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t s_tmem = tmem_base + lane_addr + 128 * buf + 64 * half;
     const uint32_t p_tmem = tmem_base + lane_addr + M_P_COL + M_P_STRIDE * grp;
     const uint32_t o_tmem = tmem_base + lane_addr + M_O_COL;
-    const uint32_t x_ref = xch_smem + r * 4;
-    const int sc = b * p.Hkv + hkv;
-    const float beta = p.softmax_scale * p.q_descale[sc] * p.k_descale[sc] * 1.4426950408889634f;
-    const float sv = p.v_descale[sc];
-    const int row_limit = p.causal ? row + shift : nk - 1;  // last visible key of this row
-    // m_ref: reference exponent of the row, fixed by the first tile (O and the sums are in units of 2^-m_ref)
-    // l: sum of the exact probabilities over this group's tiles (normaliser of O, lse, pmax)
-    float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
-    bool ok = true;
-    bool met = false;  // the one-time meeting of the two groups has taken place
+    int ci = -1;
+    uint32_t gr0 = 0;  // rounds of the blocks before this one
+    bool unit_scales_set = false;
 
-    for (int R = buf; R < n_rounds; R += 2) {
-      const int it = R >> 1;
-      const int j = 2 * R + half;  // the 64-key tile
-      if (!mbar_wait_warp(s_full(buf), it & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      // the whole row of the tile into registers, then the S buffer goes back to the MMA thread
-      uint32_t sraw[2][32];
-      tmem_ld32(s_tmem, sraw[0]);
-      tmem_ld32(s_tmem + 32, sraw[1]);
-      tc_wait_ld();
-      tc_fence_before();
-      mbar_arrive(s_free(buf));
+    for (;;) {
+      if (valid) {
+      ++ci;
+      const uint32_t xch = xch_smem + (ci & 1) * M_XCH_HALF;
+      const uint32_t x_ref = xch + r * 4;
+      const int row = it.m0 + r;
+      const int sc = it.b * p.Hkv + it.hkv;
+      const float beta = p.softmax_scale * p.q_descale[sc] * p.k_descale[sc] * 1.4426950408889634f;
+      const int row_limit = p.causal ? row + it.shift : it.nk - 1;  // last visible key of this row
+      // m_ref: reference exponent of the row, fixed by the first tile (O and the sums are in units of 2^-m_ref)
+      // l: sum of the exact probabilities over this group's tiles (normaliser of O, lse, pmax)
+      float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
+      bool have_ref = false;
 
-      const int key0 = j * BN;
-      const bool tile_masked = (key0 + BN > nk) || (p.causal && key0 + BN - 1 > m0 + shift);
-      const int limit = min(row_limit, nk - 1) - key0;  // columns > limit are masked
-      if (tile_masked) {
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i > limit) sraw[c][i] = 0xff800000u;  // -inf
-      }
-      float cm[2];
-      cm[0] = block_max(sraw[0]) * beta;  // beta > 0 (checked on the host)
-      cm[1] = block_max(sraw[1]) * beta;
-      if (j == 0) {
-        // the row reference: maximum of the first tile (every row that sees any key sees one here)
-        m_ref = fmaxf(cm[0], cm[1]);
-        asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_ref), "f"(m_ref) : "memory");
-      }
-      if (it == 0) {
-        // the groups meet once: the others pick up the reference the first one has just published
-        asm volatile("bar.sync 1, 512;" ::: "memory");
-        met = true;
-        if (grp != 0) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(m_ref) : "r"(x_ref) : "memory");
-      } else {
-        // this group's P region is free once the P.V product of its previous tile has completed
-        if (!mbar_wait_warp(p_empty(grp), (it - 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+      for (uint32_t gr = gr0 + ((buf ^ gr0) & 1); gr < gr0 + it.n_rounds; gr += 2) {
+        const uint32_t n = gr >> 1;  // this group's tiles so far
+        const int j = 2 * static_cast<int>(gr - gr0) + half;  // the 64-key tile
+        if (!mbar_wait_warp(s_full(buf), n & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
           ok = false;
           break;
         }
         tc_fence_after();
-      }
+        // the whole row of the tile into registers, then the S buffer goes back to the MMA thread
+        uint32_t sraw[2][32];
+        tmem_ld32(s_tmem, sraw[0]);
+        tmem_ld32(s_tmem + 32, sraw[1]);
+        tc_wait_ld();
+        tc_fence_before();
+        mbar_arrive(s_free(buf));
 
-      uint32_t sf_word = 0;
+        const int key0 = j * BN;
+        const bool tile_masked = (key0 + BN > it.nk) || (p.causal && key0 + BN - 1 > it.m0 + it.shift);
+        const int limit = min(row_limit, it.nk - 1) - key0;  // columns > limit are masked
+        if (tile_masked) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        m_true = fmaxf(m_true, cm[c]);
-        const bool live = cm[c] > -INFINITY;
-        float kf = live ? ceilf(cm[c] - m_ref) : 0.f;  // block exponent relative to the row reference
-        if (kf > MAX_BLOCK_EXP) {
-          // the scores have outgrown the first tile's maximum by more than 2^100: not representable here
-          atomicCAS(p.status, 0, WK_ERR_RANGE);
-          kf = MAX_BLOCK_EXP;
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i > limit) sraw[c][i] = 0xff800000u;  // -inf
         }
-        const float bias = live ? (static_cast<float>(P_OFFSET) - kf) - m_ref : 0.f;
-        uint32_t w[8], wl[8];
-        float sum_exact;
-        softmax_block<false>(sraw[c], beta, bias, w, wl, sum_exact);
-        tmem_st8(p_tmem + c * 8, w);
-        int sf = live ? 127 + static_cast<int>(kf) - P_OFFSET : 0;
-        sf = min(max(sf, 0), 254);
-        const float blk_scale = __uint_as_float(static_cast<uint32_t>(sf) << 23);
-        if (live) l = fmaf(sum_exact, blk_scale, l);
-        sf_word |= static_cast<uint32_t>(sf) << (8 * c);
-      }
-      // scale factors straight into TMEM: the MMA reads the scale of row r from lane r, column r / 32
-      tmem_st1(p_tmem + M_SFA_OFF + quad, sf_word);
-      if (it == 0) {
-        tmem_st4(tmem_base + lane_addr + M_SFB_COL, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-      }
-      tc_wait_st();
-      tc_fence_before();
-      mbar_arrive(p_full(grp));
-    }
-    if (!met) {
-      // this group had no round (or gave up on a wait): it still owes the others the meeting above
-      asm volatile("bar.sync 1, 512;" ::: "memory");
-    }
+        float cm[2];
+        cm[0] = block_max(sraw[0]) * beta;  // beta > 0 (checked on the host)
+        cm[1] = block_max(sraw[1]) * beta;
+        if (j == 0) {
+          // the row reference: maximum of the first tile (every row that sees any key sees one here)
+          m_ref = fmaxf(cm[0], cm[1]);
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(x_ref), "f"(m_ref) : "memory");
+          mbar_arrive(ref_full);
+          have_ref = true;
+        } else if (!have_ref) {
+          // this group's first tile of the block: pick up the reference the first group has published
+          if (!mbar_wait_warp(ref_full, ci & 1, p.status, WK_ERR_TIMEOUT_P)) {
+            ok = false;
+            break;
+          }
+          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(m_ref) : "r"(x_ref) : "memory");
+          have_ref = true;
+        }
+        if (n >= 1) {
+          // this group's P region is free once the P.V product of its previous tile has completed
+          if (!mbar_wait_warp(p_empty(grp), (n - 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+        }
 
-    // epilogue: the groups add up their sums; group g stores head-dim columns [32 g, 32 g + 32)
-    if (ok) ok = mbar_wait_warp(o_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
-    asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch_smem + (1 + 2 * grp) * BM * 4 + r * 4), "f"(l) : "memory");
-    asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch_smem + (2 + 2 * grp) * BM * 4 + r * 4), "f"(m_true) : "memory");
-    asm volatile("bar.sync 1, 512;" ::: "memory");
-    {
+        uint32_t sf_word = 0;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          m_true = fmaxf(m_true, cm[c]);
+          const bool live = cm[c] > -INFINITY;
+          float kf = live ? ceilf(cm[c] - m_ref) : 0.f;  // block exponent relative to the row reference
+          if (kf > MAX_BLOCK_EXP) {
+            // the scores have outgrown the first tile's maximum by more than 2^100: not representable here
+            atomicCAS(p.status, 0, WK_ERR_RANGE);
+            kf = MAX_BLOCK_EXP;
+          }
+          const float bias = live ? (static_cast<float>(P_OFFSET) - kf) - m_ref : 0.f;
+          uint32_t w[8], wl[8];
+          float sum_exact;
+          softmax_block<false>(sraw[c], beta, bias, w, wl, sum_exact);
+          tmem_st8(p_tmem + c * 8, w);
+          int sf = live ? 127 + static_cast<int>(kf) - P_OFFSET : 0;
+          sf = min(max(sf, 0), 254);
+          const float blk_scale = __uint_as_float(static_cast<uint32_t>(sf) << 23);
+          if (live) l = fmaf(sum_exact, blk_scale, l);
+          sf_word |= static_cast<uint32_t>(sf) << (8 * c);
+        }
+        // scale factors straight into TMEM: the MMA reads the scale of row r from lane r, column r / 32
+        tmem_st1(p_tmem + M_SFA_OFF + quad, sf_word);
+        if (!unit_scales_set) {
+          tmem_st4(tmem_base + lane_addr + M_SFB_COL, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+          unit_scales_set = true;
+        }
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(p_full(grp));
+      }
+      gr0 += it.n_rounds;
+      if (!ok) break;
+
+      // the block's output: the groups add up their sums; group g stores head-dim columns [32 g, 32 g + 32)
+      asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch + (1 + 2 * grp) * BM * 4 + r * 4), "f"(l) : "memory");
+      asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch + (2 + 2 * grp) * BM * 4 + r * 4), "f"(m_true) : "memory");
+      mbar_arrive(sum_meet);
+      if (!mbar_wait_warp(sum_meet, ci & 1, p.status, WK_ERR_TIMEOUT_P)) break;
       l = 0.f;
       m_true = -INFINITY;
 #pragma unroll
       for (int g = 0; g < M_GROUPS; ++g) {  // same order in every group: identical sums
         float l_g, mt_g;
-        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_g) : "r"(xch_smem + (1 + 2 * g) * BM * 4 + r * 4) : "memory");
-        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(mt_g) : "r"(xch_smem + (2 + 2 * g) * BM * 4 + r * 4) : "memory");
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_g) : "r"(xch + (1 + 2 * g) * BM * 4 + r * 4) : "memory");
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(mt_g) : "r"(xch + (2 + 2 * g) * BM * 4 + r * 4) : "memory");
         l += l_g;
         m_true = fmaxf(m_true, mt_g);
       }
-      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(m_ref) : "r"(x_ref) : "memory");
-    }
-    if (ok) {
+      if (!mbar_wait_warp(o_full, ci & 1, p.status, WK_ERR_TIMEOUT_MMA)) break;
       tc_fence_after();
       const bool empty = !(l > 0.f);
-      const float inv = empty ? 0.f : sv / l;
+      const float inv = empty ? 0.f : p.v_descale[sc] / l;
       const int col0 = 32 * grp;
-      __nv_bfloat16* out_row = p.out + b * p.out_stride_b + hq * p.out_stride_h +
+      __nv_bfloat16* out_row = p.out + it.b * p.out_stride_b + it.hq * p.out_stride_h +
                                static_cast<int64_t>(row) * p.out_stride_n + col0;
       {
         uint32_t v[32];
         tmem_ld32(o_tmem + col0, v);
         tc_wait_ld();
+        // O is in registers: the next block's first P.V product may overwrite it
+        tc_fence_before();
+        mbar_arrive(o_free);
         if (row < p.Nq) {
           uint4* dst = reinterpret_cast<uint4*>(out_row);
 #pragma unroll
@@ -780,11 +927,13 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         }
       }
       if (p.write_lse && grp == 0 && row < p.Nq) {
-        const int64_t off = b * p.lse_stride_b + hq * p.lse_stride_h + row;
+        const int64_t off = it.b * p.lse_stride_b + it.hq * p.lse_stride_h + row;
         const float lse = empty ? INFINITY : m_ref + log2f(l);
         p.lse[off] = p.lse_natural ? lse * 0.6931471805599453f : lse;
         p.pmax[off] = empty ? 0.f : exp2f(m_true - lse);
       }
+      }
+      if (!ok || !next_block()) break;
     }
   }
 
@@ -873,11 +1022,11 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
 
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<false>), SMEM_BYTES)) return WK_E_CUDA;
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_wide_kernel), M_SMEM_BYTES)) return WK_E_CUDA;
-  // ctas_per_sm: 0 picks by the number of keys.  The wide kernel pays off on long sequences; measured with equal
-  // work (causal / full, TFLOP/s): 2048 keys 818 / 1088 against 975 / 1258 of the two-CTA kernel, 4096 keys
-  // 1047 / 1304 against 1132 / 1344, 8192 keys 1220 / 1457 against 1174 / 1353, 16384 keys (causal) 1384 against 1118
+  // ctas_per_sm: 0 picks by the number of keys.  The wide kernel pays off on longer sequences; measured with equal
+  // work (causal / full, TFLOP/s): 2048 keys 949 / 1235 against 963 / 1258 of the two-CTA kernel, 4096 keys
+  // 1166 / 1395 against 1131 / 1344, 8192 keys 1296 / 1514 against 1169 / 1353, 16384 keys (causal) 1417 against 1108
   if (a->ctas_per_sm < 0 || a->ctas_per_sm > 2) return WK_E_ARG;
-  const bool wide = a->ctas_per_sm == 1 || (a->ctas_per_sm == 0 && a->Nk >= 8192);
+  const bool wide = a->ctas_per_sm == 1 || (a->ctas_per_sm == 0 && a->Nk >= 4096);
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<true>), SMEM_BYTES)) return WK_E_CUDA;
   const int num_m = (a->Nq + BM - 1) / BM;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -903,6 +1052,7 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
     p.m_first = main_first;
     dim3 grid(num_m - main_first, a->Hq, a->B);
     if (wide) {
+      // one CTA per query block in the grid; the CTAs that start take over the blocks of those that have not yet
       attn_fwd_fp8_wide_kernel<<<grid, M_THREADS, M_SMEM_BYTES, st>>>(tq, tk128, tv128, p);
     } else {
       attn_fwd_fp8_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
