@@ -38,6 +38,8 @@
 // Tensor-core bound: 4 . B . Hq . Nq . Nk . d flops (half of that when causal).
 #include <math.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "host_common.h"
 
@@ -183,7 +185,13 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   }
   // With few keys the e4m3 rounding of P does not average out; such blocks carry P as two e4m3 terms
   // (value + 2^-4 . residual) at the price of a second P.V product.
-  if ((n_tiles <= RESID_MAX_TILES) != RESID) return;
+  // The two-term launch comes first in the stream and lets the main launch start beside it; the main launch in
+  // turn does not end before the two-term one has (both write parts of the same output).
+  if (RESID) pdl_launch_dependents();
+  if ((n_tiles <= RESID_MAX_TILES) != RESID) {
+    if (!RESID) pdl_wait();
+    return;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -447,6 +455,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (!RESID) pdl_wait();
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -487,7 +496,8 @@ constexpr int M_SFB_COL = 352;
 constexpr int M_O_COL = 384;
 constexpr int M_XCH_HALF = (1 + 2 * M_GROUPS) * BM * 4;  // row reference plus (l, m_true) of each group
 constexpr int M_XCH_BYTES = 2 * M_XCH_HALF;              // blocks alternate between the halves
-constexpr int M_SMEM_BYTES = 2 * Q_BYTES + 2 * KV_STAGES * M_KV_BYTES + M_XCH_BYTES + 1024 + 512;
+constexpr int M_FIN_BYTES = M_SOFTMAX_THREADS * 16;  // what a thread remembers of a finished block
+constexpr int M_SMEM_BYTES = 2 * Q_BYTES + 2 * KV_STAGES * M_KV_BYTES + M_XCH_BYTES + M_FIN_BYTES + 1024 + 512;
 
 struct WideItem {
   int hq, b, hkv, m0, nk, shift, n_tiles, n_rounds;
@@ -540,6 +550,66 @@ __device__ __forceinline__ bool launch_control_answer(uint32_t resp, uint32_t& x
   return got != 0;
 }
 
+// Stores a finished query block's output (called by every softmax thread: group `grp` stores head-dim columns
+// [32 grp, 32 grp + 32) of row `r`) once all groups have published their sums in `xch` and the last P.V product has
+// completed; false if a wait gave up.  Kept out of line: it runs once per block, and inlined into the tile loop it
+// cost that loop registers.
+__device__ __noinline__ bool wide_store_output(const FwdParams& p, uint32_t xch, uint32_t fin_addr, uint32_t sum_meet,
+                                               uint32_t o_full, uint32_t o_free, uint32_t o_tmem, int grp, int r,
+                                               int fin_ci) {
+  int row, b, hq;
+  float m_ref;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(row), "=r"(b), "=r"(hq), "=f"(m_ref)
+               : "r"(fin_addr)
+               : "memory");
+  const int sc = b * p.Hkv + hq / (p.Hq / p.Hkv);
+  if (!mbar_wait_warp(sum_meet, fin_ci & 1, p.status, WK_ERR_TIMEOUT_P)) return false;
+  float l = 0.f, m_true = -INFINITY;
+#pragma unroll
+  for (int g = 0; g < M_GROUPS; ++g) {  // same order in every group: identical sums
+    float l_g, mt_g;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_g) : "r"(xch + (1 + 2 * g) * BM * 4 + r * 4) : "memory");
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(mt_g) : "r"(xch + (2 + 2 * g) * BM * 4 + r * 4) : "memory");
+    l += l_g;
+    m_true = fmaxf(m_true, mt_g);
+  }
+  if (!mbar_wait_warp(o_full, fin_ci & 1, p.status, WK_ERR_TIMEOUT_MMA)) return false;
+  tc_fence_after();
+  const bool empty = !(l > 0.f);
+  const float inv = empty ? 0.f : p.v_descale[sc] / l;
+  const int col0 = 32 * grp;
+  __nv_bfloat16* out_row =
+      p.out + b * p.out_stride_b + hq * p.out_stride_h + static_cast<int64_t>(row) * p.out_stride_n + col0;
+  {
+    uint32_t v[32];
+    tmem_ld32(o_tmem + col0, v);
+    tc_wait_ld();
+    // O is in registers: the next block's first P.V product may overwrite it
+    tc_fence_before();
+    mbar_arrive(o_free);
+    if (row < p.Nq) {
+      uint4* dst = reinterpret_cast<uint4*>(out_row);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 w;
+        w.x = pack_bf16x2(__uint_as_float(v[8 * i + 0]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+        w.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+        w.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+        w.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+        dst[i] = w;
+      }
+    }
+  }
+  if (p.write_lse && grp == 0 && row < p.Nq) {
+    const int64_t off = b * p.lse_stride_b + hq * p.lse_stride_h + row;
+    const float lse = empty ? INFINITY : m_ref + log2f(l);
+    p.lse[off] = p.lse_natural ? lse * 0.6931471805599453f : lse;
+    p.pmax[off] = empty ? 0.f : exp2f(m_true - lse);
+  }
+  return true;
+}
+
 __global__ void __launch_bounds__(M_THREADS, 1)
 attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FwdParams p) {
@@ -549,7 +619,8 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   const uint32_t k_smem = q_smem + 2 * Q_BYTES;
   const uint32_t v_smem = k_smem + KV_STAGES * M_KV_BYTES;
   const uint32_t xch_smem = v_smem + KV_STAGES * M_KV_BYTES;  // exchange between the softmax groups
-  const uint32_t bar_base = xch_smem + M_XCH_BYTES;
+  const uint32_t fin_smem = xch_smem + M_XCH_BYTES;
+  const uint32_t bar_base = fin_smem + M_FIN_BYTES;
   auto q_full = [&](int i) { return bar_base + 8u * i; };
   auto q_empty = [&](int i) { return bar_base + 8u * (2 + i); };
   auto k_full = [&](int s) { return bar_base + 8u * (4 + s); };
@@ -782,6 +853,17 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     uint32_t gr0 = 0;  // rounds of the blocks before this one
     bool unit_scales_set = false;
 
+    // The output of a block is stored by the groups while they are already at work on the next block: its last P.V
+    // products are still running when a group has finished its last tile, so the group first does its first tile of
+    // the next block and stores the finished block's output after that (wide_store_output; what it needs of the
+    // finished block waits in shared memory, not in registers of the tile loop).
+    const uint32_t my_fin = fin_smem + (threadIdx.x - 96) * 16;
+    bool pending = false;
+    auto store_output = [&](int fin_ci) {
+      return wide_store_output(p, xch_smem + (fin_ci & 1) * M_XCH_HALF, my_fin, sum_meet, o_full, o_free, o_tmem, grp, r,
+                               fin_ci);
+    };
+
     for (;;) {
       if (valid) {
       ++ci;
@@ -880,61 +962,30 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(p_full(grp));
+        if (pending) {
+          // first tile after a finished block: its P is handed over (the P.V product waits for O to be read
+          // anyway), now that block's output
+          pending = false;
+          if (!store_output(ci - 1)) {
+            ok = false;
+            break;
+          }
+        }
       }
       gr0 += it.n_rounds;
       if (!ok) break;
 
-      // the block's output: the groups add up their sums; group g stores head-dim columns [32 g, 32 g + 32)
+      // the groups' sums; each group stores head-dim columns [32 g, 32 g + 32) of the output later (store_output)
       asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch + (1 + 2 * grp) * BM * 4 + r * 4), "f"(l) : "memory");
       asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch + (2 + 2 * grp) * BM * 4 + r * 4), "f"(m_true) : "memory");
       mbar_arrive(sum_meet);
-      if (!mbar_wait_warp(sum_meet, ci & 1, p.status, WK_ERR_TIMEOUT_P)) break;
-      l = 0.f;
-      m_true = -INFINITY;
-#pragma unroll
-      for (int g = 0; g < M_GROUPS; ++g) {  // same order in every group: identical sums
-        float l_g, mt_g;
-        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_g) : "r"(xch + (1 + 2 * g) * BM * 4 + r * 4) : "memory");
-        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(mt_g) : "r"(xch + (2 + 2 * g) * BM * 4 + r * 4) : "memory");
-        l += l_g;
-        m_true = fmaxf(m_true, mt_g);
-      }
-      if (!mbar_wait_warp(o_full, ci & 1, p.status, WK_ERR_TIMEOUT_MMA)) break;
-      tc_fence_after();
-      const bool empty = !(l > 0.f);
-      const float inv = empty ? 0.f : p.v_descale[sc] / l;
-      const int col0 = 32 * grp;
-      __nv_bfloat16* out_row = p.out + it.b * p.out_stride_b + it.hq * p.out_stride_h +
-                               static_cast<int64_t>(row) * p.out_stride_n + col0;
-      {
-        uint32_t v[32];
-        tmem_ld32(o_tmem + col0, v);
-        tc_wait_ld();
-        // O is in registers: the next block's first P.V product may overwrite it
-        tc_fence_before();
-        mbar_arrive(o_free);
-        if (row < p.Nq) {
-          uint4* dst = reinterpret_cast<uint4*>(out_row);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(v[8 * i + 0]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
-            w.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
-            w.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
-            w.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
-            dst[i] = w;
-          }
-        }
-      }
-      if (p.write_lse && grp == 0 && row < p.Nq) {
-        const int64_t off = it.b * p.lse_stride_b + it.hq * p.lse_stride_h + row;
-        const float lse = empty ? INFINITY : m_ref + log2f(l);
-        p.lse[off] = p.lse_natural ? lse * 0.6931471805599453f : lse;
-        p.pmax[off] = empty ? 0.f : exp2f(m_true - lse);
-      }
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_fin), "r"(row), "r"(it.b), "r"(it.hq), "f"(m_ref)
+                   : "memory");
+      pending = true;
       }
       if (!ok || !next_block()) break;
     }
+    if (ok && pending) store_output(ci);
   }
 
   tc_fence_before();
@@ -943,6 +994,7 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     tc_fence_after();
     tmem_dealloc(tmem_base, M_TMEM_COLS);
   }
+  pdl_wait();  // does not end before the two-term launch, which started before this one, has
 }
 
 }  // namespace
@@ -1048,21 +1100,36 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
   }
   const int main_first = a->seqused_k ? 0 : m_split;
   const int resid_count = a->seqused_k ? num_m : m_split;
-  if (num_m - main_first > 0) {
-    p.m_first = main_first;
-    dim3 grid(num_m - main_first, a->Hq, a->B);
-    if (wide) {
-      // one CTA per query block in the grid; the CTAs that start take over the blocks of those that have not yet
-      attn_fwd_fp8_wide_kernel<<<grid, M_THREADS, M_SMEM_BYTES, st>>>(tq, tk128, tv128, p);
-    } else {
-      attn_fwd_fp8_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
-    }
-    if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
-  }
+  // The short blocks first: their CTAs are many and brief, and the main launch, allowed to start while they still
+  // run (programmatic stream serialisation), fills the SMs as they leave instead of waiting for the last of them.
   if (resid_count > 0) {
     p.m_first = 0;
     dim3 grid(resid_count, a->Hq, a->B);
     attn_fwd_fp8_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
+    if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+  }
+  if (num_m - main_first > 0) {
+    p.m_first = main_first;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_m - main_first, a->Hq, a->B);
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = resid_count > 0 ? 1 : 0;
+    cudaError_t e;
+    if (wide) {
+      // one CTA per query block in the grid; the CTAs that start take over the blocks of those that have not yet
+      cfg.blockDim = dim3(M_THREADS);
+      cfg.dynamicSmemBytes = M_SMEM_BYTES;
+      e = cudaLaunchKernelEx(&cfg, attn_fwd_fp8_wide_kernel, tq, tk128, tv128, p);
+    } else {
+      cfg.blockDim = dim3(THREADS);
+      cfg.dynamicSmemBytes = SMEM_BYTES;
+      e = cudaLaunchKernelEx(&cfg, attn_fwd_fp8_kernel<false>, tq, tk, tv, p);
+    }
+    if (e != cudaSuccess) return WK_E_CUDA;
   }
   return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
 }

@@ -134,6 +134,16 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, in
 }
 
 // ---------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with programmatic stream serialisation may start as soon as
+// every CTA of the kernel before it in the stream has executed launch_dependents (or exited), and learns of that
+// kernel's completion only through wait.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor): every CTA loads its own tiles.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
