@@ -33,8 +33,8 @@ NOMINAL = {"fp8": 4500.0, "bf16": 2250.0}  # dense TFLOP/s, B200 data sheet
 # dram__bytes_read.sum + dram__bytes_write.sum per benchmark step, from the ncu captures summarised under
 # profiles/ (attention figures: captured at half the batch and doubled, traffic grows with batch x heads)
 DRAM_TRAFFIC_BYTES = {
-    "attn_fwd": 2 * (96.5e6 + 30.3e6 + 12.6e6),
-    "attn_fwd_small": 96.5e6 + 30.3e6 + 12.6e6,
+    "attn_fwd": 2 * (96.5e6 + 29.5e6 + 12.6e6),
+    "attn_fwd_small": 96.5e6 + 29.5e6 + 12.6e6,
     "attn_gqa": 4 * (83.1e6 + 84.5e6),
     "attn_gqa_small": 83.1e6 + 84.5e6,
     "attn_bwd": 2 * (156.5e6 + 226.4e6 + 177.7e6),

@@ -114,7 +114,7 @@ def make_attn_fwd(
         softmax_scale: Scale on the logits, positive. Defaults to ``1 / sqrt(d)``.
         ctas_per_sm: FP8 inputs: 2 runs the kernel with two CTAs per SM and 64-key tiles, 1 the one with a single
             CTA per SM, 128-key rounds and four softmax groups, which is the faster one on long sequences. ``None``
-            takes the tuned value for the shape (``autotune_attn_fwd``), else 1 from 4096 keys on and 2 below.
+            takes the tuned value for the shape (``autotune_attn_fwd``), else 1 from 2048 keys on and 2 below.
         num_stages, pipelined, block_n, block_m, warp_rows, tile_local, lpt, tma, warp_spec, split_kv:
             Other tuning options of the reference's SM80-SM120 kernels; accepted and ignored.
         out: Output buffer, ``[B, Hq, Nq, d]`` bf16 with last stride 1 and even other strides. ``None`` allocates one

@@ -1,6 +1,9 @@
 // FP8 (e4m3) flash-attention forward for sm_100a, head dimension 128.
 //
-// One CTA = 128 queries of one (batch, query head), two CTAs per SM, key tiles of 64.
+// Two kernels share the numerics described below.  From 2048 keys on (and on request) the work goes to the wide
+// kernel further down: one persistent CTA per SM with four softmax groups.  Shorter sequences, and always the query
+// blocks that see at most 512 keys (two-term P), go to the kernel described first:
+// one CTA = 128 queries of one (batch, query head), two CTAs per SM, key tiles of 64.
 // 320 threads:
 //   warp 0      TMA producer: Q tile once, then K and V tiles (64 keys x 128 bytes,
 //               128-byte swizzle) into four-stage rings
@@ -1074,11 +1077,12 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
 
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<false>), SMEM_BYTES)) return WK_E_CUDA;
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_wide_kernel), M_SMEM_BYTES)) return WK_E_CUDA;
-  // ctas_per_sm: 0 picks by the number of keys.  The wide kernel pays off on longer sequences; measured with equal
-  // work (causal / full, TFLOP/s): 2048 keys 949 / 1235 against 963 / 1258 of the two-CTA kernel, 4096 keys
-  // 1166 / 1395 against 1131 / 1344, 8192 keys 1296 / 1514 against 1169 / 1353, 16384 keys (causal) 1417 against 1108
+  // ctas_per_sm: 0 picks by the number of keys.  Measured with equal work (causal / full, TFLOP/s), the wide kernel
+  // against the two-CTA kernel: 1024 keys 723 / 1066 against 723 / 1070, 2048 keys 1012 / 1289 against 989 / 1253,
+  // 4096 keys 1215 / 1412 against 1149 / 1342, 8192 keys 1321 / 1488 against 1192 / 1348, 16384 keys (causal) 1417
+  // against 1140
   if (a->ctas_per_sm < 0 || a->ctas_per_sm > 2) return WK_E_ARG;
-  const bool wide = a->ctas_per_sm == 1 || (a->ctas_per_sm == 0 && a->Nk >= 4096);
+  const bool wide = a->ctas_per_sm == 1 || (a->ctas_per_sm == 0 && a->Nk >= 2048);
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<true>), SMEM_BYTES)) return WK_E_CUDA;
   const int num_m = (a->Nq + BM - 1) / BM;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
