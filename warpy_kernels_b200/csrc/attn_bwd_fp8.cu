@@ -121,6 +121,72 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const PrepParams p) 
   }
 }
 
+// The same for tensors whose strides are multiples of 8 elements: four query rows per warp, 8 lanes per row and 16
+// consecutive elements per lane, read with 16-byte loads (64 bytes in flight per thread instead of 16: the kernel is
+// HBM-bound and the one-row-per-warp form reached a third of the copy bandwidth).
+__global__ void __launch_bounds__(256) attn_bwd_prep4_kernel(const PrepParams p) {
+  const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
+  const int sub = lane & 7;
+  const int64_t rows = static_cast<int64_t>(p.B) * p.Hq * p.nq_pad;  // a multiple of 128
+  if (warp * 4 >= rows) return;
+  const int64_t row_id = warp * 4 + (lane >> 3);
+  const int i = static_cast<int>(row_id % p.nq_pad);
+  const int h = static_cast<int>((row_id / p.nq_pad) % p.Hq);
+  const int b = static_cast<int>(row_id / (static_cast<int64_t>(p.nq_pad) * p.Hq));
+  const bool live = i < p.Nq;  // padding rows take part in the shuffles with zeros
+  uint4 draw[2] = {}, oraw[2] = {};
+  if (live) {
+    const uint4* dsrc = reinterpret_cast<const uint4*>(p.dout + b * p.do_sb + h * p.do_sh +
+                                                       static_cast<int64_t>(i) * p.do_sn + sub * 16);
+    const uint4* osrc =
+        reinterpret_cast<const uint4*>(p.out + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(i) * p.o_sn + sub * 16);
+    draw[0] = dsrc[0];
+    draw[1] = dsrc[1];
+    oraw[0] = osrc[0];
+    oraw[1] = osrc[1];
+  }
+  const uint32_t dw[8] = {draw[0].x, draw[0].y, draw[0].z, draw[0].w, draw[1].x, draw[1].y, draw[1].z, draw[1].w};
+  const uint32_t ow[8] = {oraw[0].x, oraw[0].y, oraw[0].z, oraw[0].w, oraw[1].x, oraw[1].y, oraw[1].z, oraw[1].w};
+  uint32_t amax = 0;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) amax = max(amax, max((dw[c] << 16) & 0x7fffffffu, dw[c] & 0x7fff0000u));
+#pragma unroll
+  for (int off = 4; off > 0; off >>= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  // the MXFP8 quantiser's scale: the row peak lands in (224, 448]
+  int e = static_cast<int>((amax + 0x1fffffu) >> 23) - 8;
+  e = min(max(e, 0), 254);
+  const float inv = __uint_as_float(static_cast<uint32_t>(max(254 - e, 1)) << 23);
+  const float log2_g = static_cast<float>(e - 127);  // g = 2^(e - 127) is the scale the e4m3 codes carry
+  uint32_t codes[4];
+  float dsum = 0.f;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint16_t cc = cvt_e4m3x2(__uint_as_float(dw[c] << 16) * inv, __uint_as_float(dw[c] & 0xffff0000u) * inv);
+    float q0, q1;
+    unpack_e4m3x2(cc, q0, q1);
+    dsum += q0 * __uint_as_float(ow[c] << 16) + q1 * __uint_as_float(ow[c] & 0xffff0000u);
+    if (c & 1) codes[c >> 1] |= static_cast<uint32_t>(cc) << 16;
+    else codes[c >> 1] = cc;
+  }
+#pragma unroll
+  for (int off = 4; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
+  // the two values of row i sit 128 floats apart inside the row's tile of 128
+  float* stat = p.qstat + ((static_cast<int64_t>(b) * p.Hq + h) * p.nq_pad + (i & ~127)) * 2 + (i & 127);
+  if (!live) {
+    // padding rows: lse = +inf makes every probability zero
+    if (sub < 2) stat[sub * 128] = sub == 0 ? -INFINITY : 0.f;
+    return;
+  }
+  uint8_t* dst = p.do8 + ((static_cast<int64_t>(b) * p.Hq + h) * p.Nq + i) * D + sub * 16;
+  *reinterpret_cast<uint4*>(dst) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+  if (sub == 0) {
+    const float L = p.lse[b * p.lse_sb + h * p.lse_sh + i];
+    stat[0] = log2_g - L;
+    stat[128] = -dsum;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // helpers shared by the two main kernels
 // ---------------------------------------------------------------------------
@@ -212,7 +278,8 @@ constexpr int A_STAT_BYTES = BM * 8;
 constexpr int A_STAGE_BYTES = 2 * TILE_BYTES + A_STAT_BYTES;
 // Requested size is padded past half an SM's shared memory: each CTA allocates all 512 TMEM columns, so a second
 // resident CTA could only spin in tcgen05.alloc.
-constexpr int A_SMEM_NEED = 2 * TILE_BYTES + A_STAGES * A_STAGE_BYTES + 3 * SF_BYTES + 1024 + 256;
+constexpr int SCHED_SLOTS = 4;  // answers of the launch control in flight
+constexpr int A_SMEM_NEED = 4 * TILE_BYTES + A_STAGES * A_STAGE_BYTES + 1024 + 512;
 constexpr int A_SMEM_BYTES = A_SMEM_NEED > 120 * 1024 ? A_SMEM_NEED : 120 * 1024;
 constexpr int A_ST_COL = 0, A_DPT_COL = 128, A_DV_COL = 256, A_DK_COL = 384;
 // scale-factor columns inside the consumed S^T columns; the two threads of a row own 4 columns each
@@ -225,38 +292,36 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                      const __grid_constant__ BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t k_smem = smem_base;
-  const uint32_t v_smem = k_smem + TILE_BYTES;
-  const uint32_t stage_smem = v_smem + TILE_BYTES;  // per stage: Q tile, dO tile, row records
-  const uint32_t sfp_smem = stage_smem + A_STAGES * A_STAGE_BYTES;
-  const uint32_t sfu_smem = sfp_smem + SF_BYTES;
-  const uint32_t sfd_smem = sfu_smem + SF_BYTES;
-  const uint32_t bar_base = sfd_smem + SF_BYTES;
-  const uint32_t kv_full = bar_base;
-  auto q_full = [&](int s) { return bar_base + 8u * (1 + s); };
-  auto q_empty = [&](int s) { return bar_base + 8u * (1 + A_STAGES + s); };
+  // K and V of a key block: two buffers, the blocks of the CTA's list alternate between them
+  auto k_smem = [&](int kb) { return smem_base + kb * 2 * TILE_BYTES; };
+  auto v_smem = [&](int kb) { return smem_base + kb * 2 * TILE_BYTES + TILE_BYTES; };
+  const uint32_t stage_smem = smem_base + 4 * TILE_BYTES;  // per stage: Q tile, dO tile, row records
+  const uint32_t bar_base = stage_smem + A_STAGES * A_STAGE_BYTES;
+  auto kv_full = [&](int kb) { return bar_base + 8u * kb; };
+  auto kv_empty = [&](int kb) { return bar_base + 8u * (2 + kb); };  // the S products of the block have read K and V
+  auto q_full = [&](int s) { return bar_base + 8u * (4 + s); };
+  auto q_empty = [&](int s) { return bar_base + 8u * (4 + A_STAGES + s); };
   // the two 64-query halves of a tile are handed back and forth separately (h = 0, 1)
-  auto s_full = [&](int h) { return bar_base + 8u * (1 + 2 * A_STAGES + h); };
-  auto p_full = [&](int h) { return bar_base + 8u * (3 + 2 * A_STAGES + h); };
-  const uint32_t acc_full = bar_base + 8u * (5 + 2 * A_STAGES);
-  const uint32_t tmem_slot = acc_full + 8;
+  auto s_full = [&](int h) { return bar_base + 8u * (4 + 2 * A_STAGES + h); };
+  auto p_full = [&](int h) { return bar_base + 8u * (6 + 2 * A_STAGES + h); };
+  const uint32_t acc_full = bar_base + 8u * (8 + 2 * A_STAGES);  // dK and dV of the block are complete
+  const uint32_t acc_free = acc_full + 8;                        // and every element-wise thread has read its part
+  auto sched_full = [&](int i) { return acc_free + 8u * (1 + i); };                  // answer i has landed
+  auto sched_empty = [&](int i) { return acc_free + 8u * (1 + SCHED_SLOTS + i); };  // and everybody has read it
+  const uint32_t tmem_slot = acc_free + 8u * (1 + 2 * SCHED_SLOTS);
+  auto sched_resp = [&](int i) { return acc_free + 8u * (3 + 2 * SCHED_SLOTS) + 16u * i; };  // 16-byte answers
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
-  const int n_blk = blockIdx.x;
-  const int hkv = blockIdx.y;
-  const int b = blockIdx.z;
-  const int n0 = n_blk * BN;
   const int group = p.Hq / p.Hkv;
   const int shift = p.Nk - p.Nq;
   const int num_m = (p.Nq + BM - 1) / BM;
-  // first query tile that sees a key of this block (bottom-right aligned causal mask)
-  const int m_first = p.causal ? min(num_m, max(0, n0 - shift) / BM) : 0;
-  const int tiles_per_head = num_m - m_first;
-  const int n_iter = group * tiles_per_head;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1);
+    for (int kb = 0; kb < 2; ++kb) {
+      mbar_init(kv_full(kb), 1);
+      mbar_init(kv_empty(kb), 1);
+    }
     for (int s = 0; s < A_STAGES; ++s) {
       mbar_init(q_full(s), 1);
       mbar_init(q_empty(s), 1);
@@ -266,6 +331,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       mbar_init(p_full(h), HALF_THREADS);
     }
     mbar_init(acc_full, 1);
+    mbar_init(acc_free, 2 * HALF_THREADS);
+    for (int i = 0; i < SCHED_SLOTS; ++i) {
+      mbar_init(sched_full(i), 1);
+      mbar_init(sched_empty(i), 2 + 2 * HALF_THREADS);  // the TMA thread, the MMA thread, the element-wise threads
+    }
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
     prefetch_tmap(&tmap_k);
@@ -282,44 +352,102 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
+  // The CTA's list of key blocks: its own grid index first, then the indices of CTAs that have not started, handed
+  // out by the launch control (common.cuh) one at a time.  Tiles and blocks are counted through the CTA's whole life;
+  // every barrier parity below derives from those running counts.
+  struct KeyBlock {
+    int n0, hkv, b, m_first, tiles_per_head, n_iter;
+  } blk;
+  auto set_block = [&](uint32_t x, uint32_t y, uint32_t z) {
+    blk.n0 = x * BN;
+    blk.hkv = y;
+    blk.b = z;
+    // first query tile that sees a key of this block (bottom-right aligned causal mask)
+    blk.m_first = p.causal ? min(num_m, max(0, blk.n0 - shift) / BM) : 0;
+    blk.tiles_per_head = num_m - blk.m_first;
+    blk.n_iter = group * blk.tiles_per_head;
+  };
+  set_block(blockIdx.x, blockIdx.y, blockIdx.z);
+  bool ok = true;
+  uint32_t n_answers = 0;  // answers read so far
+  // Reads the next answer of the launch control: false if no block was left (or the wait gave up: ok is false then).
+  auto next_block = [&]() {
+    const int slot = n_answers % SCHED_SLOTS;
+    if (!mbar_wait(sched_full(slot), (n_answers / SCHED_SLOTS) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) {
+      ok = false;
+      return false;
+    }
+    uint32_t x, y, z;
+    const bool got = launch_control_answer(sched_resp(slot), x, y, z);
+    // the slot's next answer is written through the async proxy: order this read before it
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_arrive(sched_empty(slot));
+    ++n_answers;
+    if (got) set_block(x, y, z);
+    return got;
+  };
+
   if (warp == 0) {
-    if (lane == 0 && n_iter > 0) {
-      mbar_expect_tx(kv_full, 2 * TILE_BYTES);
-      tma_load_4d(k_smem, &tmap_k, kv_full, 0, n0, hkv, b);
-      tma_load_4d(v_smem, &tmap_v, kv_full, 0, n0, hkv, b);
-      for (int it = 0; it < n_iter; ++it) {
-        const int s = it % A_STAGES;
-        const uint32_t ph = (it / A_STAGES) & 1;
-        const int hq = hkv * group + it / tiles_per_head;
-        const int m0 = (m_first + it % tiles_per_head) * BM;
-        if (!mbar_wait(q_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
-        const uint32_t base = stage_smem + s * A_STAGE_BYTES;
-        mbar_expect_tx(q_full(s), A_STAGE_BYTES);
-        tma_load_4d(base, &tmap_q, q_full(s), 0, m0, hq, b);
-        tma_load_4d(base + TILE_BYTES, &tmap_do, q_full(s), 0, m0, hq, b);
-        bulk_load(base + 2 * TILE_BYTES, p.qstat + ((static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0) * 2,
-                  A_STAT_BYTES, q_full(s));
+    if (lane == 0) {
+      int ci = -1;      // blocks with work so far
+      uint32_t gt = 0;  // tiles so far
+      for (;;) {
+        if (blk.n_iter > 0) {
+          ++ci;
+          const int kb = ci & 1;
+          // the S products of the block before the previous one have read this pair of buffers
+          if (ci >= 2 && !mbar_wait(kv_empty(kb), ((ci >> 1) - 1) & 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
+          mbar_expect_tx(kv_full(kb), 2 * TILE_BYTES);
+          tma_load_4d(k_smem(kb), &tmap_k, kv_full(kb), 0, blk.n0, blk.hkv, blk.b);
+          tma_load_4d(v_smem(kb), &tmap_v, kv_full(kb), 0, blk.n0, blk.hkv, blk.b);
+          for (int it = 0; it < blk.n_iter; ++it, ++gt) {
+            const int s = gt % A_STAGES;
+            const uint32_t ph = (gt / A_STAGES) & 1;
+            const int hq = blk.hkv * group + it / blk.tiles_per_head;
+            const int m0 = (blk.m_first + it % blk.tiles_per_head) * BM;
+            if (!mbar_wait(q_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) {
+              ok = false;
+              break;
+            }
+            const uint32_t base = stage_smem + s * A_STAGE_BYTES;
+            mbar_expect_tx(q_full(s), A_STAGE_BYTES);
+            tma_load_4d(base, &tmap_q, q_full(s), 0, m0, hq, blk.b);
+            tma_load_4d(base + TILE_BYTES, &tmap_do, q_full(s), 0, m0, hq, blk.b);
+            bulk_load(base + 2 * TILE_BYTES,
+                      p.qstat + ((static_cast<int64_t>(blk.b) * p.Hq + hq) * p.nq_pad + m0) * 2, A_STAT_BYTES,
+                      q_full(s));
+          }
+          if (!ok) break;
+        }
+        // this block's loads are on their way: ask for another block
+        const int slot = n_answers % SCHED_SLOTS;
+        if (n_answers >= SCHED_SLOTS &&
+            !mbar_wait(sched_empty(slot), ((n_answers / SCHED_SLOTS) - 1) & 1, p.status, WK_ERR_TIMEOUT_EMPTY))
+          break;
+        mbar_expect_tx(sched_full(slot), 16);
+        launch_control_try_cancel(sched_resp(slot), sched_full(slot));
+        if (!next_block()) break;
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0 && n_iter > 0) {
+    if (lane == 0) {
       // A tile is processed as two halves of 64 queries, each with its own pair of barriers, so that the tensor
       // pipe works on one half while the element-wise warps of the other half are busy:
       //   S^T, dP^T (h) -> element-wise (h) -> dV, dK += (h) -> S^T, dP^T of the next tile (h) -> ...
       // All MMAs come from this one thread, so the products of the next tile overwrite a half's columns only
-      // after the products that read its codes (the tensor pipe runs in issue order).
+      // after the products that read its codes (the tensor pipe runs in issue order).  The next tile may be the
+      // first one of the next key block: its S^T and dP^T are under way while this block's dK and dV are stored.
       constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BN, BM / 2);
       const uint32_t st_tmem = tmem_base + A_ST_COL;
       const uint32_t dpt_tmem = tmem_base + A_DPT_COL;
-      bool ok = mbar_wait(kv_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
-      const uint64_t k_desc = smem_desc_sw128(k_smem, 16, 1024);
-      const uint64_t v_desc = smem_desc_sw128(v_smem, 16, 1024);
-      auto q_desc_of = [&](int it) { return smem_desc_sw128(stage_smem + (it % A_STAGES) * A_STAGE_BYTES, 16, 1024); };
-      // S^T = K Q^T and dP^T = V dO8^T for queries [64 h, 64 h + 64) of tile `it`: rows 64 h.. of the Q and dO8
-      // tiles are 64 x 128 bytes further on (+512 in descriptor units)
-      auto ss_half = [&](int it, int h) {
-        const uint64_t q_desc = q_desc_of(it) + 512 * h;
+      auto q_desc_of = [&](uint32_t g) { return smem_desc_sw128(stage_smem + (g % A_STAGES) * A_STAGE_BYTES, 16, 1024); };
+      // S^T = K Q^T and dP^T = V dO8^T for queries [64 h, 64 h + 64) of tile g (K and V in buffers kb): rows 64 h..
+      // of the Q and dO8 tiles are 64 x 128 bytes further on (+512 in descriptor units)
+      auto ss_half = [&](uint32_t g, int kb, int h) {
+        const uint64_t k_desc = smem_desc_sw128(k_smem(kb), 16, 1024);
+        const uint64_t v_desc = smem_desc_sw128(v_smem(kb), 16, 1024);
+        const uint64_t q_desc = q_desc_of(g) + 512 * h;
         const uint64_t do_desc = q_desc + (TILE_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < D / 32; ++k) mma_f8_ss(st_tmem + HALF_COLS * h, k_desc + 2 * k, q_desc + 2 * k, idesc_ss, k != 0);
@@ -327,10 +455,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         for (int k = 0; k < D / 32; ++k) mma_f8_ss(dpt_tmem + HALF_COLS * h, v_desc + 2 * k, do_desc + 2 * k, idesc_ss, k != 0);
         tc_commit(s_full(h));
       };
-      // dV += (P g)^T dO8 and dK += dS^T Q8 over the same 64 queries.  B operands: the dO8 / Q8 tiles again, now
-      // read MN-major (K = queries, 32 per step = 4096 bytes, N = head dim)
-      auto ts_half = [&](int it, int h) {
-        const uint64_t q_desc = q_desc_of(it);
+      // dV += (P g)^T dO8 and dK += dS^T Q8 over the same 64 queries (`it`: the tile's number inside its key block).
+      // B operands: the dO8 / Q8 tiles again, now read MN-major (K = queries, 32 per step = 4096 bytes, N = head dim)
+      auto ts_half = [&](uint32_t g, int it, int h) {
+        const uint64_t q_desc = q_desc_of(g);
         const uint64_t do_desc = q_desc + (TILE_BYTES >> 4);
         // block k of the half keeps its codes and scale words inside its own 32 columns
 #pragma unroll
@@ -346,29 +474,84 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                       make_idesc_mx_major(BN, D, 0, 0, 0, 1), bb + A_SF_DS, bb + A_SF_UNIT, (it | h | k) != 0);
         }
       };
-      ok = ok && mbar_wait(q_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD);
-      if (ok) {
-        tc_fence_after();
-        ss_half(0, 0);
-        ss_half(0, 1);
-      }
-      for (int it = 0; ok && it < n_iter; ++it) {
-        const int s = it % A_STAGES;
-        const bool more = it + 1 < n_iter;
-        if (!mbar_wait(p_full(0), it & 1, p.status, WK_ERR_TIMEOUT_P)) break;
-        tc_fence_after();
-        ts_half(it, 0);
-        if (more) {
-          if (!mbar_wait(q_full((it + 1) % A_STAGES), ((it + 1) / A_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
-          tc_fence_after();
-          ss_half(it + 1, 0);
+      auto wait_tile = [&](uint32_t g) {  // the Q / dO8 / records of tile g have landed
+        return mbar_wait(q_full(g % A_STAGES), (g / A_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD);
+      };
+      // moves on to the next key block that has query tiles; false when the list is exhausted
+      bool have = blk.n_iter > 0;
+      auto advance = [&]() {
+        have = false;
+        while (ok && next_block()) {
+          if (blk.n_iter > 0) {
+            have = true;
+            break;
+          }
         }
-        if (!mbar_wait(p_full(1), it & 1, p.status, WK_ERR_TIMEOUT_P)) break;
-        tc_fence_after();
-        ts_half(it, 1);
-        tc_commit(q_empty(s));
-        if (more) ss_half(it + 1, 1);
-        if (!more) tc_commit(acc_full);
+        return have;
+      };
+      if (!have) advance();
+      int ci = 0;       // the current block's number among those with work
+      uint32_t g = 0;   // tiles so far
+      if (have) {
+        ok = mbar_wait(kv_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD) && wait_tile(0);
+        if (ok) {
+          tc_fence_after();
+          ss_half(0, 0, 0);
+          ss_half(0, 0, 1);
+        }
+      }
+      while (ok && have) {
+        const int n_iter = blk.n_iter;
+        const int kb = ci & 1;
+        bool next_ready = false;  // the next block is known (blk describes it) and its K and V have landed
+        for (int it = 0; ok && it < n_iter; ++it, ++g) {
+          const bool last = it + 1 == n_iter;
+          if (last) {
+            // look ahead: the first tile of the next block takes the place of this block's next tile
+            next_ready = advance();
+            if (!ok) break;
+            if (next_ready && !mbar_wait(kv_full(kb ^ 1), ((ci + 1) >> 1) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) {
+              ok = false;
+              break;
+            }
+          }
+          const bool more = !last || next_ready;
+          const int kb_next = last ? kb ^ 1 : kb;
+          if (!mbar_wait(p_full(0), g & 1, p.status, WK_ERR_TIMEOUT_P)) {
+            ok = false;
+            break;
+          }
+          // the element-wise threads have read the previous block's dK and dV
+          if (it == 0 && ci >= 1 && !mbar_wait(acc_free, (ci - 1) & 1, p.status, WK_ERR_TIMEOUT_TMEM)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          ts_half(g, it, 0);
+          if (more) {
+            if (!wait_tile(g + 1)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            ss_half(g + 1, kb_next, 0);
+          }
+          if (!mbar_wait(p_full(1), g & 1, p.status, WK_ERR_TIMEOUT_P)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          ts_half(g, it, 1);
+          tc_commit(q_empty(g % A_STAGES));
+          if (more) ss_half(g + 1, kb_next, 1);
+          // the S products of this block's last tile were issued one tile ago (or just now, for a single tile)
+          if (last) {
+            tc_commit(kv_empty(kb));
+            tc_commit(acc_full);
+          }
+        }
+        have = next_ready;
+        ++ci;
       }
     }
     __syncwarp();
@@ -377,21 +560,27 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const int c = (warp - 2) >> 2;   // which block of 32 of the tile's 128 columns this thread handles
     const int half = c >> 1;         // the half the block is handed over with
     const int r = quad * 32 + lane;  // key row of the tile == TMEM lane
-    const int key = n0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     // this thread's block: scores in columns [32 c, 32 c + 32) of both buffers
     const uint32_t st_tmem = tmem_base + lane_addr + A_ST_COL + 32 * c;
     const uint32_t dpt_tmem = tmem_base + lane_addr + A_DPT_COL + 32 * c;
-    const int sc = b * p.Hkv + hkv;
-    const float sq = p.q_descale[sc], sk = p.k_descale[sc];
-    const float beta = p.softmax_scale * sq * sk * LOG2E;
-    const uint64_t sv2 = pack_f32x2(p.v_descale[sc], p.v_descale[sc]);
-    bool ok = true;
+    int ci = -1;     // key blocks with work so far
+    uint32_t g = 0;  // tiles so far
 
-    for (int it = 0; it < n_iter; ++it) {
-      const int s = it % A_STAGES;
-      const int m0 = (m_first + it % tiles_per_head) * BM;
-      if (!mbar_wait_warp(s_full(half), it & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+    for (;;) {
+    const int n0 = blk.n0, n_iter = blk.n_iter;
+    const int key = n0 + r;
+    const int sc = blk.b * p.Hkv + blk.hkv;
+    const float beta = p.softmax_scale * p.q_descale[sc] * p.k_descale[sc] * LOG2E;
+    const uint64_t sv2 = pack_f32x2(p.v_descale[sc], p.v_descale[sc]);
+    if (n_iter > 0) ++ci;
+
+    int mt = blk.m_first;  // the query tile, restarting with every query head of the group
+    for (int it = 0; it < n_iter; ++it, ++g) {
+      const int s = g % A_STAGES;
+      const int m0 = mt * BM;
+      if (++mt == num_m) mt = blk.m_first;
+      if (!mbar_wait_warp(s_full(half), g & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
         ok = false;
         break;
       }
@@ -452,11 +641,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       mbar_arrive(p_full(half));
     }
 
-    if (n_iter > 0 && ok) ok = mbar_wait_warp(acc_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
+    if (n_iter > 0 && ok) ok = mbar_wait_warp(acc_full, ci & 1, p.status, WK_ERR_TIMEOUT_MMA);
     if (ok) {
       tc_fence_after();
-      const float dk_scale = p.softmax_scale * sq;
-      const int64_t row_off = ((static_cast<int64_t>(b) * p.Hkv + hkv) * p.Nk + key) * D;
+      const float dk_scale = p.softmax_scale * p.q_descale[sc];
+      const int64_t row_off = ((static_cast<int64_t>(blk.b) * p.Hkv + blk.hkv) * p.Nk + key) * D;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         const uint32_t src = tmem_base + lane_addr + (which == 0 ? A_DV_COL : A_DK_COL);
@@ -468,6 +657,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           if (n_iter > 0) {  // uniform: TMEM loads are warp-wide
             tmem_ld32(src + c * 32, v);
             tc_wait_ld();
+            if (which == 1) {
+              // dK and dV are in registers: the next block's first products may overwrite them
+              tc_fence_before();
+              mbar_arrive(acc_free);
+            }
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0;
@@ -486,6 +680,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           }
         }
       }
+    }
+    if (!ok || !next_block()) break;
     }
   }
 
@@ -811,8 +1007,14 @@ extern "C" int wk_attn_bwd_fp8(const wk_attn_bwd_args* a, void* stream) {
   pp.nq_pad = nq_pad;
   {
     const int64_t rows = static_cast<int64_t>(a->B) * a->Hq * nq_pad;
-    const int64_t blocks = (rows + 7) / 8;
-    attn_bwd_prep_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(pp);
+    bool wide_loads = true;  // 16-byte loads need rows that start on 16-byte boundaries
+    for (int i = 0; i < 3; ++i) wide_loads = wide_loads && a->out_strides[i] % 8 == 0 && a->dout_strides[i] % 8 == 0;
+    if (wide_loads) {
+      attn_bwd_prep4_kernel<<<static_cast<unsigned>((rows + 31) / 32), 256, 0, st>>>(pp);
+    } else {
+      const int64_t blocks = (rows + 7) / 8;
+      attn_bwd_prep_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(pp);
+    }
     if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
   }
 

@@ -144,6 +144,35 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------
+// Launch control: a running CTA takes over the grid index of a CTA that has not started yet, so that a grid with
+// one CTA per work item is worked through by the CTAs that fit the GPU, in launch order, without the start-up and
+// drain of a CTA between items.  After an answer that says "none left" no further request may be made.
+// ---------------------------------------------------------------------------
+// Asks the hardware to cancel the launch of a CTA of this grid that has not started; the 16-byte answer lands at
+// `resp` and its bytes are counted on `bar`.
+__device__ __forceinline__ void launch_control_try_cancel(uint32_t resp, uint32_t bar) {
+  asm volatile(
+      "clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];" ::"r"(resp),
+      "r"(bar)
+      : "memory");
+}
+// Decodes an answer: true and the cancelled CTA's index if one was cancelled, false if none was left.
+__device__ __forceinline__ bool launch_control_answer(uint32_t resp, uint32_t& x, uint32_t& y, uint32_t& z) {
+  uint32_t got;
+  asm volatile(
+      "{\n\t.reg .b128 ans;\n\t.reg .pred pc;\n\t.reg .b32 t;\n\t"
+      "ld.shared.b128 ans, [%4];\n\t"
+      "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 pc, ans;\n\t"
+      "selp.u32 %0, 1, 0, pc;\n\t"
+      "mov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
+      "@pc clusterlaunchcontrol.query_cancel.get_first_ctaid.v4.b32.b128 {%1, %2, %3, t}, ans;\n\t}"
+      : "=r"(got), "=r"(x), "=r"(y), "=r"(z)
+      : "r"(resp)
+      : "memory");
+  return got != 0;
+}
+
+// ---------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor): every CTA loads its own tiles.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
