@@ -85,6 +85,52 @@ __global__ void __launch_bounds__(256) attn_bwd_bf16_prep_kernel(const PrepParam
   }
 }
 
+// The same for tensors whose strides are multiples of 8 elements: four query rows per warp, 8 lanes per row and 16
+// consecutive elements per lane, read with 16-byte loads (the kernel is HBM-bound; one row per warp keeps too few
+// bytes in flight).
+__global__ void __launch_bounds__(256) attn_bwd_bf16_prep4_kernel(const PrepParams p) {
+  const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
+  const int sub = lane & 7;
+  const int64_t rows = static_cast<int64_t>(p.B) * p.Hq * p.nq_pad;  // a multiple of 128
+  if (warp * 4 >= rows) return;
+  const int64_t row_id = warp * 4 + (lane >> 3);
+  const int i = static_cast<int>(row_id % p.nq_pad);
+  const int h = static_cast<int>((row_id / p.nq_pad) % p.Hq);
+  const int b = static_cast<int>(row_id / (static_cast<int64_t>(p.nq_pad) * p.Hq));
+  const bool live = i < p.Nq;  // padding rows take part in the shuffles with zeros
+  uint4 draw[2] = {}, oraw[2] = {};
+  if (live) {
+    const uint4* dsrc = reinterpret_cast<const uint4*>(p.dout + b * p.do_sb + h * p.do_sh +
+                                                       static_cast<int64_t>(i) * p.do_sn + sub * 16);
+    const uint4* osrc =
+        reinterpret_cast<const uint4*>(p.out + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(i) * p.o_sn + sub * 16);
+    draw[0] = dsrc[0];
+    draw[1] = dsrc[1];
+    oraw[0] = osrc[0];
+    oraw[1] = osrc[1];
+  }
+  const uint32_t dw[8] = {draw[0].x, draw[0].y, draw[0].z, draw[0].w, draw[1].x, draw[1].y, draw[1].z, draw[1].w};
+  const uint32_t ow[8] = {oraw[0].x, oraw[0].y, oraw[0].z, oraw[0].w, oraw[1].x, oraw[1].y, oraw[1].z, oraw[1].w};
+  float dsum = 0.f;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    dsum += __uint_as_float(dw[c] << 16) * __uint_as_float(ow[c] << 16) +
+            __uint_as_float(dw[c] & 0xffff0000u) * __uint_as_float(ow[c] & 0xffff0000u);
+  }
+#pragma unroll
+  for (int off = 4; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
+  // the two values of row i sit 128 floats apart inside the row's tile of 128
+  float* stat = p.qstat + ((static_cast<int64_t>(b) * p.Hq + h) * p.nq_pad + (i & ~127)) * 2 + (i & 127);
+  if (!live) {
+    // padding rows: lse = +inf makes every probability zero
+    if (sub < 2) stat[sub * 128] = sub == 0 ? -INFINITY : 0.f;
+  } else if (sub == 0) {
+    stat[0] = -p.lse[b * p.lse_sb + h * p.lse_sh + i];
+    stat[128] = -dsum;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // helpers shared by the two main kernels
 // ---------------------------------------------------------------------------
@@ -718,8 +764,14 @@ extern "C" int wk_attn_bwd_bf16(const wk_attn_bwd_args* a, void* stream) {
   pp.nq_pad = nq_pad;
   {
     const int64_t rows = static_cast<int64_t>(a->B) * a->Hq * nq_pad;
-    const int64_t blocks = (rows + 7) / 8;
-    attn_bwd_bf16_prep_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(pp);
+    bool wide_loads = true;  // 16-byte loads need rows that start on 16-byte boundaries
+    for (int i = 0; i < 3; ++i) wide_loads = wide_loads && a->out_strides[i] % 8 == 0 && a->dout_strides[i] % 8 == 0;
+    if (wide_loads) {
+      attn_bwd_bf16_prep4_kernel<<<static_cast<unsigned>((rows + 31) / 32), 256, 0, st>>>(pp);
+    } else {
+      const int64_t blocks = (rows + 7) / 8;
+      attn_bwd_bf16_prep_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(pp);
+    }
     if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
   }
 
