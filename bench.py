@@ -37,8 +37,8 @@ DRAM_TRAFFIC_BYTES = {
     "attn_fwd_small": 96.5e6 + 29.5e6 + 12.6e6,
     "attn_gqa": 4 * (83.1e6 + 84.5e6),
     "attn_gqa_small": 83.1e6 + 84.5e6,
-    "attn_bwd": 2 * (156.5e6 + 226.4e6 + 177.7e6),
-    "attn_bwd_small": 156.5e6 + 226.4e6 + 177.7e6,
+    "attn_bwd": 2 * (155.4e6 + 226.5e6 + 178.0e6),
+    "attn_bwd_small": 155.4e6 + 226.5e6 + 178.0e6,
     "gemm_mx": 292.8e6 + 201.3e6,
     "gemm_bf16_8k": 1083.5e6 + 127.0e6,
     "gemm_bf16_8k_pair": 1083.5e6 + 127.0e6,

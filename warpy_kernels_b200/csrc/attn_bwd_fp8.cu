@@ -7,13 +7,16 @@
 // as in the reference's backward (warpy_kernels/attn/bwd_common.py:88-304, bwd_sm120.py:253-512):
 // every product runs on the tensor core in e4m3.  Three kernels:
 //
-//  1. attn_bwd_prep_kernel (HBM-bound): per query row, dO -> e4m3 with a power-of-two row
+//  1. attn_bwd_prep4_kernel (HBM-bound; attn_bwd_prep_kernel for rows that do not start on 16-byte
+//     boundaries): per query row, dO -> e4m3 with a power-of-two row
 //     scale g (as the MXFP8 quantiser picks it) and the two numbers per row the main kernels
 //     read, log2(g) - L and -sum(dO8 . O).  The reference scales dO per
 //     (batch, kv head) and carries a second residual term (bwd_common.py:133-266); a scale per
 //     row keeps small rows precise without it.
-//  2. attn_bwd_dkdv_kernel: CTA = 128 keys of one (batch, kv head), K and V resident in shared
-//     memory, loop over the group's query heads and query tiles.  Per tile:
+//  2. attn_bwd_dkdv_kernel: a key block = 128 keys of one (batch, kv head), K and V resident in shared
+//     memory, loop over the group's query heads and query tiles.  The grid has one CTA per key block; the
+//     CTAs that start take over the blocks of those that have not (launch control, common.cuh), with K and V
+//     double-buffered and the next block's first S^T / dP^T under way while dK and dV are stored.  Per tile:
 //       S^T = K Q^T and dP^T = V dO8^T            (tcgen05.mma kind::f8f6f4, into TMEM)
 //       threads (four per key): P^T . g and dS^T as MXFP8 (e4m3 codes back into TMEM, one
 //                              power-of-two scale per key and 32 queries, also into TMEM)
