@@ -117,6 +117,27 @@ def test_strided_inputs_and_float_dout(cuda):
         assert torch.equal(a, b)
 
 
+def test_rows_on_8_byte_boundaries(cuda):
+    """``dout`` / ``out`` rows that start on 8-byte but not 16-byte boundaries take the one-row-per-warp prep kernel
+    instead of the 16-byte-load one; the two differ only in the order of the sum over the head dimension."""
+    from warpy_kernels import attn_bwd, attn_fwd
+
+    B, H, N, d = 1, 2, 333, 128
+    q, k, v = randn_qkv(B, H, H, N, N, d, seed=11, device=cuda)
+    q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+    out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
+    dout = torch.randn(q.shape, device=cuda).bfloat16()
+    base = attn_bwd(q8, k8, v8, out, lse, pmax, dout, sq, sk, sv, causal=True)
+    wide = torch.zeros(B, H, N, d + 4, device=cuda, dtype=torch.bfloat16)
+    wide[..., :d] = dout
+    wide_out = torch.zeros(B, H, N, d + 4, device=cuda, dtype=torch.bfloat16)
+    wide_out[..., :d] = out
+    got = attn_bwd(q8, k8, v8, wide_out[..., :d], lse, pmax, wide[..., :d], sq, sk, sv, causal=True)
+    for a, b in zip(base, got):
+        assert R.cosine(a.float().cpu(), b.float().cpu()) >= 0.9999
+        assert R.rel_l2(a.float().cpu(), b.float().cpu()) <= 1e-2
+
+
 def test_validation_errors(cuda):
     from warpy_kernels import attn_bwd
 

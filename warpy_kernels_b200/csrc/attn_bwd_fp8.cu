@@ -1010,7 +1010,7 @@ extern "C" int wk_attn_bwd_fp8(const wk_attn_bwd_args* a, void* stream) {
   pp.nq_pad = nq_pad;
   {
     const int64_t rows = static_cast<int64_t>(a->B) * a->Hq * nq_pad;
-    bool wide_loads = true;  // 16-byte loads need rows that start on 16-byte boundaries
+    bool wide_loads = aligned16(a->out) && aligned16(a->dout);  // 16-byte loads: rows on 16-byte boundaries
     for (int i = 0; i < 3; ++i) wide_loads = wide_loads && a->out_strides[i] % 8 == 0 && a->dout_strides[i] % 8 == 0;
     if (wide_loads) {
       attn_bwd_prep4_kernel<<<static_cast<unsigned>((rows + 31) / 32), 256, 0, st>>>(pp);
