@@ -92,10 +92,9 @@ typedef struct {
   void* s_mx;
   int32_t a_trans; /* a is stored [K, M] (warpy_kernels/gemm/api.py:103-104, gemm/base.py:127-135) */
   int32_t b_trans; /* b is stored [K, N] */
-  int32_t cta_pair; /* 1: the CTA-pair kernel (tcgen05 cta_group::2, one 256 x 256 tile per two SMs); needs row-major
-                       operands (no a_trans / b_trans), else WK_E_ARG.  2: never pairs.  0: the library's choice (pairs
-                       when the 256 x 256 tiles fill the GPU about as well as 128 x 256 ones).  The results are
-                       bit-identical either way. */
+  int32_t cta_pair; /* 1: the CTA-pair kernel (tcgen05 cta_group::2, one 256 x 256 tile per two SMs).  2: never pairs.
+                       0: the library's choice (pairs when the 256 x 256 tiles fill the GPU about as well as
+                       128 x 256 ones).  The results are bit-identical either way. */
 } wk_gemm16_args;
 
 int wk_gemm_16bit(const wk_gemm16_args* args, void* stream);

@@ -396,8 +396,13 @@ def test_cta_pair_kernel_matches_single_cta_kernel(cuda, kind, shape):
     post, pre = gemm(a, b, out=c0.clone(), scale_a=rows, accum=True, act="gelu", store_pre=True, cta_pair=True)
     post1, pre1 = gemm(a, b, out=c0.clone(), scale_a=rows, accum=True, act="gelu", store_pre=True, cta_pair=False)
     assert torch.equal(post, post1) and torch.equal(pre, pre1)
-    with pytest.raises(ValueError):
-        gemm(a.T.contiguous(), b, a_trans=True, cta_pair=True)  # row-major operands only
+    # transposed operands (MN-major tiles) through both kernels
+    at, bt = a.T.contiguous(), b.T.contiguous()
+    for kw in (dict(a_trans=True), dict(b_trans=True), dict(a_trans=True, b_trans=True)):
+        x = at if kw.get("a_trans") else a
+        y = bt if kw.get("b_trans") else b
+        assert torch.equal(gemm(x, y, cta_pair=True, **kw), out), kw
+        assert torch.equal(gemm(x, y, cta_pair=False, **kw), out), kw
 
 
 @pytest.mark.parametrize("shape", [(256, 256, 128), (128, 128, 128), (384, 640, 384), (4096, 4096, 2048),

@@ -211,8 +211,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }  // namespace
 
 // the CTA-pair kernel (gemm_bf16_2sm.cu)
-int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n, int k, int f16, const Epilogue& e,
-                          int* status, cudaStream_t stream);
+int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n, int k, int f16, int a_trans,
+                          int b_trans, const Epilogue& e, int* status, cudaStream_t stream);
 }  // namespace wk
 
 extern "C" int wk_gemm_16bit(const wk_gemm16_args* g, void* stream) {
@@ -259,17 +259,15 @@ extern "C" int wk_gemm_16bit(const wk_gemm16_args* g, void* stream) {
   e.pre_in = g->pre_in;
   e.q_mx = static_cast<uint8_t*>(g->q_mx);
   e.s_mx = static_cast<uint8_t*>(g->s_mx);
-  // cta_pair: 1 the CTA-pair kernel (row-major operands only), 2 this file's kernel, 0 whichever should finish
+  // cta_pair: 1 the CTA-pair kernel, 2 this file's kernel, 0 whichever should finish
   // first: a pair works through a 256 x 256 tile about 10 % faster than two SMs through two 128 x 256 tiles
   // (1.53 against 1.40 PFLOP/s at 8192^3), but a small problem fills 148 SMs better with the smaller tiles
   if (g->cta_pair < 0 || g->cta_pair > 2) return WK_E_ARG;
-  const bool pair_ok = !g->a_trans && !g->b_trans;
-  if (g->cta_pair == 1 && !pair_ok) return WK_E_ARG;
   const int sms = sm_count();
   if (sms <= 0) return WK_E_CUDA;
   const int num_tiles = (m / BM) * ((n + BN - 1) / BN);
   bool pair = g->cta_pair == 1;
-  if (g->cta_pair == 0 && pair_ok && sms >= 2) {
+  if (g->cta_pair == 0 && sms >= 2) {
     const long pair_tiles = static_cast<long>((m + 255) / 256) * ((n + 255) / 256);
     const long pair_waves = (pair_tiles + sms / 2 - 1) / (sms / 2);
     const long single_waves = (num_tiles + sms - 1) / sms;
@@ -278,7 +276,8 @@ extern "C" int wk_gemm_16bit(const wk_gemm16_args* g, void* stream) {
     pair = pair_tiles > sms && pair_waves * 10 < single_waves * 11;
   }
   if (pair) {
-    return launch_gemm_16bit_2sm(g->a, g->b, g->out, m, n, k, g->f16, e, status, static_cast<cudaStream_t>(stream));
+    return launch_gemm_16bit_2sm(g->a, g->b, g->out, m, n, k, g->f16, g->a_trans, g->b_trans, e, status,
+                                 static_cast<cudaStream_t>(stream));
   }
   if (allow_smem(reinterpret_cast<const void*>(gemm_bf16_kernel), SMEM_BYTES)) return WK_E_CUDA;
   const int grid = num_tiles < sms ? num_tiles : sms;

@@ -18,8 +18,8 @@
 // Every wait is bounded (common.cuh); the two cluster-wide barriers at start and end are plain hardware barriers
 // that both CTAs always reach.
 //
-// Reached through wk_gemm_16bit for row-major operands (cta_pair = 1, or 0 when the pairs fill the GPU better); M
-// and N multiples of 128 and K of 64 as there.
+// Reached through wk_gemm_16bit (cta_pair = 1, or 0 when the pairs fill the GPU better); operands row-major or
+// transposed, M and N multiples of 128 and K of 64 as there.
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 #include "host_common.h"
@@ -34,6 +34,7 @@ constexpr int P_BK = 64;  // one 128-byte swizzle span per row
 constexpr int P_STAGES = 7;
 constexpr int P_CHUNK_BYTES = 128 * 64 * 2;    // 128 rows x 64 K elements (one swizzle span)
 constexpr int P_CHUNKS = P_BK / 64;            // swizzle spans per row of a stage
+constexpr int P_T_CHUNK_BYTES = 64 * P_BK * 2; // 64 K lines x 64 rows of a transposed operand
 constexpr int P_A_BYTES = P_CHUNKS * P_CHUNK_BYTES;   // this CTA's 128 rows of A
 constexpr int P_B_BYTES = P_CHUNKS * P_CHUNK_BYTES;   // this CTA's 128 of the tile's 256 rows of B
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
@@ -58,7 +59,7 @@ __device__ __forceinline__ PairTile pair_tile(int tile, int num_m, int num_n, in
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                     void* __restrict__ out, int M, int N, int K, int group_m, int in_f16,
+                     void* __restrict__ out, int M, int N, int K, int group_m, int in_f16, int a_trans, int b_trans,
                      const __grid_constant__ Epilogue epi, int* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -122,11 +123,21 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           const uint32_t full0 = mapa(full_bar(stage), 0);
           // the other CTA's bytes may land before this announcement: the count just goes negative meanwhile
           if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * P_STAGE_BYTES);
-#pragma unroll
-          for (int c = 0; c < P_CHUNKS; ++c) {
-            tma_load_2d_pair(sa + c * P_CHUNK_BYTES, &tmap_a, full0, kb * P_BK + 64 * c, tc.m_blk * P_BM + 128 * rank);
-            tma_load_2d_pair(sa + P_A_BYTES + c * P_CHUNK_BYTES, &tmap_b, full0, kb * P_BK + 64 * c,
-                             tc.n_blk * P_BN + 128 * rank);
+          // An operand stored [rows, K] arrives as one box of 128 rows x 64 K elements (K-major tile).  A transposed
+          // operand, stored [K, rows], arrives as two boxes of 64 K lines x 64 rows (128 bytes of rows per K line),
+          // 8 KiB apart: an MN-major tile.
+          const int a_row = tc.m_blk * P_BM + 128 * rank, b_row = tc.n_blk * P_BN + 128 * rank;
+          if (a_trans) {
+            tma_load_2d_pair(sa, &tmap_a, full0, a_row, kb * P_BK);
+            tma_load_2d_pair(sa + P_T_CHUNK_BYTES, &tmap_a, full0, a_row + 64, kb * P_BK);
+          } else {
+            tma_load_2d_pair(sa, &tmap_a, full0, kb * P_BK, a_row);
+          }
+          if (b_trans) {
+            tma_load_2d_pair(sa + P_A_BYTES, &tmap_b, full0, b_row, kb * P_BK);
+            tma_load_2d_pair(sa + P_A_BYTES + P_T_CHUNK_BYTES, &tmap_b, full0, b_row + 64, kb * P_BK);
+          } else {
+            tma_load_2d_pair(sa + P_A_BYTES, &tmap_b, full0, kb * P_BK, b_row);
           }
           if (++stage == P_STAGES) {
             stage = 0;
@@ -139,11 +150,15 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
       const uint32_t fmt = in_f16 ? 0 : 1;
-      const uint32_t idesc = make_idesc(fmt, fmt, 0, 0, P_BM, P_BN);
+      const uint32_t idesc = make_idesc(fmt, fmt, a_trans ? 1 : 0, b_trans ? 1 : 0, P_BM, P_BN);
       // descriptors of stage 0 (the same offsets hold in the other CTA); a later stage only moves the
       // 16-byte-granular start address field
-      const uint64_t a_desc0 = smem_desc_sw128(smem_base, 16, 1024);
-      const uint64_t b_desc0 = smem_desc_sw128(smem_base + P_A_BYTES, 16, 1024);
+      // K-major tile: 16 elements of K = 32 bytes inside the 128-byte swizzle span.  MN-major tile: the leading
+      // byte offset is the distance between the two 64-row chunks, 16 K lines = 2048 bytes.
+      const uint64_t a_desc0 = smem_desc_sw128(smem_base, a_trans ? P_T_CHUNK_BYTES : 16, 1024);
+      const uint64_t b_desc0 = smem_desc_sw128(smem_base + P_A_BYTES, b_trans ? P_T_CHUNK_BYTES : 16, 1024);
+      const uint64_t a_kstep = a_trans ? 2048 / 16 : 32 / 16;
+      const uint64_t b_kstep = b_trans ? 2048 / 16 : 32 / 16;
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -163,9 +178,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           const uint64_t step = static_cast<uint64_t>(stage) * (P_STAGE_BYTES / 16);
 #pragma unroll
           for (int k = 0; k < P_BK / 16; ++k) {
-            // 16 elements = 32 bytes along K inside a 128-byte swizzle span; the second span one chunk further on
-            const uint64_t off = step + (k >> 2) * (P_CHUNK_BYTES >> 4) + 2 * (k & 3);
-            mma_f16_ss_pair(d_tmem, a_desc0 + off, b_desc0 + off, idesc, (kb | k) != 0);
+            mma_f16_ss_pair(d_tmem, a_desc0 + step + k * a_kstep, b_desc0 + step + k * b_kstep, idesc, (kb | k) != 0);
           }
           // the stage is free in both CTAs once these MMAs have read it: one commit per CTA
           tc_commit_pair(mapa(empty_bar(stage), 0));
@@ -221,28 +234,33 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 }  // namespace
 
 // Launches the CTA-pair kernel.  The caller has checked the arguments; M and N are multiples of 128, K of 64.
-int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n, int k, int f16, const Epilogue& e,
-                          int* status, cudaStream_t stream) {
+int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n, int k, int f16, int a_trans,
+                          int b_trans, const Epilogue& e, int* status, cudaStream_t stream) {
   const CUtensorMapDataType dt = f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap ta, tb;
-  const uint32_t box[2] = {64, 128};
-  {
-    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+  // [rows, K] operand: boxes of 128 rows x 64 K; transposed ([K, rows]): boxes of 64 K lines x 64 rows
+  auto encode_operand = [&](CUtensorMap* t, const void* ptr, int rows, int trans) {
+    if (trans) {
+      const uint64_t dims[2] = {static_cast<uint64_t>(rows), static_cast<uint64_t>(k)};
+      const uint64_t strides[1] = {static_cast<uint64_t>(rows) * 2};
+      const uint32_t box[2] = {64, P_BK};
+      return encode_tmap(t, dt, 2, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    }
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(rows)};
     const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
-    if (int r = encode_tmap(&ta, dt, 2, a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return r;
-  }
-  {
-    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
-    if (int r = encode_tmap(&tb, dt, 2, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return r;
-  }
+    const uint32_t box[2] = {P_BK, 128};
+    return encode_tmap(t, dt, 2, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  };
+  if (int r = encode_operand(&ta, a, m, a_trans)) return r;
+  if (int r = encode_operand(&tb, b, n, b_trans)) return r;
   if (allow_smem(reinterpret_cast<const void*>(gemm_bf16_2sm_kernel), P_SMEM_BYTES)) return WK_E_CUDA;
   const int sms = sm_count();
   if (sms <= 0) return WK_E_CUDA;
   const int num_tiles = ((m + P_BM - 1) / P_BM) * ((n + P_BN - 1) / P_BN);
   const int max_pairs = sms / 2;
   const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
-  gemm_bf16_2sm_kernel<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(ta, tb, out, m, n, k, 8, f16, e, status);
+  gemm_bf16_2sm_kernel<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(ta, tb, out, m, n, k, 8, f16, a_trans, b_trans, e,
+                                                                        status);
   return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
 }
 

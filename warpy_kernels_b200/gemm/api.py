@@ -130,8 +130,7 @@ def make_gemm(
         out_mx: Whether to also write the result as MXFP8: e4m3 values ``[M, N]`` and ``[M, N / 32]`` uint8 ue8m0
             scales computed from the fp32 values before they are rounded to bf16.
         cta_pair: Not in the reference. ``True`` runs the CTA-pair kernel (``tcgen05`` ``cta_group::2``: two SMs
-            share a 256 x 256 tile); it needs row-major operands (``ValueError`` with ``a_trans`` / ``b_trans``).
-            ``False`` never uses pairs. ``None`` leaves the choice to the library: for 16-bit inputs pairs when the
+            share a 256 x 256 tile). ``False`` never uses pairs. ``None`` leaves the choice to the library: for 16-bit inputs pairs when the
             256 x 256 tiles fill the GPU about as well as 128 x 256 ones, for fp8 inputs single CTAs. The results
             are bit-identical either way.
         b_scale_mx: ``[N, K / 32]`` uint8 ue8m0 scales of ``b``. Not in the reference (which scales only ``a``);
