@@ -119,6 +119,26 @@ def test_seqused_and_natural_lse(cuda):
     assert torch.allclose(lsen, lse2 * 0.6931471805599453, rtol=1e-6, atol=1e-6)
 
 
+def test_seqused_persistent_kernel(cuda):
+    """``seqused_k`` through the persistent kernel (picked from 2048 keys on): a batch item with few keys belongs
+    wholly to the two-term launch, so the persistent CTAs skip its query blocks; one with a ragged length mixes
+    both.  Each item equals the call on its truncated K/V."""
+    from warpy_kernels import attn_fwd
+
+    q, k, v = randn_qkv(3, 4, 2, 640, 2560, 128, seed=13, device=cuda)
+    q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+    used = torch.tensor([2560, 700, 300], dtype=torch.int32, device=cuda)
+    for causal in (False, True):
+        out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=causal, seqused_k=used)
+        for b, n in enumerate(used.tolist()):
+            o1, l1, p1 = attn_fwd(q8[b : b + 1], k8[b : b + 1, :, :n], v8[b : b + 1, :, :n], sq[b : b + 1],
+                                  sk[b : b + 1], sv[b : b + 1], causal=causal, ctas_per_sm=1)
+            assert torch.equal(out[b : b + 1], o1) and torch.equal(lse[b : b + 1], l1), (causal, b)
+        qd, kd, vd = R.dequantize_qkv(q8.cpu(), k8.cpu(), v8.cpu(), sq.cpu(), sk.cpu(), sv.cpu())
+        out_ref, lse_ref = R.attention_reference(qd[:1], kd[:1], vd[:1], causal)
+        check(fwd_errors(out[:1], lse[:1], out_ref, lse_ref, 640, 2560, causal))
+
+
 @pytest.mark.parametrize("gap", [8])
 def test_sink_long_tail(cuda, gap):
     """One dominant key over a 32768-key tail (``tests/attn/test_fwd.py:104-114``, gate 2e-2)."""
