@@ -44,7 +44,7 @@ def _oracle_head(q8, k8, v8, sq, sk, sv, b, hq, rows, dout=None):
 
 
 def test_config1_attention_forward_b4_h32_n4096(cuda):
-    """BASELINE config 1: slices of two heads against the oracle (cosine >= 0.999, max-abs <= 2e-2), and rows of
+    """The forward benchmark shape (B4 H32 N4096 d128, causal): slices of two heads against the oracle (cosine >= 0.999, max-abs <= 2e-2), and rows of
     the probability simplex: every lse finite, pmax in (0, 1], out bounded by the largest |v|."""
     from warpy_kernels import attn_fwd
 
@@ -63,7 +63,7 @@ def test_config1_attention_forward_b4_h32_n4096(cuda):
 
 
 def test_config2_attention_backward_b4_h32_n4096(cuda):
-    """BASELINE config 2: gradients of one head against autograd through the oracle (cosine >= 0.995)."""
+    """The backward benchmark shape (B4 H32 N4096 d128, causal): gradients of one head against autograd through the oracle (cosine >= 0.995)."""
     from warpy_kernels import attn_bwd, attn_fwd
 
     B, H, N, d = 4, 32, 4096, 128
@@ -84,7 +84,7 @@ def test_config2_attention_backward_b4_h32_n4096(cuda):
 
 
 def test_config4_gqa_long_context_one_kv_group(cuda):
-    """BASELINE config 4 restricted to one KV head (8 query heads, N = 32768): the shard one GPU of eight runs.
+    """The GQA benchmark shape (B1 Hq64 Hkv8 N32768 d128) restricted to one KV head (8 query heads, N = 32768): the shard one GPU of eight runs.
     The last 256 queries of two heads against the oracle."""
     from warpy_kernels import attn_fwd
 
@@ -100,7 +100,7 @@ def test_config4_gqa_long_context_one_kv_group(cuda):
 
 @pytest.mark.parametrize("n,k", [(14336, 4096), (4096, 14336)])
 def test_config3_mxfp8_gemm_m8192(cuda, n, k):
-    """BASELINE config 3: a band of rows against the oracle, and linearity in the scale bytes: raising every scale
+    """The MXFP8 GEMM benchmark shape (M8192 N14336 K4096): a band of rows against the oracle, and linearity in the scale bytes: raising every scale
     byte of A by one doubles the product exactly."""
     from warpy_kernels import gemm, quantize_mx
 
