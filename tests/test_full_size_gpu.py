@@ -118,7 +118,7 @@ def test_config3_mxfp8_gemm_m8192(cuda, n, k):
 
 
 def test_config0_bf16_gemm_2048(cuda):
-    """BASELINE config 0 whole: relative Frobenius error <= 1e-2 against fp32 accumulation."""
+    """The BF16 GEMM benchmark shape (M = N = K = 2048) whole: relative Frobenius error <= 1e-2 against fp32 accumulation."""
     from warpy_kernels import gemm
 
     g = torch.Generator(device=cuda).manual_seed(0)
