@@ -45,6 +45,12 @@ extern "C" {
  * kernel in this library, 0 if not, WK_E_ARG for an unknown name.  Host only. */
 int wk_query(const char* feature);
 
+/* Replaces warpy_kernels/arch.py:29-60 (device_arch): 100 if CUDA device `device` (-1 = the current one)
+ * is compute capability 10.x, WK_E_UNSUPPORTED if it is anything else, WK_E_CUDA if there is no such
+ * device.  Every compute entry point below makes the same check on the current device before it
+ * launches anything.  Host only. */
+int wk_device_arch(int device);
+
 /* Synchronises the current device, returns its status word (0 = no kernel gave up
  * on a wait) and clears it.  Negative on a CUDA error. */
 int wk_status(void);

@@ -243,7 +243,6 @@ def test_autotune_stores_the_winner(cuda, tmp_path, monkeypatch):
     from warpy_kernels_b200 import utils
 
     monkeypatch.setattr(utils, "TUNE_CACHE_PATH", str(tmp_path / "tune.json"))
-    monkeypatch.setattr(utils, "_tune_cache", None)
     q, k, v = randn_qkv(1, 4, 2, 256, 384, 128, device=cuda)
     q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
     best, results = autotune_attn_fwd(q8, k8, v8, iters=2, verbose=False, q_descale=sq, k_descale=sk, v_descale=sv,

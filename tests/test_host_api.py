@@ -44,7 +44,7 @@ def test_import_surface_matches_reference():
     import warpy_kernels
     from warpy_kernels import attn_bwd, attn_fwd, autotune_gemm, device_arch, gemm, make_gemm, supports  # noqa: F401
     import warpy_kernels.attn  # noqa: F401
-    from warpy_kernels.utils import time_launch_ms, round_up, pad_rows, check_descale  # noqa: F401
+    from warpy_kernels.utils import time_launch_ms, round_up, check_descale, tune_key  # noqa: F401
 
     assert set(warpy_kernels.__all__) >= {
         "attn_bwd", "attn_fwd", "autotune_gemm", "device_arch", "gemm", "make_gemm", "supports",
@@ -103,14 +103,13 @@ def test_tune_cache_uses_the_reference_file_format(tmp_path, monkeypatch):
 
     path = tmp_path / "cache" / "tune.json"
     monkeypatch.setattr(utils, "TUNE_CACHE_PATH", str(path))
-    monkeypatch.setattr(utils, "_tune_cache", None)
     key = utils.tune_key("fwd", 128, True, 4096, 4000, 4)
     assert key == "fwd|d=128|causal=1|nq=4096|nk=4096|rep=4|sm100"
     assert utils.tune_key("bwd_bf16", 64, False, 5, 1025, 1, arch=120) == "bwd_bf16|d=64|causal=0|nq=1024|nk=2048|rep=1"
     assert utils.tune_lookup(key) is None
     utils.tune_store(key, {"num_stages": 3})
     assert json.load(open(path)) == {key: {"num_stages": 3}}
-    monkeypatch.setattr(utils, "_tune_cache", None)  # a new process reads the file back
+    utils.forget_tune_cache()  # a new process reads the file back
     assert utils.tune_lookup(key) == {"num_stages": 3}
     best, results = utils.autotune("fwd", 128, False, 10, 10, 1, [{"a": 1}], lambda cfg: (lambda: None), 1, False) \
         if torch.cuda.is_available() else ({"a": 1}, [])

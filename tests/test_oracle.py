@@ -24,16 +24,25 @@ def load_attn(golden_dir, name):
     )
 
 
+def _same_to_ulps(got, want, rtol, atol):
+    finite = np.isfinite(want)
+    assert np.array_equal(np.isfinite(got), finite)
+    assert np.array_equal(got[~finite], want[~finite], equal_nan=True)
+    assert np.allclose(got[finite], want[finite], rtol=rtol, atol=atol)
+
+
 @pytest.mark.parametrize("name", ATTN)
 def test_attention_oracle_matches_reference_fixture(golden_dir, name):
     z, t = load_attn(golden_dir, name)
     qd, kd, vd = [x.requires_grad_() for x in R.dequantize_qkv(t["q8"], t["k8"], t["v8"], t["sq"], t["sk"], t["sv"])]
     out, lse = R.attention_reference(qd, kd, vd, t["causal"])
     out.backward(t["dout"].float())
-    assert np.array_equal(out.detach().numpy().astype(np.float16), z["out"])
-    assert np.array_equal(lse.detach().numpy(), z["lse"])  # includes -inf rows
+    # fp32 reductions on the CPU depend on how torch splits them over threads (one thread under torchrun, all
+    # cores otherwise), so the pin is to a few ulp, not to the bit; the pattern of non-finite entries is exact
+    _same_to_ulps(out.detach().numpy(), z["out"].astype(np.float32), rtol=2.0**-10, atol=2.0**-14)  # stored as fp16
+    _same_to_ulps(lse.detach().numpy(), z["lse"], rtol=2e-6, atol=2e-6)  # includes -inf rows
     for got, key in ((qd.grad, "dq"), (kd.grad, "dk"), (vd.grad, "dv")):
-        assert np.array_equal(got.numpy(), z[key])
+        _same_to_ulps(got.numpy(), z[key], rtol=2e-5, atol=2e-6 * float(np.abs(z[key]).max()))
 
 
 @pytest.mark.parametrize("name", ATTN)

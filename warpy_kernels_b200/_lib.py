@@ -20,6 +20,7 @@ WK_BF16, WK_F32 = 0, 1
 # name -> (restype, argtypes); must list every function the header declares
 SIGNATURES = {
     "wk_query": (_i32, [_str]),
+    "wk_device_arch": (_i32, [_i32]),
     "wk_status": (_i32, []),
     "wk_error_string": (_str, [_i32]),
     "wk_quantize_mx": (_i32, [_ptr, _i32, _i64, _i64, _i64, _ptr, _ptr, _ptr]),

@@ -1,98 +1,96 @@
-"""Capability table of the B200 build.
+"""Which GPU this build runs on and which features it has.
 
-Mirrors ``warpy_kernels/arch.py:3-116`` of the reference (``device_arch``, ``supports``, ``require``) with one
-architecture: compute capability 10.0 -> 100.  The feature names are the reference's.
+Same three functions and error types as the reference's ``warpy_kernels/arch.py`` (``device_arch`` ``:29-60``,
+``supports`` ``:69-94``, ``require`` ``:97-116``), but the answers are not a Python table: the compiled library
+says which device it accepts (``wk_device_arch``: compute capability 10.x is architecture 100) and which of the
+reference's feature names it has a kernel for (``wk_query``), so the Python layer cannot drift from the kernels.
 """
 
 import torch
 
-ARCHS = {(10, 0): 100, (10, 3): 100}
-NAMES = {100: "SM100"}
-SUPPORTED = "compute capability 10.0 (SM100, B200)"
+from . import _lib
 
-# usable shared memory bytes per CTA
-_SMEM_LIMIT = {100: 232448}
+ARCH = 100
+ARCH_NAME = "SM100"
+SUPPORTED = "compute capability 10.x (SM100, B200)"
 
-_FEATURES = {
-    "gemm": (100,),
-    "gemm_gelu": (100,),
-    "gemm_dgelu": (100,),
-    "gemm_accum": (100,),
-    "gemm_fp8": (100,),
-    "gemm_mx": (100,),
-    "gemm_mx_out": (100,),
-    "attn_fwd": (100,),
-    "attn_bwd": (100,),
-    "attn_fwd_fp8": (100,),
-    "attn_bwd_fp8": (100,),
-}
+# the reference's feature vocabulary; wk_query() knows the same names
+FEATURES = (
+    "gemm", "gemm_gelu", "gemm_dgelu", "gemm_accum", "gemm_fp8", "gemm_mx", "gemm_mx_out",
+    "attn_fwd", "attn_bwd", "attn_fwd_fp8", "attn_bwd_fp8",
+)
 
-_device_arch = {}
+_arch_of_index = {}
+
+
+def _device_index(device):
+    """CUDA device ordinal of a tensor, ``torch.device``, string, integer or ``None`` (= the current device)."""
+    if isinstance(device, torch.Tensor):
+        device = device.device
+    if isinstance(device, int):
+        return device
+    if device is not None:
+        index = torch.device(device).index
+        if index is not None:
+            return index
+    return torch.cuda.current_device()
 
 
 def device_arch(device=None):
-    """Return the architecture of a CUDA device as a number (100 for B200).
+    """Architecture number of a CUDA device: 100 for B200.
 
     Args:
         device: CUDA device, index or tensor. Defaults to the current device.
 
     Raises:
-        NotImplementedError: If there is no usable CUDA device or it is not compute capability 10.x.
+        NotImplementedError: If there is no usable CUDA device or the library has no kernels for it.
     """
     if not torch.cuda.is_available():
-        raise NotImplementedError(f"warpy_kernels needs a usable CUDA device; supported: {SUPPORTED}")
-    if isinstance(device, torch.Tensor):
-        device = device.device
-    if device is None:
-        idx = torch.cuda.current_device()
-    elif isinstance(device, int):
-        idx = device
-    else:
-        device = torch.device(device)
-        idx = device.index if device.index is not None else torch.cuda.current_device()
-    arch = _device_arch.get(idx)
-    if arch is None:
-        cap = torch.cuda.get_device_capability(idx)
-        if cap not in ARCHS:
+        raise NotImplementedError(f"warpy_kernels found no usable CUDA device; it runs on {SUPPORTED}")
+    index = _device_index(device)
+    if index not in _arch_of_index:
+        answer = _lib.lib().wk_device_arch(index)
+        if answer != ARCH:
+            capability = torch.cuda.get_device_capability(index)
             raise NotImplementedError(
-                f"warpy_kernels has no kernels for compute capability {cap}; supported: {SUPPORTED}"
+                f"this build of warpy_kernels runs on {SUPPORTED}; device {index} is compute capability "
+                f"{capability[0]}.{capability[1]} ({_lib.lib().wk_error_string(answer).decode()})"
             )
-        arch = _device_arch[idx] = ARCHS[cap]
-    return arch
+        _arch_of_index[index] = answer
+    return _arch_of_index[index]
 
 
-def smem_limit(arch):
-    return _SMEM_LIMIT[arch]
+def _has_kernel(feature):
+    answer = _lib.lib().wk_query(feature.encode())
+    if answer < 0:
+        raise ValueError(f"unknown feature {feature!r}; the feature names are: {', '.join(FEATURES)}")
+    return answer == 1
 
 
 def supports(feature, device=None):
-    """Return whether a feature runs on a GPU.
+    """Whether ``feature`` runs on a GPU.
 
     Args:
-        feature: One of the reference's feature names: ``"gemm"``, ``"gemm_gelu"``, ``"gemm_dgelu"``,
-            ``"gemm_accum"``, ``"gemm_fp8"``, ``"gemm_mx"``, ``"gemm_mx_out"``, ``"attn_fwd"``, ``"attn_bwd"``,
-            ``"attn_fwd_fp8"``, ``"attn_bwd_fp8"``.
-        device: CUDA device, index or tensor, or the architecture number 100.
+        feature: One of the reference's feature names (``FEATURES``).
+        device: CUDA device, index or tensor, or the architecture number 100. Other architecture numbers (the
+            reference's 80, 86, 89, 120) are answered with ``False``: this build has kernels for 100 only.
 
     Raises:
-        ValueError: If ``feature`` is not one of the names above.
+        ValueError: If ``feature`` is not a feature name.
     """
-    if feature not in _FEATURES:
-        raise ValueError(f"unknown feature {feature!r}; known: {', '.join(_FEATURES)}")
-    if isinstance(device, int) and device in NAMES:
-        arch = device
-    else:
-        try:
-            arch = device_arch(device)
-        except NotImplementedError:
-            return False
-    return arch in _FEATURES[feature]
+    built = _has_kernel(feature)
+    if isinstance(device, int) and device >= 50:  # an architecture number, not a device ordinal
+        return built and device == ARCH
+    try:
+        device_arch(device)
+    except NotImplementedError:
+        return False
+    return built
 
 
 def require(feature, device):
-    """Raise ``NotImplementedError`` unless ``feature`` runs on ``device``; return the architecture number."""
+    """Return the architecture number of ``device``; raise ``NotImplementedError`` unless ``feature`` runs there."""
     arch = device_arch(device)
-    if arch not in _FEATURES[feature]:
-        archs = ", ".join(NAMES[a] for a in _FEATURES[feature]) or "no architecture of this build"
-        raise NotImplementedError(f"warpy_kernels has no {feature} for {NAMES[arch]}; supported on: {archs}")
+    if not _has_kernel(feature):
+        raise NotImplementedError(f"this build of warpy_kernels has no {feature} kernel for {ARCH_NAME}")
     return arch

@@ -738,6 +738,7 @@ extern "C" int wk_attn_bwd_bf16(const wk_attn_bwd_args* a, void* stream) {
     if (a->out_strides[i] % 4 || a->out_strides[i] <= 0) return WK_E_ARG;
   }
   if (a->workspace_bytes < wk_attn_bwd_bf16_workspace_bytes(a->B, a->Hq, a->Nq)) return WK_E_ARG;
+  if (int unsupported = require_sm100()) return unsupported;
   int* status = status_word();
   if (!status) return WK_E_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

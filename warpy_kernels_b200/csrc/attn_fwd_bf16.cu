@@ -422,6 +422,7 @@ extern "C" int wk_attn_fwd_bf16(const wk_attn_fwd_args* a, void* stream) {
     if (a->out_strides[i] % 8 || a->out_strides[i] <= 0) return WK_E_ARG;
   }
   if (a->B > 65535 || a->Hq > 65535) return WK_E_ARG;
+  if (int unsupported = require_sm100()) return unsupported;
   int* status = status_word();
   if (!status) return WK_E_CUDA;
 

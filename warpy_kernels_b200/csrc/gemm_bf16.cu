@@ -227,6 +227,7 @@ extern "C" int wk_gemm_16bit(const wk_gemm16_args* g, void* stream) {
   if ((g->pre_out && !aligned16(g->pre_out)) || (g->pre_in && !aligned16(g->pre_in))) return WK_E_ARG;
   if (g->scale_b && g->scale_b_cols && !aligned16(g->scale_b)) return WK_E_ARG;
   if ((g->q_mx != nullptr) != (g->s_mx != nullptr) || (g->q_mx && !aligned16(g->q_mx))) return WK_E_ARG;
+  if (int unsupported = require_sm100()) return unsupported;
   int* status = status_word();
   if (!status) return WK_E_CUDA;
 

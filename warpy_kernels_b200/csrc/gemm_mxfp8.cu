@@ -296,6 +296,7 @@ extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
   if (!epilogue_args_ok(a)) return WK_E_ARG;
   if (a->cta_pair < 0 || a->cta_pair > 2) return WK_E_ARG;
   if (a->workspace_bytes < wk_gemm_mxfp8_workspace_bytes(m, n, k)) return WK_E_ARG;
+  if (int unsupported = require_sm100()) return unsupported;
   int* status = status_word();
   if (!status) return WK_E_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -402,6 +403,7 @@ extern "C" int wk_gemm_mxfp8_noalloc(const wk_gemm_mx_args* a, void* stream) {
   if (wk_gemm_mxfp8_workspace_bytes(m, n, k) > kNoAllocScratchBytes) return WK_E_TOO_LARGE;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return WK_E_CUDA;
+  if (int unsupported = require_sm100()) return unsupported;
   int r = noalloc_setup(dev);
   if (r) return r;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -69,6 +69,27 @@ int* status_word() {
   return g_status[dev];
 }
 
+int device_arch_of(int dev) {
+  // compute capability 10.x -> 100; remembered per device (0 = not asked yet)
+  static int known[kMaxDevices] = {};
+  if (dev < 0 || dev >= kMaxDevices) return WK_E_ARG;
+  if (known[dev]) return known[dev];
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+    cudaGetLastError();  // leave no sticky error behind for the caller's next launch check
+    return WK_E_CUDA;
+  }
+  known[dev] = major == 10 ? 100 : WK_E_UNSUPPORTED;
+  return known[dev];
+}
+
+int require_sm100() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return WK_E_CUDA;
+  const int arch = device_arch_of(dev);
+  return arch == 100 ? 0 : arch;
+}
+
 int sm_count() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
@@ -116,6 +137,14 @@ int wk_query(const char* feature) {
   for (const char* f : kYes)
     if (!strcmp(f, feature)) return 1;
   return WK_E_ARG;  // every feature name of the reference is built; anything else is not a feature
+}
+
+int wk_device_arch(int device) {
+  if (device < 0 && cudaGetDevice(&device) != cudaSuccess) {
+    cudaGetLastError();
+    return WK_E_CUDA;
+  }
+  return wk::device_arch_of(device);
 }
 
 int wk_status(void) {

@@ -18,6 +18,13 @@ int encode_tmap(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank, cons
 // Device pointer of the int status word of the current device (allocated on first use).
 int* status_word();
 
+// 100 for a device of compute capability 10.x, WK_E_UNSUPPORTED for any other, WK_E_CUDA if it cannot be asked.
+int device_arch_of(int dev);
+
+// 0 if the current device can run this library's kernels, else the negative code an entry point returns
+// (WK_E_UNSUPPORTED for a device that is not compute capability 10.x).  Allocates nothing.
+int require_sm100();
+
 // Number of SMs of the current device (cached).
 int sm_count();
 

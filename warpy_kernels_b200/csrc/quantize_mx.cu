@@ -128,6 +128,7 @@ extern "C" int wk_quantize_mx(const void* x, int dtype, int64_t rows, int64_t co
   if (cols / 8 > 0x7fffffff || rows > 0x7fffffff) return WK_E_ARG;
   if (rows == 0 || cols == 0) return 0;
   if (!x || !q || !s || !wk::aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 7)) return WK_E_ARG;
+  if (int unsupported = wk::require_sm100()) return unsupported;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == WK_BF16)
     return wk::launch(static_cast<const __nv_bfloat16*>(x), rows, cols, ld_x,

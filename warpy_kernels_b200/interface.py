@@ -8,11 +8,16 @@ from .gemm.api import autotune_gemm, gemm, make_gemm
 __all__ = ["attn_bwd", "attn_fwd", "autotune_gemm", "gemm", "make_gemm"]
 
 
-def _check(q, what, feature, dtypes):
-    if q.dtype not in dtypes:
-        names = " and ".join(str(t).removeprefix("torch.") for t in dtypes)
-        raise NotImplementedError(f"warpy_kernels has no {what} for {q.dtype} yet; supported: {names}")
-    require(feature if q.dtype == torch.bfloat16 else f"{feature}_fp8", q)
+_ATTN_DTYPES = {torch.float8_e4m3fn: "_fp8", torch.bfloat16: ""}
+
+
+def _check(q, what, feature):
+    """Gate an attention entry point on the dtype of ``q`` and on the GPU it lives on."""
+    suffix = _ATTN_DTYPES.get(q.dtype)
+    if suffix is None:
+        accepted = ", ".join(str(t).split(".")[-1] for t in _ATTN_DTYPES)
+        raise NotImplementedError(f"the attention {what} takes {accepted} inputs, not {q.dtype}")
+    require(feature + suffix, q)
 
 
 def attn_fwd(q, k, v, q_descale=None, k_descale=None, v_descale=None, causal=False, softmax_scale=None, **config):
@@ -38,7 +43,7 @@ def attn_fwd(q, k, v, q_descale=None, k_descale=None, v_descale=None, causal=Fal
     """
     from .attn import attn_fwd as _attn_fwd
 
-    _check(q, "forward kernel", "attn_fwd", (torch.float8_e4m3fn, torch.bfloat16))
+    _check(q, "forward", "attn_fwd")
     return _attn_fwd(q, k, v, q_descale, k_descale, v_descale, causal, softmax_scale, **config)
 
 
@@ -56,7 +61,7 @@ def attn_bwd(
     """
     from .attn import attn_bwd as _attn_bwd
 
-    _check(q, "backward kernel", "attn_bwd", (torch.float8_e4m3fn, torch.bfloat16))
+    _check(q, "backward", "attn_bwd")
     return _attn_bwd(
         q, k, v, out, lse, pmax, dout, q_descale, k_descale, v_descale, causal, softmax_scale, **config
     )
