@@ -221,8 +221,19 @@ typedef struct {
   int32_t ctas_per_sm; /* fp8 forward: 2 = two CTAs per SM with 64-key tiles, 1 = one CTA per SM with 128-key
                           rounds and four softmax groups (long sequences), 0 = pick by Nk.  The reference's
                           tuning option of the same name (warpy_kernels/attn/fwd_api.py:196-208) */
+  void* workspace;     /* optional scratch of wk_attn_fwd_workspace_bytes(B, Hq, Nq) bytes, 4-byte aligned: one
+                          flag per block of 128 queries.  It must hold zeros when the call is made and holds zeros
+                          again when the call's work has completed, so one buffer can serve every call on a stream.
+                          The tensor-core kernels keep one reference exponent per query row, taken from the row's
+                          first 64 keys; a query block in which some later key lies more than 2^100 (69 nats) above
+                          it is flagged there and recomputed by a plain two-pass fp32 kernel (exact row maximum
+                          first), which is what the reference's moving tile maximum
+                          (warpy_kernels/attn/fwd_base.py:337-360) achieves.  NULL: no recomputation; such an
+                          input then leaves WK_ERR_RANGE (110) in the status word and a wrong result. */
+  int64_t workspace_bytes;
 } wk_attn_fwd_args;
 
+int64_t wk_attn_fwd_workspace_bytes(int B, int Hq, int Nq);
 int wk_attn_fwd_fp8(const wk_attn_fwd_args* args, void* stream);
 
 /* BF16 attention forward: q, k, v bf16 (element strides multiples of 8), the three descale

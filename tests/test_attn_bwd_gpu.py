@@ -21,6 +21,7 @@ SHAPES = [
     (2, 4, 2, 1000, 1000, 128),
     (1, 2, 1, 300, 777, 64),
     (1, 2, 2, 512, 1024, 128),
+    (1, 4, 4, 2048, 2048, 64),
     (1, 2, 1, 512, 128, 128),
     (1, 2, 1, 512, 128, 64),
     (1, 8, 2, 384, 640, 128),
@@ -68,34 +69,39 @@ def test_reference_shapes(cuda, shape, causal):
     check_grads(got, _oracle_grads(q8, k8, v8, sq, sk, sv, dout, causal))
 
 
-def test_repeat_is_bit_identical(cuda):
-    """Four runs: dK and dV bit-identical ("else a race", ``tests/attn/test_grad.py:108-135``); dQ too, since this
-    backward has no atomics."""
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", [(1, 4, 2, 640, 640, 128), (2, 4, 2, 1000, 1000, 128), (1, 4, 4, 2048, 2048, 64)])
+def test_repeat_is_bit_identical(cuda, shape, causal):
+    """Four runs: dK and dV bit-identical ("else a race", the reference's ``repeat`` shapes,
+    ``tests/attn/test_grad.py:108-135``); dQ too, since this backward has no atomics."""
     from warpy_kernels import attn_bwd, attn_fwd
 
-    q, k, v = randn_qkv(1, 4, 2, 640, 640, 128, seed=3, device=cuda)
+    q, k, v = randn_qkv(*shape, seed=3, device=cuda)
     q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
     dout = torch.randn(q.shape, device=cuda).bfloat16()
-    out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
-    first = attn_bwd(q8, k8, v8, out, lse, pmax, dout, sq, sk, sv, causal=True)
+    out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=causal)
+    first = attn_bwd(q8, k8, v8, out, lse, pmax, dout, sq, sk, sv, causal=causal)
     for _ in range(3):
-        again = attn_bwd(q8, k8, v8, out, lse, pmax, dout, sq, sk, sv, causal=True, deterministic=True)
+        again = attn_bwd(q8, k8, v8, out, lse, pmax, dout, sq, sk, sv, causal=causal, deterministic=True)
         for a, b in zip(first, again):
             assert torch.equal(a, b)
 
 
-def test_hard_inputs_mean_over_seeds(cuda):
-    """Peaky softmax, log-normal dO row norms (``grad_hard``, ``tests/attn/test_grad.py``): mean error over 3 seeds."""
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", [(1, 4, 2, 512, 512, 128), (1, 4, 2, 1024, 1024, 128), (1, 4, 4, 1024, 1024, 64)])
+def test_hard_inputs_mean_over_seeds(cuda, shape, causal):
+    """Peaky softmax, log-normal dO row norms (``grad_hard`` with the reference's ``HARD_SHAPES``,
+    ``tests/attn/test_grad.py:87-105``): mean error over 3 seeds."""
     from warpy_kernels import attn_bwd, attn_fwd
 
     errs = {"dq": 0.0, "dk": 0.0, "dv": 0.0}
     for seed in range(3):
-        q, k, v, dout = hard_inputs(1, 4, 2, 512, 512, 128, seed=seed, device=cuda)
+        q, k, v, dout = hard_inputs(*shape, seed=seed, device=cuda)
         dout = dout.bfloat16()
         q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
-        out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
-        got = attn_bwd(q8, k8, v8, out, lse, pmax, dout, sq, sk, sv, causal=True)
-        want = _oracle_grads(q8, k8, v8, sq, sk, sv, dout, True)
+        out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=causal)
+        got = attn_bwd(q8, k8, v8, out, lse, pmax, dout, sq, sk, sv, causal=causal)
+        want = _oracle_grads(q8, k8, v8, sq, sk, sv, dout, causal)
         for name, g, w in zip(errs, got, want):
             errs[name] += R.rel_l2(g, w) / 3
     assert max(errs.values()) <= 8e-2, errs

@@ -98,6 +98,49 @@ def test_config4_gqa_long_context_one_kv_group(cuda):
         assert (lse[0, h, rows] - lse_ref[0, 0]).abs().max().item() <= 5e-2
 
 
+def test_config4_gqa_long_context_whole_shape(cuda):
+    """The GQA benchmark shape whole, as one GPU runs it (B1 Hq64 Hkv8 N32768 d128, causal: 16384 query blocks through the persistent kernel's
+    hand-over): slices at the start, in the middle and at the end of heads from different KV groups against the oracle,
+    plus the properties of a probability row for every row."""
+    from warpy_kernels import attn_fwd
+
+    N = 32768
+    q8, k8, v8, sq, sk, sv = _attn_inputs(cuda, 1, 64, 8, N, 128, 4)
+    out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
+    for h, rows in ((0, slice(0, 384)), (13, slice(16000, 16256)), (42, slice(N - 4224, N - 3968)), (63, slice(N - 256, N))):
+        ref, lse_ref = _oracle_head(q8, k8, v8, sq, sk, sv, 0, h, rows)
+        assert R.cosine(out[0, h, rows].float(), ref[0, 0]) >= 0.999, h
+        assert R.max_abs(out[0, h, rows].float(), ref[0, 0]) <= 2e-2, h
+        assert (lse[0, h, rows] - lse_ref[0, 0]).abs().max().item() <= 5e-2, h
+    assert torch.isfinite(lse).all() and bool((pmax > 0).all()) and bool((pmax <= 1.0001).all())
+    vmax = (v8.float().abs().amax() * sv[0, 0]).item()
+    assert out.float().abs().max().item() <= vmax * 1.01
+
+
+def test_config2_sized_gqa_backward(cuda):
+    """A backward of the benchmark's size with grouped heads (B2 Hq32 Hkv8 N4096 d128, causal): all gradients of one
+    KV group (its four query heads' dQ, its dK and dV) against autograd through the oracle."""
+    from warpy_kernels import attn_bwd, attn_fwd
+
+    B, Hq, Hkv, N, d = 2, 32, 8, 4096, 128
+    q8, k8, v8, sq, sk, sv = _attn_inputs(cuda, B, Hq, Hkv, N, d, 1)
+    dout = torch.randn(B, Hq, N, d, device=cuda, generator=torch.Generator(device=cuda).manual_seed(7)).bfloat16()
+    out, lse, pmax = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
+    dq, dk, dv = attn_bwd(q8, k8, v8, out, lse, pmax, dout, sq, sk, sv, causal=True)
+    b, hk = 1, 5
+    heads = slice(4 * hk, 4 * hk + 4)
+    qd = (q8[b, heads].float() * sq[b, hk])[None].requires_grad_()
+    kd = (k8[b, hk].float() * sk[b, hk])[None, None].requires_grad_()
+    vd = (v8[b, hk].float() * sv[b, hk])[None, None].requires_grad_()
+    ref, _ = R.attention_reference(qd, kd, vd, True)
+    ref.backward(dout[b, heads].float()[None])
+    for got, want in ((dq[b, heads], qd.grad[0]), (dk[b, hk], kd.grad[0, 0]), (dv[b, hk], vd.grad[0, 0])):
+        assert R.cosine(got.float(), want) >= 0.995
+        assert R.rel_l2(got.float(), want) <= 8e-2
+    for g in (dq, dk, dv):
+        assert not torch.isnan(g).any()
+
+
 @pytest.mark.parametrize("n,k", [(14336, 4096), (4096, 14336)])
 def test_config3_mxfp8_gemm_m8192(cuda, n, k):
     """The MXFP8 GEMM benchmark shape (M8192 N14336 K4096): a band of rows against the oracle, and linearity in the scale bytes: raising every scale

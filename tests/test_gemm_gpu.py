@@ -429,3 +429,70 @@ def test_mx_cta_pair_kernel_matches_single_cta_kernel(cuda, shape):
     got = gemm(a8, b8, out=c0.clone(), cta_pair=True, **kw)
     want = gemm(a8, b8, out=c0.clone(), cta_pair=False, **kw)
     assert len(got) == len(want) and all(torch.equal(x.view(torch.uint8), y.view(torch.uint8)) for x, y in zip(got, want))
+
+
+# ---- accumulator precision of the block-scaled MMA (tests/gemm/test_gemm.py:244-301 of the reference) -------------
+def _wide(r, c, gen, device):
+    """Magnitudes from e4m3 subnormals to near 448, random signs (``tests/gemm/test_gemm.py:244-249``)."""
+    e = torch.rand(r, c, device=device, generator=gen) * 17.8 - 9.0
+    s = torch.randint(0, 2, (r, c), device=device, generator=gen) * 2 - 1
+    return s * torch.exp2(e)
+
+
+def _fp8_inputs(kind, m, n, k, device):
+    gen = torch.Generator(device=device).manual_seed(0)
+    if kind == "normal":
+        a, b = torch.randn(m, k, device=device, generator=gen), torch.randn(n, k, device=device, generator=gen)
+    elif kind == "wide":
+        a, b = _wide(m, k, gen, device), _wide(n, k, gen, device)
+    else:  # "cancel": the exact results are 0
+        a = torch.randn(m, k // 2, device=device, generator=gen) * 16
+        b = torch.randn(n, k // 2, device=device, generator=gen) * 16
+        a, b = torch.cat([a, -a], 1), torch.cat([b, b], 1)
+    return a.to(FP8), b.to(FP8)
+
+
+@pytest.mark.parametrize("cta_pair", [False, True])
+@pytest.mark.parametrize("kind", ["normal", "wide", "cancel"])
+def test_fp8_block_scaled_mma_accumulator(cuda, kind, cta_pair):
+    """The reference's ``fp8_block_scaled_mma`` case for the tcgen05 ``kind::mxf8f6f4`` path of both MXFP8 kernels.
+
+    Subtracting ``bf16(ref)`` through ``accum=True`` leaves the low accumulator bits in the bf16 output; the residual
+    against a float64 product must stay within ``K / 32`` units of ``2^-21 . (|a| @ |b|^T)``, the reference's bound for
+    a truncating 22-bit accumulator.  With MX scale bytes on both operands (powers of two: exact in float64) the same
+    bound must hold.  The ``cancel`` inputs, whose exact result is 0, leave only the rounding of the partial sums,
+    which the same bound covers (an fp32 accumulator does not return an exact 0 there).
+    """
+    from warpy_kernels import gemm
+
+    m, n, k = 512, 512, 4096
+    a, b = _fp8_inputs(kind, m, n, k, cuda)
+    ad, bd = a.double(), b.double()
+    ref = ad @ bd.T
+    c0 = (-ref).to(torch.bfloat16)
+    plain = gemm(a, b, cta_pair=cta_pair)
+    resid = gemm(a, b, out=c0.clone(), accum=True, cta_pair=cta_pair)
+    assert torch.equal(plain, gemm(a, b, cta_pair=not cta_pair)), "the two MXFP8 kernels differ"
+    unit = ((ad.abs() @ bd.abs().T) * 2.0**-21).clamp_min(1e-300)
+    err = ((resid.double() - c0.double() - ref).abs() / unit).max().item()
+    assert err <= k / 32, f"accumulator error {err} units of 2^-21 (bound {k / 32})"
+    if kind == "cancel":
+        assert (plain.double().abs() / unit).max().item() <= k / 32, "cancelling product left more than the bound"
+    # the same with block scales on both operands
+    g = torch.Generator(device=cuda).manual_seed(1)
+    sa = torch.randint(120, 134, (m, k // 32), device=cuda, generator=g, dtype=torch.uint8)
+    sb = torch.randint(120, 134, (n, k // 32), device=cuda, generator=g, dtype=torch.uint8)
+    if kind == "cancel":  # keep the two halves of K on equal scales so that the product still cancels
+        sa = torch.cat([sa[:, : k // 64], sa[:, : k // 64]], 1).contiguous()
+        sb = torch.cat([sb[:, : k // 64], sb[:, : k // 64]], 1).contiguous()
+    asd = ad * torch.exp2(sa.double() - 127).repeat_interleave(32, 1)
+    bsd = bd * torch.exp2(sb.double() - 127).repeat_interleave(32, 1)
+    ref_s = asd @ bsd.T
+    c1 = (-ref_s).to(torch.bfloat16)
+    resid_s = gemm(a, b, a_scale_mx=sa, b_scale_mx=sb, out=c1.clone(), accum=True, cta_pair=cta_pair)
+    unit_s = ((asd.abs() @ bsd.abs().T) * 2.0**-21).clamp_min(1e-300)
+    err_s = ((resid_s.double() - c1.double() - ref_s).abs() / unit_s).max().item()
+    assert err_s <= k / 32, f"accumulator error {err_s} units with MX scales (bound {k / 32})"
+    if kind == "cancel":
+        left = gemm(a, b, a_scale_mx=sa, b_scale_mx=sb, cta_pair=cta_pair)
+        assert (left.double().abs() / unit_s).max().item() <= k / 32

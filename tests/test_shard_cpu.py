@@ -21,15 +21,24 @@ def test_split_range_covers_everything():
             assert max(sizes) - min(sizes) <= 1
 
 
-@pytest.mark.parametrize("B,Hkv,world", [(4, 32, 8), (1, 8, 8), (1, 8, 4), (2, 3, 4), (1, 8, 3)])
+@pytest.mark.parametrize("B,Hkv,world", [(4, 32, 8), (4, 32, 1), (4, 32, 3), (1, 8, 8), (1, 8, 4), (2, 3, 4), (1, 8, 3),
+                                          (5, 2, 3)])
 def test_attention_shard_partitions_batch_times_kv_heads(B, Hkv, world):
     seen = []
     for r in range(world):
-        for b, h0, h1 in shard.attention_shard(B, Hkv, world, r):
-            assert 0 <= h0 < h1 <= Hkv
-            seen += [(b, h) for h in range(h0, h1)]
-    assert sorted(seen) == [(b, h) for b in range(B) for h in range(Hkv)]
-    assert len(seen) == len(set(seen))
+        pieces = shard.attention_shard(B, Hkv, world, r)
+        assert len(pieces) <= 3
+        mine = []
+        for b0, b1, h0, h1 in pieces:
+            assert 0 <= b0 < b1 <= B and 0 <= h0 < h1 <= Hkv
+            assert b1 - b0 == 1 or (h0, h1) == (0, Hkv)  # only whole batch items are merged
+            mine += [b * Hkv + h for b in range(b0, b1) for h in range(h0, h1)]
+        lo, hi = shard.attention_units(B, Hkv, world, r)
+        assert mine == list(range(lo, hi))  # in unit order, contiguous
+        seen += mine
+    assert seen == list(range(B * Hkv))
+    if world == 1:
+        assert shard.attention_shard(B, Hkv, 1, 0) == [(0, B, 0, Hkv)]  # one call on the whole tensors
 
 
 def test_gemm_shard_is_tile_aligned():
@@ -68,12 +77,21 @@ def _worker(rank, world, port, result_dir):
             return qs * ds[0].repeat_interleave(rep, 1)[:, :, None, None] + ks.repeat_interleave(rep, 1) - vs.repeat_interleave(rep, 1)
 
         want = fake_attn(q, k, v, (sq, None, None))
-        mine = []
-        for piece in shard.attention_shard(B, Hkv, world, rank):
+        # (a) the kernel writes into this rank's slab through per-piece views: nothing is copied before the gather
+        slab, views = shard.local_head_slab(want.shape, Hkv, world, rank, want.dtype, want.device)
+        pieces = shard.attention_shard(B, Hkv, world, rank)
+        for piece, view in zip(pieces, views):
             qs, ks, vs, ds = shard.slice_attention_inputs(q, k, v, (sq, None, None), piece)
-            mine.append((piece, fake_attn(qs, ks, vs, ds)))
-        got = shard.gather_heads(mine, want.shape, B, Hkv, want.dtype, want.device)
-        assert torch.equal(got, want)
+            view.copy_(fake_attn(qs, ks, vs, ds))
+        assert torch.equal(shard.gather_heads(slab, want.shape, Hkv), want)
+        # (b) a list of per-piece tensors works too
+        mine = [fake_attn(*shard.slice_attention_inputs(q, k, v, (sq, None, None), piece)[:3],
+                          shard.slice_attention_inputs(q, k, v, (sq, None, None), piece)[3]) for piece in pieces]
+        assert torch.equal(shard.gather_heads(mine, want.shape, Hkv), want)
+        # uneven split: 5 batch items x 1 KV head over 2 ranks
+        q5 = torch.randn(5, 2, N, d, generator=g)
+        lo5, hi5 = shard.attention_units(5, 1, world, rank)
+        assert torch.equal(shard.gather_heads([q5[lo5:hi5] * 2], q5.shape, 1), q5 * 2)
         open(os.path.join(result_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()

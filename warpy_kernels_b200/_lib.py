@@ -26,6 +26,7 @@ SIGNATURES = {
     "wk_quantize_mx": (_i32, [_ptr, _i32, _i64, _i64, _i64, _ptr, _ptr, _ptr]),
     "wk_gemm_bf16": (_i32, [_ptr, _ptr, _ptr, _i32, _i32, _i32, _ptr]),
     "wk_gemm_16bit": (_i32, [_ptr, _ptr]),
+    "wk_attn_fwd_workspace_bytes": (_i64, [_i32, _i32, _i32]),
     "wk_attn_fwd_fp8": (_i32, [_ptr, _ptr]),
     "wk_attn_fwd_bf16": (_i32, [_ptr, _ptr]),
     "wk_attn_bwd_fp8_workspace_bytes": (_i64, [_i32, _i32, _i32]),

@@ -28,7 +28,24 @@ class _FwdArgs(ctypes.Structure):
         ("Nk", ctypes.c_int32), ("d", ctypes.c_int32),
         ("causal", ctypes.c_int32), ("write_lse", ctypes.c_int32), ("lse_natural", ctypes.c_int32),
         ("seqused_k", ctypes.c_void_p), ("softmax_scale", ctypes.c_float), ("ctas_per_sm", ctypes.c_int32),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64),
     ]
+
+
+_flag_buffers = {}
+
+
+def _block_flags(dev, nbytes):
+    """Zeroed flag scratch of the forward for the current stream of ``dev``, at least ``nbytes`` long.
+
+    The kernels mark query blocks whose scores outgrow the range of their fixed row reference; the library
+    recomputes those and hands the buffer back all zero, so calls that follow one another on a stream can share it.
+    """
+    key = (dev, torch.cuda.current_stream(dev).cuda_stream)
+    buf = _flag_buffers.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = _flag_buffers[key] = torch.zeros(max(nbytes, 1 << 16), dtype=torch.uint8, device=dev)
+    return buf
 
 
 def _kernel_view(x):
@@ -209,9 +226,11 @@ def make_attn_fwd(
     keep = (qv, kv, vv, dq_, dk_, dv_, seq, out_k)  # the launch closure owns what the argument block points at
     lib = _lib.lib()
     entry = lib.wk_attn_fwd_bf16 if bf16 else lib.wk_attn_fwd_fp8
+    args.workspace_bytes = lib.wk_attn_fwd_workspace_bytes(B, Hq, Nq)
 
     def launch():
         with torch.cuda.device(dev):
+            args.workspace = _block_flags(dev, args.workspace_bytes).data_ptr()
             code = entry(ctypes.byref(args), _lib.stream_ptr(dev))
         _lib.check(code, "attn_fwd")
         if not out_direct:

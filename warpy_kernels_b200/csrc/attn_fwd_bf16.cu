@@ -17,11 +17,13 @@
 // reference moves its reference exponent with the running maximum and rescales O, this kernel fixes m_ref per
 // row at the maximum of the first tile and never rescales: bf16 has the exponent range of fp32, so
 // P = 2^(s.beta - m_ref) keeps its eight significant bits whether it lies above or below 1.  Scores that outgrow
-// m_ref by more than 2^100 are reported through the status word (WK_ERR_RANGE).
+// m_ref by more than 2^100 make the kernel flag the query block in the call's workspace, and attn_fwd_redo.cu
+// computes it again with the exact row maximum (without a workspace: WK_ERR_RANGE in the status word).
 //
 // Tensor-core bound: 4 . B . Hq . Nq . Nk . d flops (half of that when causal).
 #include <math.h>
 
+#include "attn_fwd_redo.h"
 #include "common.cuh"
 #include "host_common.h"
 
@@ -62,6 +64,7 @@ struct FwdParams {
   float softmax_scale;
   int m_first;  // first query block of this launch (the grid covers gridDim.x blocks from here)
   int* status;
+  int* redo;    // one flag per query block, or null: blocks whose scores outgrow the row reference are recomputed
 };
 
 // One block of 32 keys of one row: P as 16 bf16 pairs and the sum of the unrounded values.
@@ -310,10 +313,6 @@ attn_fwd_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         const float cm = block_max(sraw) * beta;  // beta > 0 (checked on the host)
         m_true = fmaxf(m_true, cm);
-        if (cm - m_ref > MAX_BLOCK_EXP) {
-          // the scores have outgrown the first tile's maximum by more than 2^100: P would overflow bf16
-          atomicCAS(p.status, 0, WK_ERR_RANGE);
-        }
         // masked scores are -inf and give P = 0; a row without a visible key so far has m_ref = -inf
         const float bias = m_ref > -INFINITY ? -m_ref : 0.f;
         uint32_t w[16];
@@ -353,6 +352,14 @@ attn_fwd_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       asm volatile("ld.shared.f32 %0, [%1];" : "=f"(m_ref) : "r"(x_ref) : "memory");
       l += l_o;
       m_true = fmaxf(m_true, mt_o);
+    }
+    if (grp == 0 && m_true - m_ref > MAX_BLOCK_EXP) {
+      // Some key lies more than 2^100 above the first tile's maximum: P has overflowed bf16.  With a flag array the
+      // block is computed again (attn_fwd_redo.cu) and what is stored below is overwritten.
+      if (p.redo)
+        p.redo[attn_fwd_flag_index(b, hq, m_blk, p.Hq, (p.Nq + BM - 1) / BM)] = 1;
+      else
+        atomicCAS(p.status, 0, WK_ERR_RANGE);
     }
     if (ok) {
       tc_fence_after();
@@ -469,11 +476,18 @@ extern "C" int wk_attn_fwd_bf16(const wk_attn_fwd_args* a, void* stream) {
   p.seqused_k = a->seqused_k;
   p.softmax_scale = a->softmax_scale;
   p.status = status;
+  p.redo = static_cast<int*>(a->workspace);
+  if (a->workspace && (a->workspace_bytes < attn_fwd_flag_bytes(a->B, a->Hq, a->Nq) ||
+                       (reinterpret_cast<uintptr_t>(a->workspace) & 3)))
+    return WK_E_ARG;
 
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_bf16_kernel), SMEM_BYTES)) return WK_E_CUDA;
   const int num_m = (a->Nq + BM - 1) / BM;
   p.m_first = 0;
   dim3 grid(num_m, a->Hq, a->B);
-  attn_fwd_bf16_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  attn_fwd_bf16_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
+  if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+  // blocks the kernel flagged as beyond its exponent range are computed again (normally none)
+  return p.redo ? launch_attn_fwd_redo(a, true, p.redo, st) : 0;
 }

@@ -33,8 +33,9 @@
 // reference m_ref per row.  m_ref is the row maximum of the first tile (its largest
 // probability is then stored exactly, 2^8, as in the reference) and never moves: block
 // exponents above it are as good as below it.  Scores that outgrow it by more than 2^100
-// (69 nats) cannot be represented; the kernel then reports WK_ERR_RANGE through the
-// status word instead of returning a wrong result.  Query blocks that see at most 512 keys carry P as two
+// (69 nats) cannot be represented; the kernel then flags the query block in the call's workspace and the block is
+// computed again by attn_fwd_redo.cu with the exact row maximum (without a workspace: WK_ERR_RANGE in the status
+// word).  Query blocks that see at most 512 keys carry P as two
 // e4m3 terms (value + 2^-4 . residual): with so few keys the rounding of P would not
 // average out.
 //
@@ -43,6 +44,7 @@
 
 #include <type_traits>
 
+#include "attn_fwd_redo.h"
 #include "common.cuh"
 #include "host_common.h"
 
@@ -89,7 +91,18 @@ struct FwdParams {
   float softmax_scale;
   int m_first;  // first query block of this launch (the grid covers gridDim.x blocks from here)
   int* status;
+  int* redo;    // one flag per query block, or null: blocks whose scores outgrow the row reference are recomputed
 };
+
+// Some key of the row lies more than 2^MAX_BLOCK_EXP above the row reference: with a flag array the query block is
+// marked for recomputation (attn_fwd_redo.cu) and what this kernel stores for it is overwritten; without one the
+// status word says that the result is not to be trusted.
+__device__ __noinline__ void report_out_of_range(const FwdParams& p, int b, int hq, int m_blk) {
+  if (p.redo)
+    p.redo[attn_fwd_flag_index(b, hq, m_blk, p.Hq, (p.Nq + 127) / 128)] = 1;
+  else
+    atomicCAS(p.status, 0, WK_ERR_RANGE);
+}
 
 // One block of 32 keys of one row: P codes (and the residual codes) and the sum of the exact values.
 template <bool RESID>
@@ -366,11 +379,9 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         m_true = fmaxf(m_true, cm);
         const bool live = cm > -INFINITY;
         float kf = live ? ceilf(cm - m_ref) : 0.f;  // block exponent relative to the row reference
-        if (kf > MAX_BLOCK_EXP) {
-          // the scores have outgrown the first tile's maximum by more than 2^100: not representable here
-          atomicCAS(p.status, 0, WK_ERR_RANGE);
-          kf = MAX_BLOCK_EXP;
-        }
+        // scores more than 2^100 above the first tile's maximum are not representable here: clamped, and the
+        // epilogue reports the row (m_true - m_ref tells)
+        kf = fminf(kf, MAX_BLOCK_EXP);
         const float bias = live ? (static_cast<float>(P_OFFSET) - kf) - m_ref : 0.f;
         uint32_t w[8], wl[8];
         float sum_exact;
@@ -413,6 +424,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       l += l_o;
       m_true = fmaxf(m_true, mt_o);
     }
+    if (grp == 0 && m_true - m_ref > MAX_BLOCK_EXP) report_out_of_range(p, b, hq, m_blk);
     if (ok) {
       tc_fence_after();
       const bool empty = !(l > 0.f);
@@ -553,6 +565,7 @@ __device__ __noinline__ bool wide_store_output(const FwdParams& p, uint32_t xch,
     l += l_g;
     m_true = fmaxf(m_true, mt_g);
   }
+  if (grp == 0 && m_true - m_ref > MAX_BLOCK_EXP) report_out_of_range(p, b, hq, row / BM);
   if (!mbar_wait_warp(o_full, fin_ci & 1, p.status, WK_ERR_TIMEOUT_MMA)) return false;
   tc_fence_after();
   const bool empty = !(l > 0.f);
@@ -916,11 +929,9 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           m_true = fmaxf(m_true, cm[c]);
           const bool live = cm[c] > -INFINITY;
           float kf = live ? ceilf(cm[c] - m_ref) : 0.f;  // block exponent relative to the row reference
-          if (kf > MAX_BLOCK_EXP) {
-            // the scores have outgrown the first tile's maximum by more than 2^100: not representable here
-            atomicCAS(p.status, 0, WK_ERR_RANGE);
-            kf = MAX_BLOCK_EXP;
-          }
+          // scores more than 2^100 above the first tile's maximum are not representable here: clamped, and
+          // wide_store_output reports the row (m_true - m_ref tells)
+          kf = fminf(kf, MAX_BLOCK_EXP);
           const float bias = live ? (static_cast<float>(P_OFFSET) - kf) - m_ref : 0.f;
           uint32_t w[8], wl[8];
           float sum_exact;
@@ -1051,6 +1062,10 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
   p.seqused_k = a->seqused_k;
   p.softmax_scale = a->softmax_scale;
   p.status = status;
+  p.redo = static_cast<int*>(a->workspace);
+  if (a->workspace && (a->workspace_bytes < attn_fwd_flag_bytes(a->B, a->Hq, a->Nq) ||
+                       (reinterpret_cast<uintptr_t>(a->workspace) & 3)))
+    return WK_E_ARG;
 
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<false>), SMEM_BYTES)) return WK_E_CUDA;
   if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_wide_kernel), M_SMEM_BYTES)) return WK_E_CUDA;
@@ -1112,7 +1127,9 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
     }
     if (e != cudaSuccess) return WK_E_CUDA;
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
+  if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+  // blocks the kernels above flagged as beyond their exponent range are computed again (normally none)
+  return p.redo ? launch_attn_fwd_redo(a, false, p.redo, st) : 0;
 }
 
 
