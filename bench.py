@@ -607,6 +607,9 @@ def measure(name, args, dev, dist, world, rank, clocks):
     e2e_ms = timed(w["e2e_step"], max(3, args.steps // 4), 2, flush=False)
     _lib.device_status()
 
+    if args.per_rank:
+        print(f"[rank {rank}] {name}: burst {kernel_ms:.4f} ms, sustained {sustained_ms:.4f} ms, e2e {e2e_ms:.4f} ms, "
+              f"with gather {gather_ms}", file=sys.stderr, flush=True)
     t = torch.tensor([kernel_ms, sustained_ms, e2e_ms, gather_ms or 0.0], dtype=torch.float64, device=dev)
     sums = torch.tensor([float(w["h2d"]), float(w["d2h"])], dtype=torch.float64, device=dev)
     if dist is not None:
@@ -704,6 +707,7 @@ def main():
     ap.add_argument("--workload", default="all", choices=["all"] + sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sustain-s", type=float, default=1.5, dest="sustain_s")
+    ap.add_argument("--per-rank", action="store_true", help="print every rank's own times to stderr")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

@@ -270,3 +270,22 @@ def test_wide_kernel(cuda, shape, causal):
     vis = torch.isfinite(lse2)
     assert (lse[vis] - lse2[vis]).abs().max().item() <= 1e-3 and (pmax[vis] - pmax2[vis]).abs().max().item() <= 1e-3
     assert torch.equal(attn_fwd(q8, k8, v8, sq, sk, sv, causal=causal, ctas_per_sm=1)[0], out), "repeated launches differ"
+
+
+def test_launch_closure_keeps_its_outputs_alive(cuda):
+    """A caller may keep only ``launch`` and drop ``out``, ``lse`` and ``pmax``: the closure must own them, or the
+    kernel writes into memory the allocator has already handed to someone else."""
+    import gc
+
+    from warpy_kernels.attn import make_attn_fwd
+
+    q, k, v = randn_qkv(2, 4, 4, 256, 256, 128, device=cuda)
+    q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+    launch, out, lse, pmax = make_attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
+    sizes = [t.numel() * t.element_size() for t in (out, lse, pmax)]
+    del out, lse, pmax
+    gc.collect()
+    canaries = [torch.zeros(n, dtype=torch.uint8, device=cuda) for n in sizes for _ in range(4)]
+    launch()
+    torch.cuda.synchronize()
+    assert all(int(c.count_nonzero()) == 0 for c in canaries)

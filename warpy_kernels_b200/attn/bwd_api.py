@@ -154,7 +154,7 @@ def make_attn_bwd(
     args.lse_strides = (ctypes.c_int64 * 2)(*lsev.stride()[:2])
     args.B, args.Hq, args.Hkv, args.Nq, args.Nk, args.d = B, Hq, Hkv, Nq, Nk, KERNEL_D
     args.causal, args.softmax_scale = int(bool(causal)), float(softmax_scale)
-    keep = (qv, kv, vv, ov, dov, lsev, dq_, dk_, dv_, workspace)
+    keep = (qv, kv, vv, ov, dov, lsev, dq_, dk_, dv_, workspace, dq, dk, dv)  # inputs, scratch and outputs
 
     entry = lib.wk_attn_bwd_bf16 if bf16 else lib.wk_attn_bwd_fp8
 

@@ -223,7 +223,9 @@ def make_attn_fwd(
     if ctas_per_sm not in (None, 1, 2):
         raise ValueError("ctas_per_sm must be 1 or 2")
     args.ctas_per_sm = int(ctas_per_sm or 0)
-    keep = (qv, kv, vv, dq_, dk_, dv_, seq, out_k)  # the launch closure owns what the argument block points at
+    # the launch closure owns everything the argument block points at, outputs included: a caller may keep the
+    # closure and drop the tensors it was handed
+    keep = (qv, kv, vv, dq_, dk_, dv_, seq, out_k, out, lse, pmax)
     lib = _lib.lib()
     entry = lib.wk_attn_fwd_bf16 if bf16 else lib.wk_attn_fwd_fp8
     args.workspace_bytes = lib.wk_attn_fwd_workspace_bytes(B, Hq, Nq)

@@ -227,7 +227,7 @@ def make_gemm(
         args.a_trans, args.b_trans = int(bool(a_trans)), int(bool(b_trans))
         args.cta_pair = 0 if cta_pair is None else 1 if cta_pair else 2
         fill_epilogue(args)
-        keep = (a, b, scale_a, scale_b, pre_out, pre_in)
+        keep = (a, b, out, scale_a, scale_b, pre_out, pre_in, q_mx, s_mx)  # inputs and outputs stay alive
 
         def launch():
             with torch.cuda.device(dev):
@@ -247,7 +247,7 @@ def make_gemm(
         args.out_f16 = int(odt == torch.float16)
         args.cta_pair = 0 if cta_pair is None else 1 if cta_pair else 2
         fill_epilogue(args)
-        keep = (a, b, a_scale_mx, b_scale_mx, scale_a, scale_b, workspace, pre_out, pre_in)
+        keep = (a, b, out, a_scale_mx, b_scale_mx, scale_a, scale_b, workspace, pre_out, pre_in, q_mx, s_mx)
 
         def launch():
             with torch.cuda.device(dev):
