@@ -163,7 +163,8 @@ class Pipeline:
     so the H2D copy of one chunk, the kernel of another and the D2H copy of a third run at the same time.
     """
 
-    def __init__(self, dev, n_streams=3):
+    def __init__(self, dev, n_streams=None):
+        n_streams = n_streams or E2E_STREAMS
         self.dev = dev
         self.streams = [torch.cuda.Stream(dev) for _ in range(n_streams)]
 
@@ -191,6 +192,36 @@ def pinned(t):
     return t.cpu().pin_memory()
 
 
+def copy_floor_ms(dev, h2d_bytes, d2h_bytes, reps=4):
+    """What the link between host and GPU allows for the step's bytes, with no kernel at all: the host -> device
+    bytes as one big copy, the device -> host bytes as one big copy, and both at the same time on two streams.
+    Returns the three times in milliseconds (best of ``reps``)."""
+    if h2d_bytes + d2h_bytes == 0:
+        return 0.0, 0.0, 0.0
+    up_src = torch.zeros(max(h2d_bytes, 1), dtype=torch.uint8).pin_memory()
+    up_dst = torch.empty(max(h2d_bytes, 1), dtype=torch.uint8, device=dev)
+    down_src = torch.zeros(max(d2h_bytes, 1), dtype=torch.uint8, device=dev)
+    down_dst = torch.zeros(max(d2h_bytes, 1), dtype=torch.uint8).pin_memory()
+    main = torch.cuda.current_stream(dev)
+    s_up, s_down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def once(up, down):
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(main)
+        for on, stream, dst, src in ((up, s_up, up_dst, up_src), (down, s_down, down_dst, down_src)):
+            if on:
+                stream.wait_stream(main)
+                with torch.cuda.stream(stream):
+                    dst.copy_(src, non_blocking=True)
+                main.wait_stream(stream)
+        e1.record(main)
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1)
+
+    return tuple(min(once(up, down) for _ in range(reps)) for up, down in ((True, False), (False, True), (True, True)))
+
+
 def split_even(n, parts):
     parts = max(1, min(parts, n))
     base, extra = divmod(n, parts)
@@ -214,13 +245,17 @@ def quantize_per_tensor(x):
     return (x / scale).to(torch.float8_e4m3fn), scale
 
 
-def _e2e_subpieces(piece, target=4):
-    """Split one rectangular piece (b0, b1, h0, h1) into a few chunks for the copy / compute pipeline: by batch item
-    when it spans several, else by KV head."""
+E2E_CHUNKS = int(os.environ.get("WK_BENCH_E2E_CHUNKS", "8"))
+E2E_STREAMS = int(os.environ.get("WK_BENCH_E2E_STREAMS", "3"))
+
+
+def _e2e_subpieces(piece, target=None):
+    """Split one rectangular piece (b0, b1, h0, h1) into about ``target`` chunks for the copy / compute pipeline:
+    by batch item first, then by KV head inside a batch item."""
     b0, b1, h0, h1 = piece
-    if b1 - b0 > 1:
-        return [(b0 + lo, b0 + hi, h0, h1) for lo, hi in split_even(b1 - b0, target)]
-    return [(b0, b1, h0 + lo, h0 + hi) for lo, hi in split_even(h1 - h0, target)]
+    target = target or E2E_CHUNKS
+    per_item = max(1, -(-target // (b1 - b0)))
+    return [(b, b + 1, h0 + lo, h0 + hi) for b in range(b0, b1) for lo, hi in split_even(h1 - h0, per_item)]
 
 
 def make_attn(dev, world, rank, B, Hq, Hkv, N, d, causal, seed, bf16=False, backward=False):
@@ -282,10 +317,13 @@ def make_attn(dev, world, rank, B, Hq, Hkv, N, d, causal, seed, bf16=False, back
                 h2d += sum(t.numel() * t.element_size() for t in host_in)
                 d2h += host_out.numel() * 2
 
-                def chunk(host_in=host_in, dev_in=dev_in, host_out=host_out, dsc=dsc):
+                # prepared once, as a serving loop would: the launch reads the device buffers the copies fill
+                run, o, _, _ = make_attn_fwd(*(from_u8(t) for t in dev_in), *dsc, causal=causal)
+
+                def chunk(host_in=host_in, dev_in=dev_in, host_out=host_out, run=run, o=o):
                     for d_, h_ in zip(dev_in, host_in):
                         d_.copy_(h_, non_blocking=True)
-                    o, _, _ = wk.attn_fwd(*(from_u8(t) for t in dev_in), *dsc, causal=causal)
+                    run()
                     host_out.copy_(o, non_blocking=True)
             else:
                 # the forward's saved tensors stay on the device; dout arrives from the host, gradients go back
@@ -297,10 +335,11 @@ def make_attn(dev, world, rank, B, Hq, Hkv, N, d, causal, seed, bf16=False, back
                 h2d += host_do.numel() * 2
                 d2h += sum(t.numel() * 2 for t in host_g)
 
-                def chunk(qc=qc, kc=kc, vc=vc, oc=oc, lc=lc, pc=pc, host_do=host_do, dev_do=dev_do, host_g=host_g,
-                          dsc=dsc):
+                run, finish = make_attn_bwd(qc, kc, vc, oc, lc, pc, dev_do, *dsc, causal=causal)
+
+                def chunk(host_do=host_do, dev_do=dev_do, host_g=host_g, run=run, grads=finish()):
                     dev_do.copy_(host_do, non_blocking=True)
-                    grads = wk.attn_bwd(qc, kc, vc, oc, lc, pc, dev_do, *dsc, causal=causal)
+                    run()
                     for h_, g_ in zip(host_g, grads):
                         h_.copy_(g_, non_blocking=True)
             chunks.append(chunk)
@@ -329,7 +368,7 @@ def make_gemm_bf16(dev, world, rank, m, n, k, seed, cta_pair=None, sharded=True)
     pipe = Pipeline(dev)
     hb, db = pinned(b), torch.empty_like(b)
     chunks, h2d, d2h = [], hb.numel() * 2, 0
-    for r0, r1 in ((128 * x, 128 * y) for x, y in split_even((hi - lo) // 128, 4)):
+    for r0, r1 in ((128 * x, 128 * y) for x, y in split_even((hi - lo) // 128, 8)):
         ha, da = pinned(a[r0:r1]), torch.empty(r1 - r0, k, dtype=a.dtype, device=dev)
         ho = torch.empty(r1 - r0, n, dtype=torch.bfloat16).pin_memory()
         h2d, d2h = h2d + ha.numel() * 2, d2h + ho.numel() * 2
@@ -362,7 +401,7 @@ def make_gemm_mx(dev, world, rank, m, n, k, seed, cta_pair=None):
     hb, hsb = pinned(u8(b8)), pinned(sb)
     db, dsb = torch.empty_like(hb, device=dev), torch.empty_like(hsb, device=dev)
     chunks, h2d, d2h = [], hb.numel() + hsb.numel(), 0
-    for r0, r1 in ((128 * x, 128 * y) for x, y in split_even((hi - lo) // 128, 4)):
+    for r0, r1 in ((128 * x, 128 * y) for x, y in split_even((hi - lo) // 128, 8)):
         ha, hs = pinned(u8(a8[r0:r1])), pinned(sa[r0:r1])
         da, dsa = torch.empty_like(ha, device=dev), torch.empty_like(hs, device=dev)
         ho = torch.empty(r1 - r0, n, dtype=torch.bfloat16).pin_memory()
@@ -395,7 +434,7 @@ def make_quant(dev, world, rank, m, k, seed):
     s = torch.empty(rows, k // 32, dtype=torch.uint8, device=dev)
     pipe = Pipeline(dev)
     chunks, h2d, d2h = [], 0, 0
-    for r0, r1 in ((128 * a, 128 * b) for a, b in split_even(rows // 128, 4)):
+    for r0, r1 in ((128 * a, 128 * b) for a, b in split_even(rows // 128, 8)):
         hx, dx = pinned(x[r0:r1]), torch.empty(r1 - r0, k, dtype=x.dtype, device=dev)
         hq = torch.empty(r1 - r0, k, dtype=torch.uint8).pin_memory()
         hs = torch.empty(r1 - r0, k // 32, dtype=torch.uint8).pin_memory()
@@ -606,6 +645,7 @@ def measure(name, args, dev, dist, world, rank, clocks):
     # the end-to-end step brings its inputs from the host, so there is nothing to flush
     e2e_ms = timed(w["e2e_step"], max(3, args.steps // 4), 2, flush=False)
     _lib.device_status()
+    up_ms, down_ms, floor_ms = copy_floor_ms(dev, w["h2d"], w["d2h"])
 
     if args.per_rank:
         print(f"[rank {rank}] {name}: burst {kernel_ms:.4f} ms, sustained {sustained_ms:.4f} ms, e2e {e2e_ms:.4f} ms, "
@@ -645,7 +685,9 @@ def measure(name, args, dev, dist, world, rank, clocks):
                       "ms_x_mhz": sustained_ms * clk["sm_mhz"] if clk and clk["sm_mhz"] else None,
                       "l2": "back-to-back launches, no flush" if flush_buf is not None else "larger than L2"},
         "e2e": {"value": rate(e2e_ms), "unit": wl["unit"], "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "chunks_per_rank": w["e2e_chunks"], "streams": 3},
+                "d2h_bytes_per_step": d2h, "chunks_per_rank": w["e2e_chunks"], "streams": E2E_STREAMS,
+                "copies_alone_ms": {"h2d": up_ms, "d2h": down_ms, "both_at_once": floor_ms},
+                "note": "copies_alone_ms: rank 0's bytes as one big copy per direction, no kernel: what the link allows"},
         "gpu_launches": w["launches"] * args.steps,
         "clocks": clk,
     }

@@ -496,3 +496,25 @@ def test_fp8_block_scaled_mma_accumulator(cuda, kind, cta_pair):
     if kind == "cancel":
         left = gemm(a, b, a_scale_mx=sa, b_scale_mx=sb, cta_pair=cta_pair)
         assert (left.double().abs() / unit_s).max().item() <= k / 32
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8"])
+def test_autotune_gemm_times_both_kernels_and_stores_the_winner(cuda, kind, tmp_path, monkeypatch):
+    """``autotune_gemm`` times the single-CTA and the CTA-pair kernel, writes the winner into the tune cache and
+    ``make_gemm`` picks it up (the reference's tuner: ``warpy_kernels/gemm/api.py:363-390``)."""
+    import json
+
+    from warpy_kernels import autotune_gemm, gemm
+    from warpy_kernels_b200 import utils
+
+    monkeypatch.setattr(utils, "TUNE_CACHE_PATH", str(tmp_path / "tune.json"))
+    m, n, k = 512, 768, 512
+    g = torch.Generator(device=cuda).manual_seed(0)
+    a, b = torch.randn(m, k, device=cuda, generator=g), torch.randn(n, k, device=cuda, generator=g)
+    a, b = (a.to(FP8), b.to(FP8)) if kind == "fp8" else (a.bfloat16(), b.bfloat16())
+    best, results = autotune_gemm(a, b, iters=3, verbose=False)
+    assert best in ({"cta_pair": False}, {"cta_pair": True}) and len(results) == 2
+    assert all(isinstance(t, float) for _, t in results)
+    key = f"{'gemm_fp8' if kind == 'fp8' else 'gemm'}|m={m}|n={n}|k={k}|sm100"
+    assert json.load(open(tmp_path / "tune.json")) == {key: best}
+    assert torch.equal(gemm(a, b), gemm(a, b, cta_pair=best["cta_pair"]))  # the cache entry is what runs by default

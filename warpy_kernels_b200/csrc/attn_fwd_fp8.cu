@@ -51,6 +51,31 @@
 namespace wk {
 namespace {
 
+// Cycle probe of the persistent kernel (compile with -DWK_FWD_PROBE; never part of the shipped library): lane 0 of a
+// warp adds the cycles it spent between two marks to a global counter.
+#ifdef WK_FWD_PROBE
+__device__ unsigned long long g_fwd_probe[32];
+// per-warp accumulators in shared memory (lane 0 only), flushed to the global counters once at the end
+#define PROBE_SMEM __shared__ unsigned long long probe_acc[20][20]
+#define PROBE_DECL long long probe_t = clock64()
+#define PROBE(slot)                                                                        \
+  do {                                                                                     \
+    const long long probe_now = clock64();                                                 \
+    if ((threadIdx.x & 31) == 0) probe_acc[threadIdx.x >> 5][slot] += probe_now - probe_t; \
+    probe_t = probe_now;                                                                   \
+  } while (0)
+#define PROBE_COUNT(slot) do { if ((threadIdx.x & 31) == 0) probe_acc[threadIdx.x >> 5][slot] += 1; } while (0)
+#define PROBE_INIT do { if ((threadIdx.x & 31) == 0) for (int i = 0; i < 20; ++i) probe_acc[threadIdx.x >> 5][i] = 0; } while (0)
+#define PROBE_FLUSH do { if ((threadIdx.x & 31) == 0) for (int i = 0; i < 20; ++i) if (probe_acc[threadIdx.x >> 5][i]) atomicAdd(&g_fwd_probe[i], probe_acc[threadIdx.x >> 5][i]); } while (0)
+#else
+#define PROBE_SMEM
+#define PROBE_DECL
+#define PROBE(slot)
+#define PROBE_COUNT(slot)
+#define PROBE_INIT
+#define PROBE_FLUSH
+#endif
+
 constexpr int BM = 128;       // queries per CTA
 constexpr int BN = 64;        // keys per tile
 constexpr int D = 128;        // head dimension (bytes per row in e4m3)
@@ -606,6 +631,8 @@ __global__ void __launch_bounds__(M_THREADS, 1)
 attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
+  PROBE_SMEM;
+  PROBE_INIT;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = smem_base;  // two buffers
   const uint32_t k_smem = q_smem + 2 * Q_BYTES;
@@ -615,15 +642,17 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   const uint32_t bar_base = fin_smem + M_FIN_BYTES;
   auto q_full = [&](int i) { return bar_base + 8u * i; };
   auto q_empty = [&](int i) { return bar_base + 8u * (2 + i); };
-  auto k_full = [&](int s) { return bar_base + 8u * (4 + s); };
-  auto k_empty = [&](int s) { return bar_base + 8u * (4 + KV_STAGES + s); };
-  auto v_full = [&](int s) { return bar_base + 8u * (4 + 2 * KV_STAGES + s); };
-  auto v_empty = [&](int s) { return bar_base + 8u * (4 + 3 * KV_STAGES + s); };
+  // A thread that issues MMAs pays 100-150 cycles for every barrier operation while shared memory is busy, so a
+  // round of 128 keys costs each of the two issuing threads as few of them as possible: K and V of a stage arrive
+  // on one barrier, both groups of an S buffer announce their P on one barrier, and one commit per round
+  // (round_done) tells the producer that the stage's K and V may be overwritten and the two groups that their P
+  // regions may be.
+  auto kv_full = [&](int s) { return bar_base + 8u * (4 + s); };                   // K and V of stage s have landed
+  auto round_done = [&](int s) { return bar_base + 8u * (4 + KV_STAGES + s); };    // the round's P.V has completed
   const uint32_t misc_bar = bar_base + 8u * (4 + 4 * KV_STAGES);
   auto s_full = [&](int buf) { return misc_bar + 8u * buf; };        // S buffer `buf` holds a round's scores
   auto s_free = [&](int buf) { return misc_bar + 8u * (2 + buf); };  // both of its groups have read them
-  auto p_full = [&](int g) { return misc_bar + 8u * (4 + g); };      // group g has written P
-  auto p_empty = [&](int g) { return misc_bar + 8u * (8 + g); };     // the P.V product has read group g's P
+  auto p_full = [&](int buf) { return misc_bar + 8u * (4 + buf); };  // both groups of buffer `buf` have written P
   const uint32_t o_full = misc_bar + 8u * 12;    // the block's last P.V product has completed
   const uint32_t o_free = misc_bar + 8u * 13;    // every softmax thread has read its part of O
   const uint32_t ref_full = misc_bar + 8u * 14;  // the block's row references are published
@@ -646,18 +675,13 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       mbar_init(sched_empty(i), M_CONSUMERS);
     }
     for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(k_full(s), 1);
-      mbar_init(k_empty(s), 1);
-      mbar_init(v_full(s), 1);
-      mbar_init(v_empty(s), 1);
+      mbar_init(kv_full(s), 1);
+      mbar_init(round_done(s), 1);
     }
     for (int buf = 0; buf < 2; ++buf) {
       mbar_init(s_full(buf), 1);
       mbar_init(s_free(buf), 2 * GROUP_THREADS);
-    }
-    for (int g = 0; g < M_GROUPS; ++g) {
-      mbar_init(p_full(g), GROUP_THREADS);
-      mbar_init(p_empty(g), 1);
+      mbar_init(p_full(buf), 2 * GROUP_THREADS);
     }
     mbar_init(o_full, 1);
     mbar_init(o_free, M_SOFTMAX_THREADS);
@@ -713,18 +737,14 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         for (int R = 0; R < it.n_rounds; ++R, ++gr) {
           const int s = gr % KV_STAGES;
           const uint32_t ph = (gr / KV_STAGES) & 1;
-          if (!mbar_wait(k_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) {
+          // the stage is free when the P.V product of the round that used it last has completed
+          if (!mbar_wait(round_done(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(k_full(s), M_KV_BYTES);
-          tma_load_4d(k_smem + s * M_KV_BYTES, &tmap_k, k_full(s), 0, R * M_BN, it.hkv, it.b);
-          if (!mbar_wait(v_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) {
-            ok = false;
-            break;
-          }
-          mbar_expect_tx(v_full(s), M_KV_BYTES);
-          tma_load_4d(v_smem + s * M_KV_BYTES, &tmap_v, v_full(s), 0, R * M_BN, it.hkv, it.b);
+          mbar_expect_tx(kv_full(s), 2 * M_KV_BYTES);
+          tma_load_4d(k_smem + s * M_KV_BYTES, &tmap_k, kv_full(s), 0, R * M_BN, it.hkv, it.b);
+          tma_load_4d(v_smem + s * M_KV_BYTES, &tmap_v, kv_full(s), 0, R * M_BN, it.hkv, it.b);
         }
         }
         if (!ok) break;
@@ -745,32 +765,34 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       constexpr uint32_t idesc_qk = make_idesc(0, 0, 0, 0, BM, M_BN);
       int ci = -1;
       uint32_t gr = 0;
+      PROBE_DECL;
       for (;;) {
         if (valid) {
         ++ci;
         const int qb = ci & 1;
         const uint64_t q_desc = smem_desc_sw128(q_smem + qb * Q_BYTES, 16, 1024);
+        PROBE(16);
         if (!mbar_wait(q_full(qb), (ci >> 1) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        PROBE(17);
         for (int R = 0; R < it.n_rounds; ++R, ++gr) {
           const int s = gr % KV_STAGES;
           const uint32_t ph = (gr / KV_STAGES) & 1;
           const int buf = gr & 1;
           // the buffer is free when both groups have the scores of the round before the previous one in registers
+          PROBE(16);
           if (gr >= 2 && !mbar_wait(s_free(buf), ((gr >> 1) - 1) & 1, p.status, WK_ERR_TIMEOUT_P)) {
             ok = false;
             break;
           }
-          if (!mbar_wait(k_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) {
-            ok = false;
-            break;
-          }
-          // Also the round's V tile, on behalf of warp 2: this thread has time to spare, that one is the busiest of
-          // the kernel, and what it does with V comes after this S, the softmax and the hand-over of P.
-          if (!mbar_wait(v_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) {
+          PROBE(14);
+          // K of the round, and its V on behalf of warp 2 (what that one does with V comes after this S, the
+          // softmax and the hand-over of P)
+          if (!mbar_wait(kv_full(s), ph, p.status, WK_ERR_TIMEOUT_LOAD)) {
             ok = false;
             break;
           }
           tc_fence_after();
+          PROBE(15);
           const uint64_t k_desc = smem_desc_sw128(k_smem + s * M_KV_BYTES, 16, 1024);
           const uint32_t s_tmem = tmem_base + 128 * buf;
 #pragma unroll
@@ -778,7 +800,6 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             // 32 e4m3 = 32 bytes along the head dimension inside the 128-byte swizzle span
             mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k != 0);
           }
-          tc_commit(k_empty(s));
           tc_commit(s_full(buf));
         }
         if (ok) tc_commit(q_empty(qb));
@@ -793,36 +814,40 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       const uint32_t o_tmem = tmem_base + M_O_COL;
       int ci = -1;
       uint32_t gr = 0;
+      PROBE_DECL;
       for (;;) {
         if (valid) {
         ++ci;
+        PROBE(11);
         // the softmax threads have read the previous block's O
         if (ci >= 1 && !mbar_wait(o_free, (ci - 1) & 1, p.status, WK_ERR_TIMEOUT_TMEM)) break;
         tc_fence_after();
+        PROBE(12);
         for (int R = 0; ok && R < it.n_rounds; ++R, ++gr) {
           const int s = gr % KV_STAGES;
-          const uint32_t it_par = (gr >> 1) & 1;
+          const int buf = gr & 1;
+          PROBE(11);
           // V tile: 128 keys (the MMA's K) x 128 bytes of head dim (the MMA's N): MN-major,
           // one 128-byte span wide, 8-key groups 1024 bytes apart, 32 keys per MMA = 4096 bytes
           const uint64_t v_desc = smem_desc_sw128(v_smem + s * M_KV_BYTES, 16, 1024);
-#pragma unroll 1
+          if (!mbar_wait(p_full(buf), (gr >> 1) & 1, p.status, WK_ERR_TIMEOUT_P)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          PROBE(10);
+          PROBE_COUNT(13);
+#pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const int g = 2 * (gr & 1) + h;
-            const uint32_t p_tmem = tmem_base + M_P_COL + M_P_STRIDE * g;
-            if (!mbar_wait(p_full(g), it_par, p.status, WK_ERR_TIMEOUT_P)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after();
+            const uint32_t p_tmem = tmem_base + M_P_COL + M_P_STRIDE * (2 * buf + h);
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
               // P: 32 e4m3 per K step = 8 TMEM columns; scale byte k of the row's scale word
               mma_mxf8_ts(o_tmem, p_tmem + 8 * k, v_desc + 256 * (2 * h + k), make_idesc_mx_major(BM, D, k, 0, 0, 1),
                           p_tmem + M_SFA_OFF, tmem_base + M_SFB_COL, (R | h | k) != 0);
             }
-            tc_commit(p_empty(g));
-            if (h == 1) tc_commit(v_empty(s));
           }
+          tc_commit(round_done(s));
         }
         if (ok) tc_commit(o_full);
         }
@@ -844,6 +869,21 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     int ci = -1;
     uint32_t gr0 = 0;  // rounds of the blocks before this one
     bool unit_scales_set = false;
+    // A barrier operation costs 100-300 cycles of latency while shared memory feeds the MMAs, and a thread's tile has
+    // four of them.  Two are taken off its critical path: whether the next S and the P region are ready is asked
+    // early (test_wait, answer used later), and the hand-over of a tile's P (wait for the TMEM stores, arrive) is
+    // put off until the loads of the next tile's scores are on their way.
+    bool s_ready = false;   // the scores of this group's next tile were already there when last asked
+    bool handing_over = false;  // P of the last tile is stored but not yet announced
+    auto hand_over = [&]() {
+      if (handing_over) {
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(p_full(buf));
+        handing_over = false;
+      }
+    };
+    PROBE_DECL;
 
     // The output of a block is stored by the groups while they are already at work on the next block: its last P.V
     // products are still running when a group has finished its last tile, so the group first does its first tile of
@@ -873,18 +913,26 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       for (uint32_t gr = gr0 + ((buf ^ gr0) & 1); gr < gr0 + it.n_rounds; gr += 2) {
         const uint32_t n = gr >> 1;  // this group's tiles so far
         const int j = 2 * static_cast<int>(gr - gr0) + half;  // the 64-key tile
-        if (!mbar_wait_warp(s_full(buf), n & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+        PROBE(7);
+        if (!__all_sync(0xffffffffu, s_ready) &&
+            !mbar_wait_warp(s_full(buf), n & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
           ok = false;
           break;
         }
         tc_fence_after();
+        PROBE(1);
         // the whole row of the tile into registers, then the S buffer goes back to the MMA thread
         uint32_t sraw[2][32];
         tmem_ld32(s_tmem, sraw[0]);
         tmem_ld32(s_tmem + 32, sraw[1]);
+        hand_over();  // the previous tile's P, while the loads are in flight
         tc_wait_ld();
         tc_fence_before();
         mbar_arrive(s_free(buf));
+        // is this group's P region free (the P.V product of its previous tile completed)?  Needed after the
+        // exponentials; asked now so that the answer is there by then.
+        const bool p_free = n == 0 || mbar_test_wait(round_done((gr - 2) % KV_STAGES), ((gr - 2) / KV_STAGES) & 1);
+        PROBE(2);
 
         const int key0 = j * BN;
         const bool tile_masked = (key0 + BN > it.nk) || (p.causal && key0 + BN - 1 > it.m0 + it.shift);
@@ -899,6 +947,7 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         float cm[2];
         cm[0] = block_max(sraw[0]) * beta;  // beta > 0 (checked on the host)
         cm[1] = block_max(sraw[1]) * beta;
+        PROBE(3);
         if (j == 0) {
           // the row reference: maximum of the first tile (every row that sees any key sees one here)
           m_ref = fmaxf(cm[0], cm[1]);
@@ -914,16 +963,11 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           asm volatile("ld.shared.f32 %0, [%1];" : "=f"(m_ref) : "r"(x_ref) : "memory");
           have_ref = true;
         }
-        if (n >= 1) {
-          // this group's P region is free once the P.V product of its previous tile has completed
-          if (!mbar_wait_warp(p_empty(grp), (n - 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-        }
-
+        PROBE(4);
+        // The codes of both 32-key blocks are computed into registers first; the group's P region is only needed
+        // when they are stored, and by then the P.V product of the previous tile has long completed.
         uint32_t sf_word = 0;
+        uint32_t w[2][8];
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           m_true = fmaxf(m_true, cm[c]);
@@ -933,37 +977,52 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           // wide_store_output reports the row (m_true - m_ref tells)
           kf = fminf(kf, MAX_BLOCK_EXP);
           const float bias = live ? (static_cast<float>(P_OFFSET) - kf) - m_ref : 0.f;
-          uint32_t w[8], wl[8];
+          uint32_t wl[8];
           float sum_exact;
-          softmax_block<false>(sraw[c], beta, bias, w, wl, sum_exact);
-          tmem_st8(p_tmem + c * 8, w);
+          softmax_block<false>(sraw[c], beta, bias, w[c], wl, sum_exact);
           int sf = live ? 127 + static_cast<int>(kf) - P_OFFSET : 0;
           sf = min(max(sf, 0), 254);
           const float blk_scale = __uint_as_float(static_cast<uint32_t>(sf) << 23);
           if (live) l = fmaf(sum_exact, blk_scale, l);
           sf_word |= static_cast<uint32_t>(sf) << (8 * c);
         }
+        PROBE(5);
+        if (!__all_sync(0xffffffffu, p_free)) {
+          if (!mbar_wait_warp(round_done((gr - 2) % KV_STAGES), ((gr - 2) / KV_STAGES) & 1, p.status,
+                              WK_ERR_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+        }
+        tc_fence_after();
+        PROBE(6);
+        PROBE_COUNT(9);
+        tmem_st8(p_tmem, w[0]);
+        tmem_st8(p_tmem + 8, w[1]);
         // scale factors straight into TMEM: the MMA reads the scale of row r from lane r, column r / 32
         tmem_st1(p_tmem + M_SFA_OFF + quad, sf_word);
         if (!unit_scales_set) {
           tmem_st4(tmem_base + lane_addr + M_SFB_COL, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
           unit_scales_set = true;
         }
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(p_full(grp));
+        handing_over = true;
+        hand_over();
+        s_ready = mbar_test_wait(s_full(buf), (n + 1) & 1);  // this group's next tile, in this block or the next
         if (pending) {
           // first tile after a finished block: its P is handed over (the P.V product waits for O to be read
           // anyway), now that block's output
           pending = false;
+          PROBE(7);
           if (!store_output(ci - 1)) {
             ok = false;
             break;
           }
+          PROBE(8);
         }
       }
       gr0 += it.n_rounds;
       if (!ok) break;
+      hand_over();  // the block's last tile
 
       // the groups' sums; each group stores head-dim columns [32 g, 32 g + 32) of the output later (store_output)
       asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch + (1 + 2 * grp) * BM * 4 + r * 4), "f"(l) : "memory");
@@ -978,6 +1037,7 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     if (ok && pending) store_output(ci);
   }
 
+  PROBE_FLUSH;
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -989,6 +1049,18 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 
 }  // namespace
 }  // namespace wk
+
+#ifdef WK_FWD_PROBE
+extern "C" int wk_fwd_probe_read(unsigned long long* out, int clear) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return -2;
+  if (cudaMemcpyFromSymbol(out, wk::g_fwd_probe, 32 * sizeof(unsigned long long)) != cudaSuccess) return -2;
+  if (clear) {
+    unsigned long long zero[32] = {};
+    if (cudaMemcpyToSymbol(wk::g_fwd_probe, zero, sizeof(zero)) != cudaSuccess) return -2;
+  }
+  return 0;
+}
+#endif
 
 extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
   using namespace wk;

@@ -13,7 +13,7 @@ import torch
 
 from .. import _lib
 from ..arch import require
-from ..utils import time_candidates
+from ..utils import gemm_tune_key, time_candidates, tune_lookup, tune_store
 
 _TYPES = {torch.bfloat16: "bf16", torch.float16: "f16"}
 BM = 128
@@ -204,6 +204,9 @@ def make_gemm(
         scale_b = scale_b if col_scale else None
     if col_scale and scale_b.data_ptr() % 16:
         scale_b = scale_b.clone()  # the kernel reads column scales as 16-byte vectors
+    if cta_pair is None:
+        # the kernel autotune_gemm found fastest for this shape, if it was run; else the library's own choice
+        cta_pair = (tune_lookup(gemm_tune_key("gemm_fp8" if fp8 else "gemm", m, n, k)) or {}).get("cta_pair")
     _check_mx("a_scale_mx", a_scale_mx, m, k, fp8)
     _check_mx("b_scale_mx", b_scale_mx, n, k, fp8)
     q_mx = torch.empty(m, n, dtype=torch.float8_e4m3fn, device=a.device) if out_mx else None
@@ -271,15 +274,41 @@ def gemm(a, b, out=None, **kwargs):
     return (out, *rest) if kwargs.get("act") == "gelu" or kwargs.get("out_mx") else out
 
 
-def autotune_gemm(a, b, candidates=None, iters=20, verbose=True, **kwargs):
-    """Time candidate configs for these shapes.
+def candidates_for(fp8):
+    """The kernel variants ``autotune_gemm`` times: single CTAs (128 x 256 tiles) and CTA pairs (``tcgen05``
+    ``cta_group::2``, 256 x 256 tiles over two SMs), for 16-bit and for fp8 inputs alike.  The counterpart of the
+    reference's ``candidates_for`` (``warpy_kernels/gemm/configs.py``), whose knobs tune its SM80-SM120 kernels."""
+    del fp8  # the same two kernels exist for both input types
+    return [{"cta_pair": False}, {"cta_pair": True}]
 
-    The sm_100a kernels have a single tiling, so the default candidate list has one entry; the function exists so
-    that callers of the reference's ``autotune_gemm`` keep working.
+
+def autotune_gemm(a, b, candidates=None, iters=20, verbose=True, **kwargs):
+    """Time candidate configs for these shapes and remember the fastest.
+
+    ``make_gemm`` and ``gemm`` look the winner up (tune cache, keyed by input type and ``M, N, K``) whenever
+    ``cta_pair`` is not given; without an entry the library chooses by a size rule.
+
+    Args:
+        a: As in ``make_gemm``.
+        b: As in ``make_gemm``.
+        candidates: Config dicts with keyword arguments of ``make_gemm``. Defaults to ``candidates_for`` the input type.
+        iters: Timed launches per candidate.
+        verbose: Whether to print one line per candidate.
+        **kwargs: Extra keyword arguments for ``make_gemm``, such as ``scale_a``.
 
     Returns:
         ``(best_config, results)``, where ``results`` is a list of ``(config, milliseconds or error string)``.
+
+    Raises:
+        RuntimeError: If no candidate runs.
+        NotImplementedError: If the GPU does not support the dtype of ``a``.
     """
     require("gemm", a)
-    candidates = candidates or [{}]
-    return time_candidates(candidates, lambda cfg: make_gemm(a, b, **cfg, **kwargs)[0], iters, verbose, "gemm")
+    fp8 = a.dtype == torch.float8_e4m3fn
+    best, results = time_candidates(
+        candidates or candidates_for(fp8), lambda cfg: make_gemm(a, b, **cfg, **kwargs)[0], iters, verbose, "gemm"
+    )
+    m, k = a.shape[::-1] if kwargs.get("a_trans") else a.shape
+    n = b.shape[1] if kwargs.get("b_trans") else b.shape[0]
+    tune_store(gemm_tune_key("gemm_fp8" if fp8 else "gemm", m, n, k), best)
+    return best, results
