@@ -131,3 +131,24 @@ def test_without_workspace_the_status_word_reports_the_range(cuda):
     # a workspace that is too small is rejected before anything is launched
     a.workspace_bytes = 0
     assert lib.wk_attn_fwd_fp8(ctypes.byref(a), _lib.stream_ptr(cuda)) == -1
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_head_dim_64_late_peaks_match_oracle(cuda, bf16):
+    """Head dimension 64 takes the same path: flagged blocks are recomputed with half the head-dim lanes idle."""
+    from warpy_kernels import attn_fwd
+
+    q, k, v = late_peak_qkv(1, 4, 2, 300, 700, 64, [(200, 100.0), (650, 300.0)], seed=3, device=cuda)
+    if bf16:
+        qx, kx, vx = q.bfloat16(), k.bfloat16(), v.bfloat16()
+        out, lse, _ = attn_fwd(qx, kx, vx, causal=True)
+        out_ref, lse_ref = R.attention_reference(qx.float().cpu(), kx.float().cpu(), vx.float().cpu(), True)
+        errs = fwd_errors(out, lse, out_ref, lse_ref, 300, 700, True)
+        assert errs["out"] <= 1e-2 and errs["lse"] <= 1e-2, errs
+    else:
+        q8, k8, v8, sq, sk, sv = R.quantize_qkv(q, k, v)
+        out, lse, _ = attn_fwd(q8, k8, v8, sq, sk, sv, causal=True)
+        qd, kd, vd = R.dequantize_qkv(q8.cpu(), k8.cpu(), v8.cpu(), sq.cpu(), sk.cpu(), sv.cpu())
+        out_ref, lse_ref = R.attention_reference(qd, kd, vd, True)
+        gates(fwd_errors(out, lse, out_ref, lse_ref, 300, 700, True))
+    assert out.shape == q.shape

@@ -118,8 +118,7 @@ def make_attn_fwd(
     ``launch()`` may not see later in-place changes to the inputs. Call ``make_attn_fwd`` again for new values.
 
     Args:
-        q: ``[B, Hq, Nq, d]`` ``torch.float8_e4m3fn`` or bf16, ``d`` 64 or 128 (64 runs through the 128 kernels on
-            zero-padded copies). Any strides work if the last one is 1, such as a
+        q: ``[B, Hq, Nq, d]`` ``torch.float8_e4m3fn`` or bf16, ``d`` 64 or 128. Any strides work if the last one is 1, such as a
             transposed ``[B, N, H, d]`` tensor. Inputs are copied if a stride or the base address is not a multiple
             of 16 bytes.
         k: ``[B, Hkv, Nk, d]``, same dtype and stride rules. ``Hq`` must be a multiple of ``Hkv``.
@@ -173,7 +172,7 @@ def make_attn_fwd(
         ones = cached_tensor(("ones", dev, B, Hkv), lambda: torch.ones(B, Hkv, dtype=torch.float32, device=dev))
         dq_, dk_, dv_ = [(x if x is not None else ones).float().contiguous() for x in (q_descale, k_descale, v_descale)]
 
-    qv, kv, vv = (_pad_head_dim(x) for x in (q, k, v)) if d != KERNEL_D else (_kernel_view(x) for x in (q, k, v))
+    qv, kv, vv = (_kernel_view(x) for x in (q, k, v))  # head dimension 64 and 128 both run natively
     if out is None:
         out = torch.empty_like(q, dtype=torch.bfloat16)
     elif (
@@ -186,10 +185,8 @@ def make_attn_fwd(
     ):
         raise ValueError("out must be a bf16 tensor shaped like q, with last stride 1 and even other strides")
     # the kernel stores 16-byte vectors; an output it cannot address that way is filled through a staging copy
-    out_direct = (
-        d == KERNEL_D and out.stride(3) == 1 and out.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in out.stride()[:3])
-    )
-    out_k = out if out_direct else torch.empty(B, Hq, Nq, KERNEL_D, dtype=torch.bfloat16, device=dev)
+    out_direct = out.stride(3) == 1 and out.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in out.stride()[:3])
+    out_k = out if out_direct else torch.empty(B, Hq, Nq, d, dtype=torch.bfloat16, device=dev)
     if seqused_k is not None and (
         seqused_k.shape != (B,) or seqused_k.dtype != torch.int32 or seqused_k.device != dev
     ):
@@ -213,7 +210,7 @@ def make_attn_fwd(
     args.v_strides = (ctypes.c_int64 * 3)(*vv.stride()[:3])
     args.out_strides = (ctypes.c_int64 * 3)(*out_k.stride()[:3])
     args.lse_strides = (ctypes.c_int64 * 2)(Hq * nq_pad, nq_pad)
-    args.B, args.Hq, args.Hkv, args.Nq, args.Nk, args.d = B, Hq, Hkv, Nq, Nk, KERNEL_D
+    args.B, args.Hq, args.Hkv, args.Nq, args.Nk, args.d = B, Hq, Hkv, Nq, Nk, d
     args.causal, args.write_lse, args.lse_natural = int(bool(causal)), int(bool(return_lse)), int(bool(lse_natural))
     args.seqused_k = seq.data_ptr() if seq is not None else None
     args.softmax_scale = float(softmax_scale)
@@ -236,7 +233,7 @@ def make_attn_fwd(
             code = entry(ctypes.byref(args), _lib.stream_ptr(dev))
         _lib.check(code, "attn_fwd")
         if not out_direct:
-            out.copy_(out_k[..., :d])
+            out.copy_(out_k)
         return keep
 
     if return_lse:

@@ -32,7 +32,8 @@ namespace {
 
 constexpr int BM = 128;       // queries per CTA
 constexpr int BN = 64;        // keys per tile
-constexpr int D = 128;        // head dimension
+constexpr int D = 128;        // largest head dimension; the kernel is instantiated for DH = 128 and 64 (one 128-byte
+                              // span per row instead of two: the second box of every tile is simply not loaded)
 constexpr int CHUNK = 64;     // head-dim elements per 128-byte swizzle span
 constexpr int KV_STAGES = 2;
 constexpr int Q_CHUNK_BYTES = BM * CHUNK * 2;   // 16 KiB: 128 rows x 128 bytes
@@ -111,6 +112,7 @@ __device__ __forceinline__ float block_max(const uint32_t (&s)[32]) {
   return fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
 }
 
+template <int DH>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_fwd_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FwdParams p) {
@@ -180,27 +182,27 @@ attn_fwd_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(q_full, Q_BYTES);
+      mbar_expect_tx(q_full, (DH / CHUNK) * Q_CHUNK_BYTES);
       tma_load_4d(q_smem, &tmap_q, q_full, 0, m0, hq, b);
-      tma_load_4d(q_smem + Q_CHUNK_BYTES, &tmap_q, q_full, CHUNK, m0, hq, b);
+      if (DH > CHUNK) tma_load_4d(q_smem + Q_CHUNK_BYTES, &tmap_q, q_full, CHUNK, m0, hq, b);
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
         if (!mbar_wait(k_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
-        mbar_expect_tx(k_full(s), KV_BYTES);
+        mbar_expect_tx(k_full(s), (DH / CHUNK) * KV_CHUNK_BYTES);
         tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, k_full(s), 0, j * BN, hkv, b);
-        tma_load_4d(k_smem + s * KV_BYTES + KV_CHUNK_BYTES, &tmap_k, k_full(s), CHUNK, j * BN, hkv, b);
+        if (DH > CHUNK) tma_load_4d(k_smem + s * KV_BYTES + KV_CHUNK_BYTES, &tmap_k, k_full(s), CHUNK, j * BN, hkv, b);
         if (!mbar_wait(v_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
-        mbar_expect_tx(v_full(s), KV_BYTES);
+        mbar_expect_tx(v_full(s), (DH / CHUNK) * KV_CHUNK_BYTES);
         tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, v_full(s), 0, j * BN, hkv, b);
-        tma_load_4d(v_smem + s * KV_BYTES + KV_CHUNK_BYTES, &tmap_v, v_full(s), CHUNK, j * BN, hkv, b);
+        if (DH > CHUNK) tma_load_4d(v_smem + s * KV_BYTES + KV_CHUNK_BYTES, &tmap_v, v_full(s), CHUNK, j * BN, hkv, b);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_qk = make_idesc(1, 1, 0, 0, BM, BN);
-      constexpr uint32_t idesc_pv = make_idesc(1, 1, 0, 1, BM, D);  // B = V read MN-major
+      constexpr uint32_t idesc_pv = make_idesc(1, 1, 0, 1, BM, DH);  // B = V read MN-major
       const uint32_t o_tmem = tmem_base + O_COL;
       const uint64_t q_desc = smem_desc_sw128(q_smem, 16, 1024);
       bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
@@ -213,7 +215,7 @@ attn_fwd_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const uint64_t k_desc = smem_desc_sw128(k_smem + s * KV_BYTES, 16, 1024);
         const uint32_t s_tmem = tmem_base + (j & 1) * S_COLS;
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
+        for (int k = 0; k < DH / 16; ++k) {
           // 16 bf16 = 32 bytes along the head dimension inside a 128-byte swizzle span; the second span of
           // a tile starts one chunk further on
           mma_f16_ss(s_tmem, q_desc + (k >> 2) * (Q_CHUNK_BYTES >> 4) + 2 * (k & 3),
@@ -365,11 +367,11 @@ attn_fwd_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tc_fence_after();
       const bool empty = !(l > 0.f);
       const float inv = empty ? 0.f : 1.f / l;
-      const int col0 = 64 * grp;
+      const int col0 = (DH / 2) * grp;
       __nv_bfloat16* out_row = p.out + b * p.out_stride_b + hq * p.out_stride_h +
                                static_cast<int64_t>(row) * p.out_stride_n + col0;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < DH / 64; ++c) {
         uint32_t v[32];
         if (n_tiles > 0) {
           tmem_ld32(o_tmem + col0 + c * 32, v);
@@ -414,7 +416,7 @@ attn_fwd_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 extern "C" int wk_attn_fwd_bf16(const wk_attn_fwd_args* a, void* stream) {
   using namespace wk;
   if (!a) return WK_E_ARG;
-  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Nq <= 0 || a->Nk <= 0 || a->d != D) return WK_E_ARG;
+  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Nq <= 0 || a->Nk <= 0 || (a->d != 128 && a->d != 64)) return WK_E_ARG;
   if (a->Hq % a->Hkv) return WK_E_ARG;
   if (!a->q || !a->k || !a->v || !a->out) return WK_E_ARG;
   if (a->q_descale || a->k_descale || a->v_descale) return WK_E_ARG;  // descales belong to the fp8 kernels
@@ -437,7 +439,7 @@ extern "C" int wk_attn_fwd_bf16(const wk_attn_fwd_args* a, void* stream) {
   const uint32_t box[4] = {CHUNK, BM, 1, 1};
   const uint32_t box_kv[4] = {CHUNK, BN, 1, 1};
   {
-    const uint64_t dims[4] = {D, static_cast<uint64_t>(a->Nq), static_cast<uint64_t>(a->Hq),
+    const uint64_t dims[4] = {static_cast<uint64_t>(a->d), static_cast<uint64_t>(a->Nq), static_cast<uint64_t>(a->Hq),
                               static_cast<uint64_t>(a->B)};
     const uint64_t str[3] = {static_cast<uint64_t>(qs[2]) * 2, static_cast<uint64_t>(qs[1]) * 2,
                              static_cast<uint64_t>(qs[0]) * 2};
@@ -445,7 +447,7 @@ extern "C" int wk_attn_fwd_bf16(const wk_attn_fwd_args* a, void* stream) {
     if (r) return r;
   }
   {
-    const uint64_t dims[4] = {D, static_cast<uint64_t>(a->Nk), static_cast<uint64_t>(a->Hkv),
+    const uint64_t dims[4] = {static_cast<uint64_t>(a->d), static_cast<uint64_t>(a->Nk), static_cast<uint64_t>(a->Hkv),
                               static_cast<uint64_t>(a->B)};
     const uint64_t strk[3] = {static_cast<uint64_t>(ks[2]) * 2, static_cast<uint64_t>(ks[1]) * 2,
                               static_cast<uint64_t>(ks[0]) * 2};
@@ -481,13 +483,15 @@ extern "C" int wk_attn_fwd_bf16(const wk_attn_fwd_args* a, void* stream) {
                        (reinterpret_cast<uintptr_t>(a->workspace) & 3)))
     return WK_E_ARG;
 
-  if (allow_smem(reinterpret_cast<const void*>(attn_fwd_bf16_kernel), SMEM_BYTES)) return WK_E_CUDA;
+  const void* kernel = a->d == 64 ? reinterpret_cast<const void*>(attn_fwd_bf16_kernel<64>)
+                                  : reinterpret_cast<const void*>(attn_fwd_bf16_kernel<128>);
+  if (allow_smem(kernel, SMEM_BYTES)) return WK_E_CUDA;
   const int num_m = (a->Nq + BM - 1) / BM;
   p.m_first = 0;
   dim3 grid(num_m, a->Hq, a->B);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  attn_fwd_bf16_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
-  if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+  void* args[] = {&tq, &tk, &tv, &p};
+  if (cudaLaunchKernel(kernel, grid, dim3(THREADS), args, SMEM_BYTES, st) != cudaSuccess) return WK_E_CUDA;
   // blocks the kernel flagged as beyond its exponent range are computed again (normally none)
   return p.redo ? launch_attn_fwd_redo(a, true, p.redo, st) : 0;
 }

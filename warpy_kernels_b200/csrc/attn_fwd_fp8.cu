@@ -78,7 +78,11 @@ __device__ unsigned long long g_fwd_probe[32];
 
 constexpr int BM = 128;       // queries per CTA
 constexpr int BN = 64;        // keys per tile
-constexpr int D = 128;        // head dimension (bytes per row in e4m3)
+constexpr int D = 128;        // bytes per row of a tile in shared memory: head dimension 128, or head dimension 64
+                              // with the upper half of every row zero (filled in by TMA: the tensor maps
+                              // describe 64-byte rows, the boxes are 128 bytes wide).  The kernels are
+                              // instantiated for DH = 128 and 64; with 64 the products over the head
+                              // dimension take two K steps instead of four, P.V has N = 64, and O is 64 columns.
 constexpr int KV_STAGES = 4;
 constexpr int Q_BYTES = BM * D;     // 16 KiB
 constexpr int KV_BYTES = BN * D;    // 8 KiB
@@ -109,6 +113,7 @@ struct FwdParams {
   int64_t out_stride_b, out_stride_h, out_stride_n;  // elements
   int64_t lse_stride_b, lse_stride_h;                // elements
   int B, Hq, Hkv, Nq, Nk;
+  int d;  // head dimension, 128 or 64 (the persistent kernel reads it at run time; the two-CTA kernel is instantiated)
   int causal;
   int write_lse;
   int lse_natural;
@@ -184,7 +189,7 @@ __device__ __forceinline__ float block_max(const uint32_t (&s)[32]) {
 // RESID: this instantiation handles the query blocks that see at most RESID_MAX_TILES key tiles and carries P
 // as two e4m3 terms; the other instantiation handles all other blocks.  Both are launched on the full grid and
 // a CTA leaves at once when the block is not of its kind.
-template <bool RESID>
+template <bool RESID, int DH>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FwdParams p) {
@@ -293,7 +298,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const uint64_t k_desc = smem_desc_sw128(k_smem + s * KV_BYTES, 16, 1024);
         const uint32_t s_tmem = tmem_base + (j & 1) * S_COLS;
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k) {
+        for (int k = 0; k < DH / 32; ++k) {
           // 32 e4m3 = 32 bytes along the head dimension inside the 128-byte swizzle span
           mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k != 0);
         }
@@ -316,14 +321,14 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
         for (int k = 0; k < BN / 32; ++k) {
           // P: 32 e4m3 per K step = 8 TMEM columns at column 32 k; scale byte k of the row's scale word
-          mma_mxf8_ts(o_tmem, s_tmem + 32 * k, v_desc + 256 * k, make_idesc_mx_major(BM, D, k, 0, 0, 1),
+          mma_mxf8_ts(o_tmem, s_tmem + 32 * k, v_desc + 256 * k, make_idesc_mx_major(BM, DH, k, 0, 0, 1),
                       s_tmem + SFA_COL, s_tmem + SFB_COL, (j | k) != 0);
         }
         if (RESID) {
 #pragma unroll
           for (int k = 0; k < BN / 32; ++k) {
             mma_mxf8_ts(o_tmem, s_tmem + 32 * k + PLO_OFF, v_desc + 256 * k,
-                        make_idesc_mx_major(BM, D, k, 0, 0, 1), s_tmem + SFA_LO_COL, s_tmem + SFB_COL, 1);
+                        make_idesc_mx_major(BM, DH, k, 0, 0, 1), s_tmem + SFA_LO_COL, s_tmem + SFB_COL, 1);
           }
         }
         tc_commit(v_empty(s));
@@ -434,7 +439,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       asm volatile("bar.sync 1, 256;" ::: "memory");
     }
 
-    // epilogue: the groups add up their sums; group g stores head-dim columns [64 g, 64 g + 64)
+    // epilogue: the groups add up their sums; group g stores head-dim columns [DH / 2 . g, DH / 2 . (g + 1))
     if (n_tiles > 0 && ok) ok = mbar_wait_warp(o_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
     const uint32_t x_mine = xch_smem + (1 + 3 * grp) * BM * 4 + r * 4;
     const uint32_t x_other = xch_smem + (1 + 3 * (grp ^ 1)) * BM * 4 + r * 4;
@@ -454,11 +459,11 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       tc_fence_after();
       const bool empty = !(l > 0.f);
       const float inv = empty ? 0.f : sv / l;
-      const int col0 = 64 * grp;
+      const int col0 = (DH / 2) * grp;
       __nv_bfloat16* out_row = p.out + b * p.out_stride_b + hq * p.out_stride_h +
                                static_cast<int64_t>(row) * p.out_stride_n + col0;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < DH / 64; ++c) {
         uint32_t v[32];
         if (n_tiles > 0) {
           tmem_ld32(o_tmem + col0 + c * 32, v);
@@ -600,12 +605,13 @@ __device__ __noinline__ bool wide_store_output(const FwdParams& p, uint32_t xch,
       p.out + b * p.out_stride_b + hq * p.out_stride_h + static_cast<int64_t>(row) * p.out_stride_n + col0;
   {
     uint32_t v[32];
+    // head dimension 64: the first two groups store it all (the others read columns nobody has written and drop them)
     tmem_ld32(o_tmem + col0, v);
     tc_wait_ld();
     // O is in registers: the next block's first P.V product may overwrite it
     tc_fence_before();
     mbar_arrive(o_free);
-    if (row < p.Nq) {
+    if (col0 < p.d && row < p.Nq) {
       uint4* dst = reinterpret_cast<uint4*>(out_row);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -797,8 +803,8 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           const uint32_t s_tmem = tmem_base + 128 * buf;
 #pragma unroll
           for (int k = 0; k < D / 32; ++k) {
-            // 32 e4m3 = 32 bytes along the head dimension inside the 128-byte swizzle span
-            mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k != 0);
+            // 32 e4m3 = 32 bytes along the head dimension inside the 128-byte swizzle span (two steps for d = 64)
+            if (32 * k < p.d) mma_f8_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k != 0);
           }
           tc_commit(s_full(buf));
         }
@@ -812,6 +818,8 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     // ---- O += P.V, 64 keys at a time ------------------------------------------------------------------------------
     if (lane == 0) {
       const uint32_t o_tmem = tmem_base + M_O_COL;
+      // N = head dimension; the scale-factor id of A (the byte of the row's scale word) is added per K step
+      const uint32_t idesc_pv = make_idesc_mx_major(BM, p.d, 0, 0, 0, 1);
       int ci = -1;
       uint32_t gr = 0;
       PROBE_DECL;
@@ -843,7 +851,7 @@ attn_fwd_fp8_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
               // P: 32 e4m3 per K step = 8 TMEM columns; scale byte k of the row's scale word
-              mma_mxf8_ts(o_tmem, p_tmem + 8 * k, v_desc + 256 * (2 * h + k), make_idesc_mx_major(BM, D, k, 0, 0, 1),
+              mma_mxf8_ts(o_tmem, p_tmem + 8 * k, v_desc + 256 * (2 * h + k), idesc_pv | (k << 29),
                           p_tmem + M_SFA_OFF, tmem_base + M_SFB_COL, (R | h | k) != 0);
             }
           }
@@ -1065,7 +1073,7 @@ extern "C" int wk_fwd_probe_read(unsigned long long* out, int clear) {
 extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
   using namespace wk;
   if (!a) return WK_E_ARG;
-  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Nq <= 0 || a->Nk <= 0 || a->d != D) return WK_E_ARG;
+  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Nq <= 0 || a->Nk <= 0 || (a->d != 128 && a->d != 64)) return WK_E_ARG;
   if (a->Hq % a->Hkv) return WK_E_ARG;
   if (!a->q || !a->k || !a->v || !a->out || !a->q_descale || !a->k_descale || !a->v_descale) return WK_E_ARG;
   if (a->write_lse && (!a->lse || !a->pmax)) return WK_E_ARG;
@@ -1087,7 +1095,8 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
   const uint32_t box[4] = {D, BM, 1, 1};
   const uint32_t box_kv[4] = {D, BN, 1, 1};
   {
-    const uint64_t dims[4] = {D, static_cast<uint64_t>(a->Nq), static_cast<uint64_t>(a->Hq),
+    // rows of a->d bytes under boxes of 128: with head dimension 64 TMA fills the upper half of every row with zeros
+    const uint64_t dims[4] = {static_cast<uint64_t>(a->d), static_cast<uint64_t>(a->Nq), static_cast<uint64_t>(a->Hq),
                               static_cast<uint64_t>(a->B)};
     const uint64_t str[3] = {static_cast<uint64_t>(qs[2]), static_cast<uint64_t>(qs[1]),
                              static_cast<uint64_t>(qs[0])};
@@ -1095,7 +1104,7 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
     if (r) return r;
   }
   {
-    const uint64_t dims[4] = {D, static_cast<uint64_t>(a->Nk), static_cast<uint64_t>(a->Hkv),
+    const uint64_t dims[4] = {static_cast<uint64_t>(a->d), static_cast<uint64_t>(a->Nk), static_cast<uint64_t>(a->Hkv),
                               static_cast<uint64_t>(a->B)};
     const uint64_t strk[3] = {static_cast<uint64_t>(ks[2]), static_cast<uint64_t>(ks[1]),
                               static_cast<uint64_t>(ks[0])};
@@ -1128,6 +1137,7 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
   p.Hkv = a->Hkv;
   p.Nq = a->Nq;
   p.Nk = a->Nk;
+  p.d = a->d;
   p.causal = a->causal;
   p.write_lse = a->write_lse;
   p.lse_natural = a->lse_natural;
@@ -1139,15 +1149,20 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
                        (reinterpret_cast<uintptr_t>(a->workspace) & 3)))
     return WK_E_ARG;
 
-  if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<false>), SMEM_BYTES)) return WK_E_CUDA;
-  if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_wide_kernel), M_SMEM_BYTES)) return WK_E_CUDA;
+  const bool d64 = a->d == 64;
+  const void* k_main = d64 ? reinterpret_cast<const void*>(attn_fwd_fp8_kernel<false, 64>)
+                           : reinterpret_cast<const void*>(attn_fwd_fp8_kernel<false, 128>);
+  const void* k_resid = d64 ? reinterpret_cast<const void*>(attn_fwd_fp8_kernel<true, 64>)
+                            : reinterpret_cast<const void*>(attn_fwd_fp8_kernel<true, 128>);
+  const void* k_wide = reinterpret_cast<const void*>(attn_fwd_fp8_wide_kernel);
+  if (allow_smem(k_main, SMEM_BYTES) || allow_smem(k_resid, SMEM_BYTES) || allow_smem(k_wide, M_SMEM_BYTES))
+    return WK_E_CUDA;
   // ctas_per_sm: 0 picks by the number of keys.  Measured with equal work (causal / full, TFLOP/s), the wide kernel
   // against the two-CTA kernel: 1024 keys 723 / 1066 against 723 / 1070, 2048 keys 1012 / 1289 against 989 / 1253,
   // 4096 keys 1215 / 1412 against 1149 / 1342, 8192 keys 1321 / 1488 against 1192 / 1348, 16384 keys (causal) 1417
   // against 1140
   if (a->ctas_per_sm < 0 || a->ctas_per_sm > 2) return WK_E_ARG;
   const bool wide = a->ctas_per_sm == 1 || (a->ctas_per_sm == 0 && a->Nk >= 2048);
-  if (allow_smem(reinterpret_cast<const void*>(attn_fwd_fp8_kernel<true>), SMEM_BYTES)) return WK_E_CUDA;
   const int num_m = (a->Nq + BM - 1) / BM;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // Query blocks that see few key tiles run the two-term variant.  The tile count never decreases with the
@@ -1172,9 +1187,9 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
   // run (programmatic stream serialisation), fills the SMs as they leave instead of waiting for the last of them.
   if (resid_count > 0) {
     p.m_first = 0;
-    dim3 grid(resid_count, a->Hq, a->B);
-    attn_fwd_fp8_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
-    if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+    void* args[] = {&tq, &tk, &tv, &p};
+    if (cudaLaunchKernel(k_resid, dim3(resid_count, a->Hq, a->B), dim3(THREADS), args, SMEM_BYTES, st) != cudaSuccess)
+      return WK_E_CUDA;
   }
   if (num_m - main_first > 0) {
     p.m_first = main_first;
@@ -1186,18 +1201,11 @@ extern "C" int wk_attn_fwd_fp8(const wk_attn_fwd_args* a, void* stream) {
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = resid_count > 0 ? 1 : 0;
-    cudaError_t e;
-    if (wide) {
-      // one CTA per query block in the grid; the CTAs that start take over the blocks of those that have not yet
-      cfg.blockDim = dim3(M_THREADS);
-      cfg.dynamicSmemBytes = M_SMEM_BYTES;
-      e = cudaLaunchKernelEx(&cfg, attn_fwd_fp8_wide_kernel, tq, tk128, tv128, p);
-    } else {
-      cfg.blockDim = dim3(THREADS);
-      cfg.dynamicSmemBytes = SMEM_BYTES;
-      e = cudaLaunchKernelEx(&cfg, attn_fwd_fp8_kernel<false>, tq, tk, tv, p);
-    }
-    if (e != cudaSuccess) return WK_E_CUDA;
+    // wide: one CTA per query block in the grid; the CTAs that start take over the blocks of those that have not yet
+    cfg.blockDim = dim3(wide ? M_THREADS : THREADS);
+    cfg.dynamicSmemBytes = wide ? M_SMEM_BYTES : SMEM_BYTES;
+    void* args[] = {&tq, wide ? &tk128 : &tk, wide ? &tv128 : &tv, &p};
+    if (cudaLaunchKernelExC(&cfg, wide ? k_wide : k_main, args) != cudaSuccess) return WK_E_CUDA;
   }
   if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
   // blocks the kernels above flagged as beyond their exponent range are computed again (normally none)

@@ -1,4 +1,4 @@
-// Recomputation of flagged query blocks of the attention forward (FP8 and BF16 inputs), head dimension 128.
+// Recomputation of flagged query blocks of the attention forward (FP8 and BF16 inputs), head dimension 128 or 64.
 //
 // The tensor-core forward kernels keep one reference exponent per query row, fixed by the row's first 64 keys, and
 // can represent scores up to 2^100 above it.  A query block in which some row meets a later key beyond that range
@@ -9,7 +9,8 @@
 // pathological (one key more than 69 nats above the start of the row), so this path is written for clarity, not speed.
 //
 // One CTA of 512 threads per flagged block: four threads per query row, each owning 32 of the 128 head-dim
-// elements; K and V pass through shared memory 64 keys at a time.  A launch covers every block of the call with a
+// elements (with head dimension 64 two of the four hold zeros and only join the reductions); K and V pass through
+// shared memory 64 keys at a time.  A launch covers every block of the call with a
 // grid-stride loop over the flags, so with nothing flagged it costs one small launch that reads the flags and leaves.
 #include <math.h>
 
@@ -20,7 +21,7 @@ namespace wk {
 namespace {
 
 constexpr int R_BM = 128;    // queries per block (the forward kernels' block)
-constexpr int R_D = 128;     // head dimension
+constexpr int R_D = 128;     // largest head dimension
 constexpr int R_KEYS = 64;   // keys per shared-memory chunk
 constexpr int R_THREADS = 512;
 constexpr int R_PART = 32;   // head-dim elements per thread
@@ -37,7 +38,7 @@ struct RedoParams {
   const float* v_descale;
   int64_t q_strides[3], k_strides[3], v_strides[3], out_strides[3];  // elements, dims (B, H, N)
   int64_t lse_stride_b, lse_stride_h;
-  int B, Hq, Hkv, Nq, Nk, causal, write_lse, lse_natural;
+  int B, Hq, Hkv, Nq, Nk, d, causal, write_lse, lse_natural;
   const int* seqused_k;
   float softmax_scale;
   int* flags;
@@ -76,14 +77,15 @@ __device__ __forceinline__ void load32(const uint8_t* src, float (&x)[R_PART]) {
 template <bool BF16>
 __global__ void __launch_bounds__(R_THREADS) attn_fwd_redo_kernel(const RedoParams p) {
   constexpr int ES = BF16 ? 2 : 1;                 // bytes per element
-  constexpr int ROW_BYTES = R_D * ES;
-  constexpr int CHUNK_VECS = R_KEYS * ROW_BYTES / 16;  // 16-byte vectors per chunk
-  __shared__ __align__(16) uint8_t k_s[R_KEYS * ROW_BYTES];
-  __shared__ __align__(16) uint8_t v_s[R_KEYS * ROW_BYTES];
+  __shared__ __align__(16) uint8_t k_s[R_KEYS * R_D * ES];
+  __shared__ __align__(16) uint8_t v_s[R_KEYS * R_D * ES];
+  const int ROW_BYTES = p.d * ES;
+  const int CHUNK_VECS = R_KEYS * ROW_BYTES / 16;  // 16-byte vectors per chunk
 
   const int tid = threadIdx.x;
   const int r = tid >> 2;     // query row of the block
   const int part = tid & 3;   // which 32 head-dim elements
+  const bool part_ok = part * R_PART < p.d;
   const int num_m = (p.Nq + R_BM - 1) / R_BM;
   const int total = p.B * p.Hq * num_m;
 
@@ -112,7 +114,7 @@ __global__ void __launch_bounds__(R_THREADS) attn_fwd_redo_kernel(const RedoPara
     const float sv = BF16 ? 1.f : p.v_descale[sc];
 
     float qf[R_PART];
-    if (row_ok) {
+    if (row_ok && part_ok) {
       load32<BF16>(p.q + (b * p.q_strides[0] + hq * p.q_strides[1] + static_cast<int64_t>(row) * p.q_strides[2] +
                           part * R_PART) * ES, qf);
     } else {
@@ -134,11 +136,13 @@ __global__ void __launch_bounds__(R_THREADS) attn_fwd_redo_kernel(const RedoPara
     };
     // score of this thread's row against key j of the staged chunk (the four threads of a row each hold a quarter)
     auto score = [&](int j) {
-      float kf[R_PART];
-      load32<BF16>(k_s + j * ROW_BYTES + part * R_PART * ES, kf);
       float acc = 0.f;
+      if (part_ok) {
+        float kf[R_PART];
+        load32<BF16>(k_s + j * ROW_BYTES + part * R_PART * ES, kf);
 #pragma unroll
-      for (int i = 0; i < R_PART; ++i) acc = fmaf(qf[i], kf[i], acc);
+        for (int i = 0; i < R_PART; ++i) acc = fmaf(qf[i], kf[i], acc);
+      }
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       return acc * beta;
@@ -172,10 +176,12 @@ __global__ void __launch_bounds__(R_THREADS) attn_fwd_redo_kernel(const RedoPara
         if (c0 + j <= limit) {
           const float pj = exp2f(s - m);
           l += pj;
-          float vf[R_PART];
-          load32<BF16>(v_s + j * ROW_BYTES + part * R_PART * ES, vf);
+          if (part_ok) {
+            float vf[R_PART];
+            load32<BF16>(v_s + j * ROW_BYTES + part * R_PART * ES, vf);
 #pragma unroll
-          for (int i = 0; i < R_PART; ++i) o[i] = fmaf(pj, vf[i], o[i]);
+            for (int i = 0; i < R_PART; ++i) o[i] = fmaf(pj, vf[i], o[i]);
+          }
         }
       }
     }
@@ -187,7 +193,7 @@ __global__ void __launch_bounds__(R_THREADS) attn_fwd_redo_kernel(const RedoPara
                                static_cast<int64_t>(row) * p.out_strides[2] + part * R_PART;
       uint4* dst = reinterpret_cast<uint4*>(out_row);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; part_ok && i < 4; ++i) {
         uint4 w;
         w.x = pack_bf16x2(o[8 * i + 0] * inv, o[8 * i + 1] * inv);
         w.y = pack_bf16x2(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
@@ -236,6 +242,7 @@ int launch_attn_fwd_redo(const wk_attn_fwd_args* a, bool bf16, int* flags, cudaS
   p.Hkv = a->Hkv;
   p.Nq = a->Nq;
   p.Nk = a->Nk;
+  p.d = a->d;
   p.causal = a->causal;
   p.write_lse = a->write_lse;
   p.lse_natural = a->lse_natural;
