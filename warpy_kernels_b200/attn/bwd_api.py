@@ -13,7 +13,7 @@ import torch
 from .. import _lib
 from ..arch import require
 from ..utils import autotune, cached_tensor, check_descale
-from .fwd_api import KERNEL_D, _check_qkv, _check_shapes, _kernel_view, _pad_head_dim
+from .fwd_api import _check_qkv, _check_shapes, _kernel_view
 
 
 class _BwdArgs(ctypes.Structure):
@@ -121,20 +121,16 @@ def make_attn_bwd(
     else:
         ones = cached_tensor(("ones", dev, B, Hkv), lambda: torch.ones(B, Hkv, dtype=torch.float32, device=dev))
         dq_, dk_, dv_ = [(x if x is not None else ones).float().contiguous() for x in (q_descale, k_descale, v_descale)]
-    if d != KERNEL_D:
-        # head dimension 64: the 128 kernels on zero-padded copies; the extra gradient columns are dropped
-        qv, kv, vv, ov, dov = (_pad_head_dim(x) for x in (q, k, v, out, dout))
-    else:
-        qv, kv, vv = _kernel_view(q), _kernel_view(k), _kernel_view(v)
-        ov = _bf16_view(out)
-        # the bf16 kernels read dout through TMA like q: 16-byte aligned base and strides
-        dov = _kernel_view(dout if dout.dtype == torch.bfloat16 else dout.to(torch.bfloat16)) if bf16 else _bf16_view(dout)
+    qv, kv, vv = _kernel_view(q), _kernel_view(k), _kernel_view(v)  # head dimension 64 and 128 both run natively
+    ov = _bf16_view(out)
+    # the bf16 kernels read dout through TMA like q: 16-byte aligned base and strides
+    dov = _kernel_view(dout if dout.dtype == torch.bfloat16 else dout.to(torch.bfloat16)) if bf16 else _bf16_view(dout)
     lsev = lse.float()
     if lsev.stride(2) != 1:
         lsev = lsev.contiguous()
-    dq = torch.empty(B, Hq, Nq, KERNEL_D, dtype=torch.bfloat16, device=dev)
-    dk = torch.empty(B, Hkv, Nk, KERNEL_D, dtype=torch.bfloat16, device=dev)
-    dv = torch.empty(B, Hkv, Nk, KERNEL_D, dtype=torch.bfloat16, device=dev)
+    dq = torch.empty(B, Hq, Nq, d, dtype=torch.bfloat16, device=dev)
+    dk = torch.empty(B, Hkv, Nk, d, dtype=torch.bfloat16, device=dev)
+    dv = torch.empty(B, Hkv, Nk, d, dtype=torch.bfloat16, device=dev)
     lib = _lib.lib()
     ws_bytes = (lib.wk_attn_bwd_bf16_workspace_bytes if bf16 else lib.wk_attn_bwd_fp8_workspace_bytes)(B, Hq, Nq)
     workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
@@ -152,7 +148,7 @@ def make_attn_bwd(
     args.out_strides = (ctypes.c_int64 * 3)(*ov.stride()[:3])
     args.dout_strides = (ctypes.c_int64 * 3)(*dov.stride()[:3])
     args.lse_strides = (ctypes.c_int64 * 2)(*lsev.stride()[:2])
-    args.B, args.Hq, args.Hkv, args.Nq, args.Nk, args.d = B, Hq, Hkv, Nq, Nk, KERNEL_D
+    args.B, args.Hq, args.Hkv, args.Nq, args.Nk, args.d = B, Hq, Hkv, Nq, Nk, d
     args.causal, args.softmax_scale = int(bool(causal)), float(softmax_scale)
     keep = (qv, kv, vv, ov, dov, lsev, dq_, dk_, dv_, workspace, dq, dk, dv)  # inputs, scratch and outputs
 
@@ -165,8 +161,6 @@ def make_attn_bwd(
         return keep
 
     def finish():
-        if d != KERNEL_D:
-            return tuple(g[..., :d].contiguous() for g in (dq, dk, dv))
         return dq, dk, dv
 
     return launch, finish

@@ -58,21 +58,6 @@ def _kernel_view(x):
     return x if direct else x.contiguous()
 
 
-KERNEL_D = 128  # head dimension of the compiled kernels
-
-
-def _pad_head_dim(x):
-    """Zero-padded contiguous copy ``[..., 128]`` of a ``[..., 64]`` tensor.
-
-    Head dimension 64 runs through the head-dimension-128 kernels: zero columns add nothing to ``Q K^T`` and give
-    zero output columns, which the wrappers drop. Correct, at half the tensor-core efficiency of a native kernel.
-    """
-    padded = torch.zeros(*x.shape[:-1], KERNEL_D, dtype=torch.uint8 if x.element_size() == 1 else x.dtype, device=x.device)
-    src = x.view(torch.uint8) if x.element_size() == 1 else x
-    padded[..., : x.shape[-1]] = src
-    return padded.view(x.dtype) if x.element_size() == 1 else padded
-
-
 def _check_qkv(q, k, v):
     if not (q.dtype == k.dtype == v.dtype and q.dtype in (torch.float8_e4m3fn, torch.bfloat16)):
         raise ValueError("q, k and v must all be torch.float8_e4m3fn or all torch.bfloat16")

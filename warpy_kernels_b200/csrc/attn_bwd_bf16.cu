@@ -28,7 +28,8 @@ namespace {
 
 constexpr int BM = 128;  // queries per tile
 constexpr int BN = 128;  // keys per tile
-constexpr int D = 128;
+constexpr int D = 128;  // largest head dimension; with 64 (a run-time parameter) a row is one swizzle span instead of
+                        // two: the second box of every tile is not loaded and the products take half the K steps
 constexpr int CHUNK = 64;                        // head-dim elements per 128-byte swizzle span
 constexpr int CHUNK_BYTES = 128 * CHUNK * 2;     // 16 KiB: 128 rows x 128 bytes
 constexpr int TILE_BYTES = 2 * CHUNK_BYTES;      // 32 KiB: 128 rows x 256 bytes
@@ -50,7 +51,7 @@ struct PrepParams {
   int64_t do_sb, do_sh, do_sn;
   int64_t o_sb, o_sh, o_sn;
   int64_t lse_sb, lse_sh;
-  int B, Hq, Nq, nq_pad;
+  int B, Hq, Nq, nq_pad, d;
 };
 
 // one warp per query row, 4 consecutive elements per lane
@@ -71,8 +72,9 @@ __global__ void __launch_bounds__(256) attn_bwd_bf16_prep_kernel(const PrepParam
   }
   const __nv_bfloat16* dsrc = p.dout + b * p.do_sb + h * p.do_sh + static_cast<int64_t>(i) * p.do_sn + lane * 4;
   const __nv_bfloat16* osrc = p.out + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(i) * p.o_sn + lane * 4;
-  const uint2 draw = *reinterpret_cast<const uint2*>(dsrc);
-  const uint2 oraw = *reinterpret_cast<const uint2*>(osrc);
+  const bool mine = lane * 4 < p.d;  // head dimension 64: half the lanes only join the reduction
+  const uint2 draw = mine ? *reinterpret_cast<const uint2*>(dsrc) : make_uint2(0, 0);
+  const uint2 oraw = mine ? *reinterpret_cast<const uint2*>(osrc) : make_uint2(0, 0);
   float dsum = __uint_as_float(draw.x << 16) * __uint_as_float(oraw.x << 16) +
                __uint_as_float(draw.x & 0xffff0000u) * __uint_as_float(oraw.x & 0xffff0000u) +
                __uint_as_float(draw.y << 16) * __uint_as_float(oraw.y << 16) +
@@ -100,7 +102,7 @@ __global__ void __launch_bounds__(256) attn_bwd_bf16_prep4_kernel(const PrepPara
   const int b = static_cast<int>(row_id / (static_cast<int64_t>(p.nq_pad) * p.Hq));
   const bool live = i < p.Nq;  // padding rows take part in the shuffles with zeros
   uint4 draw[2] = {}, oraw[2] = {};
-  if (live) {
+  if (live && sub * 16 < p.d) {  // head dimension 64: half the lanes only join the reduction
     const uint4* dsrc = reinterpret_cast<const uint4*>(p.dout + b * p.do_sb + h * p.do_sh +
                                                        static_cast<int64_t>(i) * p.do_sn + sub * 16);
     const uint4* osrc =
@@ -162,6 +164,7 @@ struct BwdParams {
   __nv_bfloat16* dk;     // [B,Hkv,Nk,D] contiguous
   __nv_bfloat16* dv;
   int B, Hq, Hkv, Nq, Nk, nq_pad;
+  int d;  // head dimension, 128 or 64
   int causal;
   float softmax_scale;
   int* status;
@@ -239,8 +242,9 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 
   if (warp == 0) {
     if (lane == 0 && n_iter > 0) {
-      mbar_expect_tx(kv_full, 2 * TILE_BYTES);
-      for (int c = 0; c < 2; ++c) {
+      const int chunks = p.d / CHUNK;
+      mbar_expect_tx(kv_full, 2 * chunks * CHUNK_BYTES);
+      for (int c = 0; c < chunks; ++c) {
         tma_load_4d(k_smem + c * CHUNK_BYTES, &tmap_k, kv_full, c * CHUNK, n0, hkv, b);
         tma_load_4d(v_smem + c * CHUNK_BYTES, &tmap_v, kv_full, c * CHUNK, n0, hkv, b);
       }
@@ -251,8 +255,8 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         const int m0 = (m_first + it % tiles_per_head) * BM;
         if (!mbar_wait(q_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
         const uint32_t base = stage_smem + s * A_STAGE_BYTES;
-        mbar_expect_tx(q_full(s), A_STAGE_BYTES);
-        for (int c = 0; c < 2; ++c) {
+        mbar_expect_tx(q_full(s), 2 * chunks * CHUNK_BYTES + A_STAT_BYTES);
+        for (int c = 0; c < chunks; ++c) {
           tma_load_4d(base + c * CHUNK_BYTES, &tmap_q, q_full(s), c * CHUNK, m0, hq, b);
           tma_load_4d(base + TILE_BYTES + c * CHUNK_BYTES, &tmap_do, q_full(s), c * CHUNK, m0, hq, b);
         }
@@ -269,7 +273,7 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       // All MMAs come from this one thread, so the products of the next tile overwrite a half's columns only
       // after the products that read its codes (the tensor pipe runs in issue order).
       constexpr uint32_t idesc_ss = make_idesc(1, 1, 0, 0, BN, BM / 2);
-      constexpr uint32_t idesc_ts = make_idesc(1, 1, 0, 1, BN, D);  // B read MN-major
+      const uint32_t idesc_ts = make_idesc(1, 1, 0, 1, BN, p.d);  // B read MN-major, N = head dimension
       const uint32_t st_tmem = tmem_base + A_ST_COL;
       const uint32_t dpt_tmem = tmem_base + A_DPT_COL;
       bool ok = mbar_wait(kv_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
@@ -285,12 +289,12 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t off = (k >> 2) * (CHUNK_BYTES >> 4) + 2 * (k & 3);
-          mma_f16_ss(st_tmem + HALF_COLS * h, k_desc + off, q_desc + off, idesc_ss, k != 0);
+          if (16 * k < p.d) mma_f16_ss(st_tmem + HALF_COLS * h, k_desc + off, q_desc + off, idesc_ss, k != 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t off = (k >> 2) * (CHUNK_BYTES >> 4) + 2 * (k & 3);
-          mma_f16_ss(dpt_tmem + HALF_COLS * h, v_desc + off, do_desc + off, idesc_ss, k != 0);
+          if (16 * k < p.d) mma_f16_ss(dpt_tmem + HALF_COLS * h, v_desc + off, do_desc + off, idesc_ss, k != 0);
         }
         tc_commit(s_full(h));
       };
@@ -417,7 +421,7 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
     if (ok) {
       tc_fence_after();
       const float dk_scale = p.softmax_scale;
-      const int64_t row_off = ((static_cast<int64_t>(b) * p.Hkv + hkv) * p.Nk + key) * D;
+      const int64_t row_off = ((static_cast<int64_t>(b) * p.Hkv + hkv) * p.Nk + key) * p.d;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         const uint32_t src = tmem_base + lane_addr + (which == 0 ? A_DV_COL : A_DK_COL);
@@ -433,7 +437,7 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0;
           }
-          if (key < p.Nk) {
+          if (key < p.Nk && c * 32 < p.d) {
             uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -528,8 +532,9 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(q_full, 2 * TILE_BYTES);
-      for (int c = 0; c < 2; ++c) {
+      const int chunks = p.d / CHUNK;
+      mbar_expect_tx(q_full, 2 * chunks * CHUNK_BYTES);
+      for (int c = 0; c < chunks; ++c) {
         tma_load_4d(q_smem + c * CHUNK_BYTES, &tmap_q, q_full, c * CHUNK, m0, hq, b);
         tma_load_4d(do_smem + c * CHUNK_BYTES, &tmap_do, q_full, c * CHUNK, m0, hq, b);
       }
@@ -538,8 +543,8 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         const uint32_t ph = (j / B_STAGES) & 1;
         if (!mbar_wait(kv_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
         const uint32_t base = stage_smem + s * B_STAGE_BYTES;
-        mbar_expect_tx(kv_full(s), B_STAGE_BYTES);
-        for (int c = 0; c < 2; ++c) {
+        mbar_expect_tx(kv_full(s), 2 * chunks * CHUNK_BYTES);
+        for (int c = 0; c < chunks; ++c) {
           tma_load_4d(base + c * CHUNK_BYTES, &tmap_k, kv_full(s), c * CHUNK, j * BN, hkv, b);
           tma_load_4d(base + TILE_BYTES + c * CHUNK_BYTES, &tmap_v, kv_full(s), c * CHUNK, j * BN, hkv, b);
         }
@@ -551,7 +556,7 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       // Key tiles are processed as two halves of 64 keys, as in the dK/dV kernel: the tensor pipe works on one
       // half while the element-wise warps of the other are busy.
       constexpr uint32_t idesc_ss = make_idesc(1, 1, 0, 0, BM, BN / 2);
-      constexpr uint32_t idesc_ts = make_idesc(1, 1, 0, 1, BM, D);  // B read MN-major
+      const uint32_t idesc_ts = make_idesc(1, 1, 0, 1, BM, p.d);  // B read MN-major, N = head dimension
       const uint32_t s_tmem = tmem_base + B_S_COL;
       const uint32_t dp_tmem = tmem_base + B_DP_COL;
       bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
@@ -566,12 +571,12 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t off = (k >> 2) * (CHUNK_BYTES >> 4) + 2 * (k & 3);
-          mma_f16_ss(s_tmem + HALF_COLS * h, q_desc + off, k_desc + off, idesc_ss, k != 0);
+          if (16 * k < p.d) mma_f16_ss(s_tmem + HALF_COLS * h, q_desc + off, k_desc + off, idesc_ss, k != 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t off = (k >> 2) * (CHUNK_BYTES >> 4) + 2 * (k & 3);
-          mma_f16_ss(dp_tmem + HALF_COLS * h, do_desc + off, v_desc + off, idesc_ss, k != 0);
+          if (16 * k < p.d) mma_f16_ss(dp_tmem + HALF_COLS * h, do_desc + off, v_desc + off, idesc_ss, k != 0);
         }
         tc_commit(s_full(h));
       };
@@ -667,7 +672,7 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     if (ok) {
       tc_fence_after();
       const float scale = p.softmax_scale;
-      __nv_bfloat16* dst_row = p.dq + ((static_cast<int64_t>(b) * p.Hq + hq) * p.Nq + row) * D;
+      __nv_bfloat16* dst_row = p.dq + ((static_cast<int64_t>(b) * p.Hq + hq) * p.Nq + row) * p.d;
 #pragma unroll 1
       {
         uint32_t v[32];
@@ -678,7 +683,7 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0;
         }
-        if (row < p.Nq) {
+        if (row < p.Nq && c * 32 < p.d) {
           uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -702,8 +707,8 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   }
 }
 
-int make_map4(CUtensorMap* m, const void* base, int n, int h, int b, const int64_t* strides) {
-  const uint64_t dims[4] = {D, static_cast<uint64_t>(n), static_cast<uint64_t>(h), static_cast<uint64_t>(b)};
+int make_map4(CUtensorMap* m, const void* base, int d, int n, int h, int b, const int64_t* strides) {
+  const uint64_t dims[4] = {static_cast<uint64_t>(d), static_cast<uint64_t>(n), static_cast<uint64_t>(h), static_cast<uint64_t>(b)};
   const uint64_t str[3] = {static_cast<uint64_t>(strides[2]) * 2, static_cast<uint64_t>(strides[1]) * 2,
                            static_cast<uint64_t>(strides[0]) * 2};
   const uint32_t box[4] = {CHUNK, 128, 1, 1};
@@ -722,7 +727,7 @@ extern "C" int64_t wk_attn_bwd_bf16_workspace_bytes(int B, int Hq, int Nq) {
 extern "C" int wk_attn_bwd_bf16(const wk_attn_bwd_args* a, void* stream) {
   using namespace wk;
   if (!a) return WK_E_ARG;
-  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Nq <= 0 || a->Nk <= 0 || a->d != D) return WK_E_ARG;
+  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Nq <= 0 || a->Nk <= 0 || (a->d != 128 && a->d != 64)) return WK_E_ARG;
   if (a->Hq % a->Hkv || a->B > 65535 || a->Hq > 65535) return WK_E_ARG;
   if (!a->q || !a->k || !a->v || !a->out || !a->dout || !a->lse || !a->dq || !a->dk || !a->dv) return WK_E_ARG;
   if (a->q_descale || a->k_descale || a->v_descale || !a->workspace) return WK_E_ARG;
@@ -763,6 +768,7 @@ extern "C" int wk_attn_bwd_bf16(const wk_attn_bwd_args* a, void* stream) {
   pp.Hq = a->Hq;
   pp.Nq = a->Nq;
   pp.nq_pad = nq_pad;
+  pp.d = a->d;
   {
     const int64_t rows = static_cast<int64_t>(a->B) * a->Hq * nq_pad;
     bool wide_loads = aligned16(a->out) && aligned16(a->dout);  // 16-byte loads: rows on 16-byte boundaries
@@ -777,13 +783,13 @@ extern "C" int wk_attn_bwd_bf16(const wk_attn_bwd_args* a, void* stream) {
   }
 
   CUtensorMap tq, tk, tv, tdo;
-  int r = make_map4(&tq, a->q, a->Nq, a->Hq, a->B, a->q_strides);
+  int r = make_map4(&tq, a->q, a->d, a->Nq, a->Hq, a->B, a->q_strides);
   if (r) return r;
-  r = make_map4(&tk, a->k, a->Nk, a->Hkv, a->B, a->k_strides);
+  r = make_map4(&tk, a->k, a->d, a->Nk, a->Hkv, a->B, a->k_strides);
   if (r) return r;
-  r = make_map4(&tv, a->v, a->Nk, a->Hkv, a->B, a->v_strides);
+  r = make_map4(&tv, a->v, a->d, a->Nk, a->Hkv, a->B, a->v_strides);
   if (r) return r;
-  r = make_map4(&tdo, a->dout, a->Nq, a->Hq, a->B, a->dout_strides);
+  r = make_map4(&tdo, a->dout, a->d, a->Nq, a->Hq, a->B, a->dout_strides);
   if (r) return r;
 
   BwdParams p;
@@ -797,6 +803,7 @@ extern "C" int wk_attn_bwd_bf16(const wk_attn_bwd_args* a, void* stream) {
   p.Nq = a->Nq;
   p.Nk = a->Nk;
   p.nq_pad = nq_pad;
+  p.d = a->d;
   p.causal = a->causal;
   p.softmax_scale = a->softmax_scale;
   p.status = status;

@@ -1,4 +1,7 @@
-// FP8 (e4m3) flash-attention backward for sm_100a, head dimension 128.
+// FP8 (e4m3) flash-attention backward for sm_100a, head dimension 128 or 64 (64: tiles keep their 128-byte rows in
+// shared memory with the upper half zero -- the tensor maps describe 64-byte rows under 128-byte boxes and TMA fills
+// in the rest -- while the products over the head dimension take two K steps instead of four and dQ / dK / dV are
+// 64 columns wide; `d` is a run-time parameter of the kernels).
 //
 // Gradients with respect to the dequantised q, k, v (q = q_descale . q8 and so on):
 //   S = alpha . q k^T,  P = softmax(S) = 2^(S . log2e - L)   (L: the forward's base-2 lse)
@@ -40,7 +43,7 @@ namespace {
 
 constexpr int BM = 128;  // queries per tile
 constexpr int BN = 128;  // keys per tile
-constexpr int D = 128;
+constexpr int D = 128;  // bytes per row of a tile in shared memory (the largest head dimension)
 constexpr int TILE_BYTES = 128 * 128;
 constexpr int SF_BYTES = 512;
 constexpr int THREADS = 576;          // TMA warp, MMA warp, 16 element-wise warps (four threads per row)
@@ -62,7 +65,7 @@ struct PrepParams {
   int64_t do_sb, do_sh, do_sn;
   int64_t o_sb, o_sh, o_sn;
   int64_t lse_sb, lse_sh;
-  int B, Hq, Hkv, Nq, nq_pad;
+  int B, Hq, Hkv, Nq, nq_pad, d;
 };
 
 // one warp per query row, 4 consecutive elements per lane
@@ -83,8 +86,9 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const PrepParams p) 
   }
   const __nv_bfloat16* dsrc = p.dout + b * p.do_sb + h * p.do_sh + static_cast<int64_t>(i) * p.do_sn + lane * 4;
   const __nv_bfloat16* osrc = p.out + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(i) * p.o_sn + lane * 4;
-  const uint2 draw = *reinterpret_cast<const uint2*>(dsrc);
-  const uint2 oraw = *reinterpret_cast<const uint2*>(osrc);
+  const bool mine = lane * 4 < p.d;  // head dimension 64: half the lanes hold zeros and only join the reductions
+  const uint2 draw = mine ? *reinterpret_cast<const uint2*>(dsrc) : make_uint2(0, 0);
+  const uint2 oraw = mine ? *reinterpret_cast<const uint2*>(osrc) : make_uint2(0, 0);
   float dv[4], ov[4];
   dv[0] = __uint_as_float(draw.x << 16);
   dv[1] = __uint_as_float(draw.x & 0xffff0000u);
@@ -112,8 +116,8 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const PrepParams p) 
   float dsum = (q0 * ov[0] + q1 * ov[1]) + (q2 * ov[2] + q3 * ov[3]);
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
-  uint8_t* dst = p.do8 + ((static_cast<int64_t>(b) * p.Hq + h) * p.Nq + i) * D + lane * 4;
-  *reinterpret_cast<uint32_t*>(dst) = static_cast<uint32_t>(c01) | (static_cast<uint32_t>(c23) << 16);
+  uint8_t* dst = p.do8 + ((static_cast<int64_t>(b) * p.Hq + h) * p.Nq + i) * p.d + lane * 4;
+  if (mine) *reinterpret_cast<uint32_t*>(dst) = static_cast<uint32_t>(c01) | (static_cast<uint32_t>(c23) << 16);
   if (lane == 0) {
     const float sv = p.v_descale[b * p.Hkv + h / (p.Hq / p.Hkv)];
     const float L = p.lse[b * p.lse_sb + h * p.lse_sh + i];
@@ -138,8 +142,9 @@ __global__ void __launch_bounds__(256) attn_bwd_prep4_kernel(const PrepParams p)
   const int h = static_cast<int>((row_id / p.nq_pad) % p.Hq);
   const int b = static_cast<int>(row_id / (static_cast<int64_t>(p.nq_pad) * p.Hq));
   const bool live = i < p.Nq;  // padding rows take part in the shuffles with zeros
+  const bool mine = sub * 16 < p.d;  // head dimension 64: half the lanes hold zeros and only join the reductions
   uint4 draw[2] = {}, oraw[2] = {};
-  if (live) {
+  if (live && mine) {
     const uint4* dsrc = reinterpret_cast<const uint4*>(p.dout + b * p.do_sb + h * p.do_sh +
                                                        static_cast<int64_t>(i) * p.do_sn + sub * 16);
     const uint4* osrc =
@@ -181,8 +186,8 @@ __global__ void __launch_bounds__(256) attn_bwd_prep4_kernel(const PrepParams p)
     if (sub < 2) stat[sub * 128] = sub == 0 ? -INFINITY : 0.f;
     return;
   }
-  uint8_t* dst = p.do8 + ((static_cast<int64_t>(b) * p.Hq + h) * p.Nq + i) * D + sub * 16;
-  *reinterpret_cast<uint4*>(dst) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+  uint8_t* dst = p.do8 + ((static_cast<int64_t>(b) * p.Hq + h) * p.Nq + i) * p.d + sub * 16;
+  if (mine) *reinterpret_cast<uint4*>(dst) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
   if (sub == 0) {
     const float L = p.lse[b * p.lse_sb + h * p.lse_sh + i];
     stat[0] = log2_g - L;
@@ -268,6 +273,7 @@ struct BwdParams {
   __nv_bfloat16* dk;     // [B,Hkv,Nk,D] contiguous
   __nv_bfloat16* dv;
   int B, Hq, Hkv, Nq, Nk, nq_pad;
+  int d;  // head dimension, 128 or 64
   int causal;
   float softmax_scale;
   int* status;
@@ -453,9 +459,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const uint64_t q_desc = q_desc_of(g) + 512 * h;
         const uint64_t do_desc = q_desc + (TILE_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k) mma_f8_ss(st_tmem + HALF_COLS * h, k_desc + 2 * k, q_desc + 2 * k, idesc_ss, k != 0);
+        for (int k = 0; k < D / 32; ++k)
+          if (32 * k < p.d) mma_f8_ss(st_tmem + HALF_COLS * h, k_desc + 2 * k, q_desc + 2 * k, idesc_ss, k != 0);
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k) mma_f8_ss(dpt_tmem + HALF_COLS * h, v_desc + 2 * k, do_desc + 2 * k, idesc_ss, k != 0);
+        for (int k = 0; k < D / 32; ++k)
+          if (32 * k < p.d) mma_f8_ss(dpt_tmem + HALF_COLS * h, v_desc + 2 * k, do_desc + 2 * k, idesc_ss, k != 0);
         tc_commit(s_full(h));
       };
       // dV += (P g)^T dO8 and dK += dS^T Q8 over the same 64 queries (`it`: the tile's number inside its key block).
@@ -467,14 +475,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const uint32_t bb = st_tmem + HALF_COLS * h + 32 * k;
-          mma_mxf8_ts(tmem_base + A_DV_COL, bb, do_desc + 256 * (2 * h + k), make_idesc_mx_major(BN, D, 0, 0, 0, 1),
+          mma_mxf8_ts(tmem_base + A_DV_COL, bb, do_desc + 256 * (2 * h + k), make_idesc_mx_major(BN, p.d, 0, 0, 0, 1),
                       bb + A_SF_P, bb + A_SF_UNIT, (it | h | k) != 0);
         }
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const uint32_t bb = st_tmem + HALF_COLS * h + 32 * k;
           mma_mxf8_ts(tmem_base + A_DK_COL, dpt_tmem + HALF_COLS * h + 32 * k, q_desc + 256 * (2 * h + k),
-                      make_idesc_mx_major(BN, D, 0, 0, 0, 1), bb + A_SF_DS, bb + A_SF_UNIT, (it | h | k) != 0);
+                      make_idesc_mx_major(BN, p.d, 0, 0, 0, 1), bb + A_SF_DS, bb + A_SF_UNIT, (it | h | k) != 0);
         }
       };
       auto wait_tile = [&](uint32_t g) {  // the Q / dO8 / records of tile g have landed
@@ -648,7 +656,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     if (ok) {
       tc_fence_after();
       const float dk_scale = p.softmax_scale * p.q_descale[sc];
-      const int64_t row_off = ((static_cast<int64_t>(blk.b) * p.Hkv + blk.hkv) * p.Nk + key) * D;
+      const int64_t row_off = ((static_cast<int64_t>(blk.b) * p.Hkv + blk.hkv) * p.Nk + key) * p.d;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         const uint32_t src = tmem_base + lane_addr + (which == 0 ? A_DV_COL : A_DK_COL);
@@ -669,7 +677,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0;
           }
-          if (key < p.Nk) {
+          if (key < p.Nk && c * 32 < p.d) {
             uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -801,9 +809,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         const uint64_t k_desc = k_desc_of(j) + 512 * h;
         const uint64_t v_desc = k_desc + (TILE_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k) mma_f8_ss(s_tmem + HALF_COLS * h, q_desc + 2 * k, k_desc + 2 * k, idesc_ss, k != 0);
+        for (int k = 0; k < D / 32; ++k)
+          if (32 * k < p.d) mma_f8_ss(s_tmem + HALF_COLS * h, q_desc + 2 * k, k_desc + 2 * k, idesc_ss, k != 0);
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k) mma_f8_ss(dp_tmem + HALF_COLS * h, do_desc + 2 * k, v_desc + 2 * k, idesc_ss, k != 0);
+        for (int k = 0; k < D / 32; ++k)
+          if (32 * k < p.d) mma_f8_ss(dp_tmem + HALF_COLS * h, do_desc + 2 * k, v_desc + 2 * k, idesc_ss, k != 0);
         tc_commit(s_full(h));
       };
       // dQ += dS K over the same 64 keys: A = dS codes in the dP columns, B = the K tile read MN-major
@@ -813,7 +823,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         for (int k = 0; k < 2; ++k) {
           const uint32_t bb = s_tmem + HALF_COLS * h + 32 * k;  // the block's scale words sit in its own S columns
           mma_mxf8_ts(tmem_base + B_DQ_COL, dp_tmem + HALF_COLS * h + 32 * k, k_desc + 256 * (2 * h + k),
-                      make_idesc_mx_major(BM, D, 0, 0, 0, 1), bb + B_SF_DS, bb + B_SF_UNIT, (j | h | k) != 0);
+                      make_idesc_mx_major(BM, p.d, 0, 0, 0, 1), bb + B_SF_DS, bb + B_SF_UNIT, (j | h | k) != 0);
         }
       };
       ok = ok && mbar_wait(kv_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD);
@@ -908,7 +918,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     if (ok) {
       tc_fence_after();
       const float scale = p.softmax_scale * sk;
-      __nv_bfloat16* dst_row = p.dq + ((static_cast<int64_t>(b) * p.Hq + hq) * p.Nq + row) * D;
+      __nv_bfloat16* dst_row = p.dq + ((static_cast<int64_t>(b) * p.Hq + hq) * p.Nq + row) * p.d;
 #pragma unroll 1
       {
         uint32_t v[32];
@@ -919,7 +929,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0;
         }
-        if (row < p.Nq) {
+        if (row < p.Nq && c * 32 < p.d) {
           uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -943,8 +953,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   }
 }
 
-int make_map4(CUtensorMap* m, const void* base, int n, int h, int b, const int64_t* strides) {
-  const uint64_t dims[4] = {D, static_cast<uint64_t>(n), static_cast<uint64_t>(h), static_cast<uint64_t>(b)};
+// Rows of `d` bytes under boxes of 128: with head dimension 64 TMA fills the upper half of every row with zeros.
+int make_map4(CUtensorMap* m, const void* base, int d, int n, int h, int b, const int64_t* strides) {
+  const uint64_t dims[4] = {static_cast<uint64_t>(d), static_cast<uint64_t>(n), static_cast<uint64_t>(h), static_cast<uint64_t>(b)};
   const uint64_t str[3] = {static_cast<uint64_t>(strides[2]), static_cast<uint64_t>(strides[1]),
                            static_cast<uint64_t>(strides[0])};
   const uint32_t box[4] = {D, 128, 1, 1};
@@ -963,7 +974,7 @@ extern "C" int64_t wk_attn_bwd_fp8_workspace_bytes(int B, int Hq, int Nq) {
 extern "C" int wk_attn_bwd_fp8(const wk_attn_bwd_args* a, void* stream) {
   using namespace wk;
   if (!a) return WK_E_ARG;
-  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Nq <= 0 || a->Nk <= 0 || a->d != D) return WK_E_ARG;
+  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Nq <= 0 || a->Nk <= 0 || (a->d != 128 && a->d != 64)) return WK_E_ARG;
   if (a->Hq % a->Hkv || a->B > 65535 || a->Hq > 65535) return WK_E_ARG;
   if (!a->q || !a->k || !a->v || !a->out || !a->dout || !a->lse || !a->dq || !a->dk || !a->dv) return WK_E_ARG;
   if (!a->q_descale || !a->k_descale || !a->v_descale || !a->workspace) return WK_E_ARG;
@@ -986,7 +997,7 @@ extern "C" int wk_attn_bwd_fp8(const wk_attn_bwd_args* a, void* stream) {
 
   const int nq_pad = (a->Nq + 127) / 128 * 128;
   uint8_t* do8 = static_cast<uint8_t*>(a->workspace);
-  const int64_t do8_bytes = (static_cast<int64_t>(a->B) * a->Hq * a->Nq * D + 255) / 256 * 256;
+  const int64_t do8_bytes = (static_cast<int64_t>(a->B) * a->Hq * a->Nq * a->d + 255) / 256 * 256;
   float* qstat = reinterpret_cast<float*>(do8 + do8_bytes);
 
   PrepParams pp;
@@ -1009,6 +1020,7 @@ extern "C" int wk_attn_bwd_fp8(const wk_attn_bwd_args* a, void* stream) {
   pp.Hkv = a->Hkv;
   pp.Nq = a->Nq;
   pp.nq_pad = nq_pad;
+  pp.d = a->d;
   {
     const int64_t rows = static_cast<int64_t>(a->B) * a->Hq * nq_pad;
     bool wide_loads = aligned16(a->out) && aligned16(a->dout);  // 16-byte loads: rows on 16-byte boundaries
@@ -1023,14 +1035,14 @@ extern "C" int wk_attn_bwd_fp8(const wk_attn_bwd_args* a, void* stream) {
   }
 
   CUtensorMap tq, tk, tv, tdo;
-  int r = make_map4(&tq, a->q, a->Nq, a->Hq, a->B, a->q_strides);
+  int r = make_map4(&tq, a->q, a->d, a->Nq, a->Hq, a->B, a->q_strides);
   if (r) return r;
-  r = make_map4(&tk, a->k, a->Nk, a->Hkv, a->B, a->k_strides);
+  r = make_map4(&tk, a->k, a->d, a->Nk, a->Hkv, a->B, a->k_strides);
   if (r) return r;
-  r = make_map4(&tv, a->v, a->Nk, a->Hkv, a->B, a->v_strides);
+  r = make_map4(&tv, a->v, a->d, a->Nk, a->Hkv, a->B, a->v_strides);
   if (r) return r;
-  const int64_t do_str[3] = {static_cast<int64_t>(a->Hq) * a->Nq * D, static_cast<int64_t>(a->Nq) * D, D};
-  r = make_map4(&tdo, do8, a->Nq, a->Hq, a->B, do_str);
+  const int64_t do_str[3] = {static_cast<int64_t>(a->Hq) * a->Nq * a->d, static_cast<int64_t>(a->Nq) * a->d, a->d};
+  r = make_map4(&tdo, do8, a->d, a->Nq, a->Hq, a->B, do_str);
   if (r) return r;
 
   BwdParams p;
@@ -1047,6 +1059,7 @@ extern "C" int wk_attn_bwd_fp8(const wk_attn_bwd_args* a, void* stream) {
   p.Nq = a->Nq;
   p.Nk = a->Nk;
   p.nq_pad = nq_pad;
+  p.d = a->d;
   p.causal = a->causal;
   p.softmax_scale = a->softmax_scale;
   p.status = status;
