@@ -34,10 +34,15 @@ import math
 import os
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 
 import torch
+
+# the bench's tuner runs write their winners here, not into the user's cache file
+os.environ.setdefault("WARPY_KERNELS_TUNE_CACHE",
+                      os.path.join(tempfile.gettempdir(), f"warpy_kernels_bench_tune_{os.getpid()}.json"))
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
@@ -394,6 +399,11 @@ def make_gemm_mx(dev, world, rank, m, n, k, seed, cta_pair=None):
     a8, sa = wk.quantize_mx(torch.randn(hi - lo, k, device=dev, generator=g).bfloat16())
     b8, sb = wk.quantize_mx(torch.randn(n, k, device=dev,
                                         generator=torch.Generator(device=dev).manual_seed(seed + 1)).bfloat16())
+    tuned = None
+    if cta_pair is None:
+        # untimed set-up, like the reference's tuner: time the two kernels once for this shape; make_gemm then
+        # finds the winner in the tune cache
+        tuned, _ = wk.autotune_gemm(a8, b8, iters=5, verbose=False, a_scale_mx=sa, b_scale_mx=sb)
     launch, out = wk.make_gemm(a8, b8, a_scale_mx=sa, b_scale_mx=sb, cta_pair=cta_pair)
     pipe = Pipeline(dev)
     u8 = lambda t: t.view(torch.uint8)
@@ -420,7 +430,7 @@ def make_gemm_mx(dev, world, rank, m, n, k, seed, cta_pair=None):
     return dict(step=launch, e2e_step=lambda: pipe.run(chunks, first), gather=lambda: shard.gather_rows(out, m),
                 work=2.0 * m * n * k, work_local=2.0 * (hi - lo) * n * k, bound="tensor", dtype="fp8", launches=3,
                 h2d=h2d, d2h=d2h, e2e_chunks=len(chunks), gather_bytes=m * n * 2, keep=(a8, b8, sa, sb, out),
-                shard=f"rows {lo}:{hi} of {m}")
+                shard=f"rows {lo}:{hi} of {m}", tuned=tuned)
 
 
 def make_quant(dev, world, rank, m, k, seed):
@@ -691,6 +701,8 @@ def measure(name, args, dev, dist, world, rank, clocks):
         "gpu_launches": w["launches"] * args.steps,
         "clocks": clk,
     }
+    if w.get("tuned") is not None:
+        res["autotuned"] = w["tuned"]
     if gather_ms:
         res["with_gather"] = {"value": rate(gather_ms), "ms_per_step": gather_ms, "gathered_bytes": w["gather_bytes"],
                               "collective": "one NCCL all_gather_into_tensor per step, after the kernels"}

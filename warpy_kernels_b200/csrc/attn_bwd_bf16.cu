@@ -28,7 +28,7 @@ namespace {
 
 constexpr int BM = 128;  // queries per tile
 constexpr int BN = 128;  // keys per tile
-constexpr int D = 128;  // largest head dimension; with 64 (a run-time parameter) a row is one swizzle span instead of
+constexpr int D = 128;  // largest head dimension; with 64 (the main kernels are instantiated per head dimension) a row is one swizzle span instead of
                         // two: the second box of every tile is not loaded and the products take half the K steps
 constexpr int CHUNK = 64;                        // head-dim elements per 128-byte swizzle span
 constexpr int CHUNK_BYTES = 128 * CHUNK * 2;     // 16 KiB: 128 rows x 128 bytes
@@ -180,6 +180,7 @@ constexpr int A_STAGE_BYTES = 2 * TILE_BYTES + A_STAT_BYTES;
 // resident CTA could only spin in tcgen05.alloc.
 constexpr int A_SMEM_BYTES = 2 * TILE_BYTES + A_STAGES * A_STAGE_BYTES + 1024 + 256;  // 197 KiB: one CTA per SM
 constexpr int A_ST_COL = 0, A_DPT_COL = 128, A_DV_COL = 256, A_DK_COL = 384;
+template <int DH>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -242,7 +243,7 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 
   if (warp == 0) {
     if (lane == 0 && n_iter > 0) {
-      const int chunks = p.d / CHUNK;
+      const int chunks = DH / CHUNK;
       mbar_expect_tx(kv_full, 2 * chunks * CHUNK_BYTES);
       for (int c = 0; c < chunks; ++c) {
         tma_load_4d(k_smem + c * CHUNK_BYTES, &tmap_k, kv_full, c * CHUNK, n0, hkv, b);
@@ -273,7 +274,7 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       // All MMAs come from this one thread, so the products of the next tile overwrite a half's columns only
       // after the products that read its codes (the tensor pipe runs in issue order).
       constexpr uint32_t idesc_ss = make_idesc(1, 1, 0, 0, BN, BM / 2);
-      const uint32_t idesc_ts = make_idesc(1, 1, 0, 1, BN, p.d);  // B read MN-major, N = head dimension
+      const uint32_t idesc_ts = make_idesc(1, 1, 0, 1, BN, DH);  // B read MN-major, N = head dimension
       const uint32_t st_tmem = tmem_base + A_ST_COL;
       const uint32_t dpt_tmem = tmem_base + A_DPT_COL;
       bool ok = mbar_wait(kv_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
@@ -289,12 +290,12 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t off = (k >> 2) * (CHUNK_BYTES >> 4) + 2 * (k & 3);
-          if (16 * k < p.d) mma_f16_ss(st_tmem + HALF_COLS * h, k_desc + off, q_desc + off, idesc_ss, k != 0);
+          if (16 * k < DH) mma_f16_ss(st_tmem + HALF_COLS * h, k_desc + off, q_desc + off, idesc_ss, k != 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t off = (k >> 2) * (CHUNK_BYTES >> 4) + 2 * (k & 3);
-          if (16 * k < p.d) mma_f16_ss(dpt_tmem + HALF_COLS * h, v_desc + off, do_desc + off, idesc_ss, k != 0);
+          if (16 * k < DH) mma_f16_ss(dpt_tmem + HALF_COLS * h, v_desc + off, do_desc + off, idesc_ss, k != 0);
         }
         tc_commit(s_full(h));
       };
@@ -421,7 +422,7 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
     if (ok) {
       tc_fence_after();
       const float dk_scale = p.softmax_scale;
-      const int64_t row_off = ((static_cast<int64_t>(b) * p.Hkv + hkv) * p.Nk + key) * p.d;
+      const int64_t row_off = ((static_cast<int64_t>(b) * p.Hkv + hkv) * p.Nk + key) * DH;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         const uint32_t src = tmem_base + lane_addr + (which == 0 ? A_DV_COL : A_DK_COL);
@@ -437,7 +438,7 @@ attn_bwd_bf16_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0;
           }
-          if (key < p.Nk && c * 32 < p.d) {
+          if (key < p.Nk && c * 32 < DH) {
             uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -470,6 +471,7 @@ constexpr int B_STAGE_BYTES = 2 * TILE_BYTES;  // K tile, V tile
 constexpr int B_SMEM_BYTES = 2 * TILE_BYTES + B_STAGES * B_STAGE_BYTES + 1024 + 256;  // 193 KiB: one CTA per SM
 constexpr int B_S_COL = 0, B_DP_COL = 128, B_DQ_COL = 256;
 
+template <int DH>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -532,7 +534,7 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
-      const int chunks = p.d / CHUNK;
+      const int chunks = DH / CHUNK;
       mbar_expect_tx(q_full, 2 * chunks * CHUNK_BYTES);
       for (int c = 0; c < chunks; ++c) {
         tma_load_4d(q_smem + c * CHUNK_BYTES, &tmap_q, q_full, c * CHUNK, m0, hq, b);
@@ -556,7 +558,7 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       // Key tiles are processed as two halves of 64 keys, as in the dK/dV kernel: the tensor pipe works on one
       // half while the element-wise warps of the other are busy.
       constexpr uint32_t idesc_ss = make_idesc(1, 1, 0, 0, BM, BN / 2);
-      const uint32_t idesc_ts = make_idesc(1, 1, 0, 1, BM, p.d);  // B read MN-major, N = head dimension
+      const uint32_t idesc_ts = make_idesc(1, 1, 0, 1, BM, DH);  // B read MN-major, N = head dimension
       const uint32_t s_tmem = tmem_base + B_S_COL;
       const uint32_t dp_tmem = tmem_base + B_DP_COL;
       bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
@@ -571,12 +573,12 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t off = (k >> 2) * (CHUNK_BYTES >> 4) + 2 * (k & 3);
-          if (16 * k < p.d) mma_f16_ss(s_tmem + HALF_COLS * h, q_desc + off, k_desc + off, idesc_ss, k != 0);
+          if (16 * k < DH) mma_f16_ss(s_tmem + HALF_COLS * h, q_desc + off, k_desc + off, idesc_ss, k != 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t off = (k >> 2) * (CHUNK_BYTES >> 4) + 2 * (k & 3);
-          if (16 * k < p.d) mma_f16_ss(dp_tmem + HALF_COLS * h, do_desc + off, v_desc + off, idesc_ss, k != 0);
+          if (16 * k < DH) mma_f16_ss(dp_tmem + HALF_COLS * h, do_desc + off, v_desc + off, idesc_ss, k != 0);
         }
         tc_commit(s_full(h));
       };
@@ -672,7 +674,7 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     if (ok) {
       tc_fence_after();
       const float scale = p.softmax_scale;
-      __nv_bfloat16* dst_row = p.dq + ((static_cast<int64_t>(b) * p.Hq + hq) * p.Nq + row) * p.d;
+      __nv_bfloat16* dst_row = p.dq + ((static_cast<int64_t>(b) * p.Hq + hq) * p.Nq + row) * DH;
 #pragma unroll 1
       {
         uint32_t v[32];
@@ -683,7 +685,7 @@ attn_bwd_bf16_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0;
         }
-        if (row < p.Nq && c * 32 < p.d) {
+        if (row < p.Nq && c * 32 < DH) {
           uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -808,17 +810,19 @@ extern "C" int wk_attn_bwd_bf16(const wk_attn_bwd_args* a, void* stream) {
   p.softmax_scale = a->softmax_scale;
   p.status = status;
 
-  if (allow_smem(reinterpret_cast<const void*>(attn_bwd_bf16_dkdv_kernel), A_SMEM_BYTES)) return WK_E_CUDA;
-  if (allow_smem(reinterpret_cast<const void*>(attn_bwd_bf16_dq_kernel), B_SMEM_BYTES)) return WK_E_CUDA;
+  if (allow_smem((a->d == 64 ? reinterpret_cast<const void*>(attn_bwd_bf16_dkdv_kernel<64>) : reinterpret_cast<const void*>(attn_bwd_bf16_dkdv_kernel<128>)), A_SMEM_BYTES)) return WK_E_CUDA;
+  if (allow_smem((a->d == 64 ? reinterpret_cast<const void*>(attn_bwd_bf16_dq_kernel<64>) : reinterpret_cast<const void*>(attn_bwd_bf16_dq_kernel<128>)), B_SMEM_BYTES)) return WK_E_CUDA;
   {
     dim3 grid((a->Nk + BN - 1) / BN, a->Hkv, a->B);
-    attn_bwd_bf16_dkdv_kernel<<<grid, THREADS, A_SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
-    if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+    void* args[] = {&tq, &tk, &tv, &tdo, &p};
+    const void* kernel = a->d == 64 ? reinterpret_cast<const void*>(attn_bwd_bf16_dkdv_kernel<64>) : reinterpret_cast<const void*>(attn_bwd_bf16_dkdv_kernel<128>);
+    if (cudaLaunchKernel(kernel, grid, dim3(THREADS), args, A_SMEM_BYTES, st) != cudaSuccess) return WK_E_CUDA;
   }
   {
     dim3 grid((a->Nq + BM - 1) / BM, a->Hq, a->B);
-    attn_bwd_bf16_dq_kernel<<<grid, THREADS, B_SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
-    if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+    void* args[] = {&tq, &tk, &tv, &tdo, &p};
+    const void* kernel = a->d == 64 ? reinterpret_cast<const void*>(attn_bwd_bf16_dq_kernel<64>) : reinterpret_cast<const void*>(attn_bwd_bf16_dq_kernel<128>);
+    if (cudaLaunchKernel(kernel, grid, dim3(THREADS), args, B_SMEM_BYTES, st) != cudaSuccess) return WK_E_CUDA;
   }
   return 0;
 }

@@ -1,7 +1,7 @@
 // FP8 (e4m3) flash-attention backward for sm_100a, head dimension 128 or 64 (64: tiles keep their 128-byte rows in
 // shared memory with the upper half zero -- the tensor maps describe 64-byte rows under 128-byte boxes and TMA fills
 // in the rest -- while the products over the head dimension take two K steps instead of four and dQ / dK / dV are
-// 64 columns wide; `d` is a run-time parameter of the kernels).
+// 64 columns wide; the two main kernels are instantiated per head dimension, the prep kernels read it at run time).
 //
 // Gradients with respect to the dequantised q, k, v (q = q_descale . q8 and so on):
 //   S = alpha . q k^T,  P = softmax(S) = 2^(S . log2e - L)   (L: the forward's base-2 lse)
@@ -295,6 +295,7 @@ constexpr int A_ST_COL = 0, A_DPT_COL = 128, A_DV_COL = 256, A_DK_COL = 384;
 // Inside the 32 S^T columns of a block, once its thread has read them: codes in 0..7, then the scale words
 constexpr int A_SF_P = 8, A_SF_UNIT = 12, A_SF_DS = 16;
 
+template <int DH>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -460,10 +461,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const uint64_t do_desc = q_desc + (TILE_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < D / 32; ++k)
-          if (32 * k < p.d) mma_f8_ss(st_tmem + HALF_COLS * h, k_desc + 2 * k, q_desc + 2 * k, idesc_ss, k != 0);
+          if (32 * k < DH) mma_f8_ss(st_tmem + HALF_COLS * h, k_desc + 2 * k, q_desc + 2 * k, idesc_ss, k != 0);
 #pragma unroll
         for (int k = 0; k < D / 32; ++k)
-          if (32 * k < p.d) mma_f8_ss(dpt_tmem + HALF_COLS * h, v_desc + 2 * k, do_desc + 2 * k, idesc_ss, k != 0);
+          if (32 * k < DH) mma_f8_ss(dpt_tmem + HALF_COLS * h, v_desc + 2 * k, do_desc + 2 * k, idesc_ss, k != 0);
         tc_commit(s_full(h));
       };
       // dV += (P g)^T dO8 and dK += dS^T Q8 over the same 64 queries (`it`: the tile's number inside its key block).
@@ -475,14 +476,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const uint32_t bb = st_tmem + HALF_COLS * h + 32 * k;
-          mma_mxf8_ts(tmem_base + A_DV_COL, bb, do_desc + 256 * (2 * h + k), make_idesc_mx_major(BN, p.d, 0, 0, 0, 1),
+          mma_mxf8_ts(tmem_base + A_DV_COL, bb, do_desc + 256 * (2 * h + k), make_idesc_mx_major(BN, DH, 0, 0, 0, 1),
                       bb + A_SF_P, bb + A_SF_UNIT, (it | h | k) != 0);
         }
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const uint32_t bb = st_tmem + HALF_COLS * h + 32 * k;
           mma_mxf8_ts(tmem_base + A_DK_COL, dpt_tmem + HALF_COLS * h + 32 * k, q_desc + 256 * (2 * h + k),
-                      make_idesc_mx_major(BN, p.d, 0, 0, 0, 1), bb + A_SF_DS, bb + A_SF_UNIT, (it | h | k) != 0);
+                      make_idesc_mx_major(BN, DH, 0, 0, 0, 1), bb + A_SF_DS, bb + A_SF_UNIT, (it | h | k) != 0);
         }
       };
       auto wait_tile = [&](uint32_t g) {  // the Q / dO8 / records of tile g have landed
@@ -656,7 +657,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     if (ok) {
       tc_fence_after();
       const float dk_scale = p.softmax_scale * p.q_descale[sc];
-      const int64_t row_off = ((static_cast<int64_t>(blk.b) * p.Hkv + blk.hkv) * p.Nk + key) * p.d;
+      const int64_t row_off = ((static_cast<int64_t>(blk.b) * p.Hkv + blk.hkv) * p.Nk + key) * DH;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         const uint32_t src = tmem_base + lane_addr + (which == 0 ? A_DV_COL : A_DK_COL);
@@ -677,7 +678,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0;
           }
-          if (key < p.Nk && c * 32 < p.d) {
+          if (key < p.Nk && c * 32 < DH) {
             uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -714,6 +715,7 @@ constexpr int B_SMEM_BYTES = B_SMEM_NEED > 120 * 1024 ? B_SMEM_NEED : 120 * 1024
 constexpr int B_S_COL = 0, B_DP_COL = 128, B_DQ_COL = 256;
 constexpr int B_SF_DS = 8, B_SF_UNIT = 12;
 
+template <int DH>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -810,10 +812,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         const uint64_t v_desc = k_desc + (TILE_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < D / 32; ++k)
-          if (32 * k < p.d) mma_f8_ss(s_tmem + HALF_COLS * h, q_desc + 2 * k, k_desc + 2 * k, idesc_ss, k != 0);
+          if (32 * k < DH) mma_f8_ss(s_tmem + HALF_COLS * h, q_desc + 2 * k, k_desc + 2 * k, idesc_ss, k != 0);
 #pragma unroll
         for (int k = 0; k < D / 32; ++k)
-          if (32 * k < p.d) mma_f8_ss(dp_tmem + HALF_COLS * h, do_desc + 2 * k, v_desc + 2 * k, idesc_ss, k != 0);
+          if (32 * k < DH) mma_f8_ss(dp_tmem + HALF_COLS * h, do_desc + 2 * k, v_desc + 2 * k, idesc_ss, k != 0);
         tc_commit(s_full(h));
       };
       // dQ += dS K over the same 64 keys: A = dS codes in the dP columns, B = the K tile read MN-major
@@ -823,7 +825,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         for (int k = 0; k < 2; ++k) {
           const uint32_t bb = s_tmem + HALF_COLS * h + 32 * k;  // the block's scale words sit in its own S columns
           mma_mxf8_ts(tmem_base + B_DQ_COL, dp_tmem + HALF_COLS * h + 32 * k, k_desc + 256 * (2 * h + k),
-                      make_idesc_mx_major(BM, p.d, 0, 0, 0, 1), bb + B_SF_DS, bb + B_SF_UNIT, (j | h | k) != 0);
+                      make_idesc_mx_major(BM, DH, 0, 0, 0, 1), bb + B_SF_DS, bb + B_SF_UNIT, (j | h | k) != 0);
         }
       };
       ok = ok && mbar_wait(kv_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD);
@@ -918,7 +920,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     if (ok) {
       tc_fence_after();
       const float scale = p.softmax_scale * sk;
-      __nv_bfloat16* dst_row = p.dq + ((static_cast<int64_t>(b) * p.Hq + hq) * p.Nq + row) * p.d;
+      __nv_bfloat16* dst_row = p.dq + ((static_cast<int64_t>(b) * p.Hq + hq) * p.Nq + row) * DH;
 #pragma unroll 1
       {
         uint32_t v[32];
@@ -929,7 +931,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0;
         }
-        if (row < p.Nq && c * 32 < p.d) {
+        if (row < p.Nq && c * 32 < DH) {
           uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -1064,17 +1066,19 @@ extern "C" int wk_attn_bwd_fp8(const wk_attn_bwd_args* a, void* stream) {
   p.softmax_scale = a->softmax_scale;
   p.status = status;
 
-  if (allow_smem(reinterpret_cast<const void*>(attn_bwd_dkdv_kernel), A_SMEM_BYTES)) return WK_E_CUDA;
-  if (allow_smem(reinterpret_cast<const void*>(attn_bwd_dq_kernel), B_SMEM_BYTES)) return WK_E_CUDA;
+  if (allow_smem((a->d == 64 ? reinterpret_cast<const void*>(attn_bwd_dkdv_kernel<64>) : reinterpret_cast<const void*>(attn_bwd_dkdv_kernel<128>)), A_SMEM_BYTES)) return WK_E_CUDA;
+  if (allow_smem((a->d == 64 ? reinterpret_cast<const void*>(attn_bwd_dq_kernel<64>) : reinterpret_cast<const void*>(attn_bwd_dq_kernel<128>)), B_SMEM_BYTES)) return WK_E_CUDA;
   {
     dim3 grid((a->Nk + BN - 1) / BN, a->Hkv, a->B);
-    attn_bwd_dkdv_kernel<<<grid, THREADS, A_SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
-    if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+    void* args[] = {&tq, &tk, &tv, &tdo, &p};
+    const void* kernel = a->d == 64 ? reinterpret_cast<const void*>(attn_bwd_dkdv_kernel<64>) : reinterpret_cast<const void*>(attn_bwd_dkdv_kernel<128>);
+    if (cudaLaunchKernel(kernel, grid, dim3(THREADS), args, A_SMEM_BYTES, st) != cudaSuccess) return WK_E_CUDA;
   }
   {
     dim3 grid((a->Nq + BM - 1) / BM, a->Hq, a->B);
-    attn_bwd_dq_kernel<<<grid, THREADS, B_SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
-    if (cudaGetLastError() != cudaSuccess) return WK_E_CUDA;
+    void* args[] = {&tq, &tk, &tv, &tdo, &p};
+    const void* kernel = a->d == 64 ? reinterpret_cast<const void*>(attn_bwd_dq_kernel<64>) : reinterpret_cast<const void*>(attn_bwd_dq_kernel<128>);
+    if (cudaLaunchKernel(kernel, grid, dim3(THREADS), args, B_SMEM_BYTES, st) != cudaSuccess) return WK_E_CUDA;
   }
   return 0;
 }
