@@ -22,7 +22,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("WARPY_REFERENCE", os.path.join(os.sep, "root", "reference"))
+REF = os.environ.get("WARPY_REFERENCE")  # checkout of the reference repository (tan0210/warpy-kernels)
+if not REF or not os.path.isdir(os.path.join(REF, "tests")):
+    raise SystemExit("set WARPY_REFERENCE to a checkout of the reference repository (its tests/fixtures.py is imported)")
 
 
 def _load_reference_tests():

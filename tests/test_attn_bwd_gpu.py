@@ -1,6 +1,6 @@
 """GPU: FP8 attention backward against the fp32 oracle (autograd through the reference's attention).
 
-Tolerances: north star (cosine >= 0.995 for dq, dk, dv) and the reference's gate (rel-L2 <= 8e-2,
+Tolerances: this library's target (cosine >= 0.995 for dq, dk, dv) and the reference's gate (rel-L2 <= 8e-2,
 ``tests/attn/test_grad.py:19``).
 """
 

@@ -1,6 +1,6 @@
 """GPU: FP8 attention forward against the fp32 oracle.
 
-Tolerances: the north-star gates (cosine >= 0.999, max-abs <= 2e-2) and the reference's own
+Tolerances: this library's target gates (cosine >= 0.999, max-abs <= 2e-2) and the reference's own
 (``tests/attn/test_fwd.py:21``: out rel-L2 <= 6e-2, lse max-abs <= 5e-2).
 """
 

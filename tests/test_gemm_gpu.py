@@ -22,7 +22,7 @@ def test_bf16_matches_fp32_product(cuda, shape):
     out = gemm(a, b)
     assert out.dtype == torch.bfloat16 and out.shape == (m, n)
     want = R.gemm_reference(a.cpu(), b.cpu())
-    # north-star tolerance 1e-2 (relative Frobenius vs fp32 accumulation); reference's matches_cublas gate is 1e-3
+    # target tolerance 1e-2 (relative Frobenius vs fp32 accumulation); reference's matches_cublas gate is 1e-3
     # against the bf16-rounded product
     assert R.rel_l2(out.cpu(), want) <= 1e-2
     assert R.rel_l2(out.cpu(), want.bfloat16()) <= 1e-3

@@ -10,8 +10,8 @@
 //
 // One CTA of 512 threads per flagged block: four threads per query row, each owning 32 of the 128 head-dim
 // elements (with head dimension 64 two of the four hold zeros and only join the reductions); K and V pass through
-// shared memory 64 keys at a time.  A launch covers every block of the call with a
-// grid-stride loop over the flags, so with nothing flagged it costs one small launch that reads the flags and leaves.
+// shared memory 64 keys at a time.  A launch covers every block of the call: each CTA reads its share of the
+// flags in one go, so with nothing flagged it costs one small launch that reads the flags and leaves.
 #include <math.h>
 
 #include "attn_fwd_redo.h"
@@ -89,7 +89,19 @@ __global__ void __launch_bounds__(R_THREADS) attn_fwd_redo_kernel(const RedoPara
   const int num_m = (p.Nq + R_BM - 1) / R_BM;
   const int total = p.B * p.Hq * num_m;
 
-  for (int blk = blockIdx.x; blk < total; blk += gridDim.x) {
+  // launched with programmatic stream serialisation: the launch itself overlaps the end of the forward kernel, and
+  // the flags are read only once that kernel has completed
+  pdl_wait();
+  // Every CTA owns a contiguous range of flags and looks at all of them at once, one per thread: with nothing
+  // flagged (the normal case) the kernel is one load per thread and a barrier.
+  const int per_cta = (total + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int first = static_cast<int>(blockIdx.x) * per_cta;
+  const int last = min(total, first + per_cta);
+  int any = 0;
+  for (int i = first + tid; i < last; i += R_THREADS) any |= p.flags[i];
+  if (!__syncthreads_or(any)) return;
+
+  for (int blk = first; blk < last; ++blk) {
     const int flagged = p.flags[blk];  // the same word for every thread: the branch is uniform
     if (!flagged) continue;
     __syncthreads();  // everybody has read the flag
@@ -253,12 +265,20 @@ int launch_attn_fwd_redo(const wk_attn_fwd_args* a, bool bf16, int* flags, cudaS
   if (blocks > 0x7fffffff) return WK_E_ARG;
   int sms = sm_count();
   if (sms <= 0) return WK_E_CUDA;
-  const int grid = static_cast<int>(blocks < 4ll * sms ? blocks : 4ll * sms);
-  if (bf16)
-    attn_fwd_redo_kernel<true><<<grid, R_THREADS, 0, st>>>(p);
-  else
-    attn_fwd_redo_kernel<false><<<grid, R_THREADS, 0, st>>>(p);
-  return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
+  const int grid = static_cast<int>(blocks < sms ? blocks : sms);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(R_THREADS);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = bf16 ? cudaLaunchKernelEx(&cfg, attn_fwd_redo_kernel<true>, p)
+                             : cudaLaunchKernelEx(&cfg, attn_fwd_redo_kernel<false>, p);
+  return e == cudaSuccess ? 0 : WK_E_CUDA;
 }
 
 }  // namespace wk
