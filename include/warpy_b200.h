@@ -145,10 +145,22 @@ typedef struct {
   int32_t cta_pair;     /* kernel choice as in wk_gemm16_args: 0 the library's, 1 CTA pairs (tcgen05 cta_group::2, one
                            256 x 256 tile per two SMs), 2 single CTAs; bit-identical results.  wk_gemm_mxfp8_noalloc
                            always runs single CTAs. */
+  int32_t a_scale_tiled; /* 1: a_scale_mx is not the row-major [M, K/32] tensor but the output of wk_tile_mx_scales
+                            for it (16-byte aligned): the layout the kernels read, made once for scales that do not
+                            change from call to call (weights).  0: row-major, re-tiled into the workspace per call. */
+  int32_t b_scale_tiled; /* the same for b_scale_mx.  With both set the workspace may be NULL. */
 } wk_gemm_mx_args;
 
 int64_t wk_gemm_mxfp8_workspace_bytes(int m, int n, int k);
 int wk_gemm_mxfp8(const wk_gemm_mx_args* args, void* stream);
+
+/* Re-tiles MX scale bytes for wk_gemm_mxfp8: s [rows, k/32] ue8m0 row-major (NULL: unit scales) ->
+ * dst, wk_mx_scales_tiled_bytes(rows, k) bytes, 16-byte aligned: one 512-byte atom per 128 rows and 128 K
+ * elements (byte (row % 32) * 16 + (row / 32 % 4) * 4 + kblock % 4), atoms ordered [row block][K block], which is
+ * how tcgen05.mma reads block scales from tensor memory.  rows % 128 == 0, k % 128 == 0.  No counterpart in the
+ * reference, whose mma.sync kernels read the row-major tensor (warpy_kernels/gemm/sm120.py:121-146). */
+int64_t wk_mx_scales_tiled_bytes(int rows, int k);
+int wk_tile_mx_scales(const void* s, int rows, int k, void* dst, void* stream);
 
 /* MXFP8 GEMM for callers that cannot allocate device memory.  No counterpart in the
  * reference (its host API allocates its workspaces with torch on every make_gemm).

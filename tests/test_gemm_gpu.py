@@ -518,3 +518,47 @@ def test_autotune_gemm_times_both_kernels_and_stores_the_winner(cuda, kind, tmp_
     key = f"{'gemm_fp8' if kind == 'fp8' else 'gemm'}|m={m}|n={n}|k={k}|sm100"
     assert json.load(open(tmp_path / "tune.json")) == {key: best}
     assert torch.equal(gemm(a, b), gemm(a, b, cta_pair=best["cta_pair"]))  # the cache entry is what runs by default
+
+
+def test_mx_scales_tiled_once_through_the_c_abi(cuda):
+    """``wk_tile_mx_scales`` + ``a_scale_tiled`` / ``b_scale_tiled``: scale tensors that do not change between calls
+    (weights) are re-tiled once; with both tiled the GEMM needs no workspace and gives the same bits, on both kernels.
+    ``make_gemm`` does this for ``b_scale_mx``: a prepared launch keeps the scales of ``b`` it was made with."""
+    import ctypes
+
+    from warpy_kernels import gemm, make_gemm
+    from warpy_kernels_b200 import _lib
+    from warpy_kernels_b200.gemm.api import _MxArgs
+
+    lib = _lib.lib()
+    m, n, k = 384, 640, 512
+    g = torch.Generator(device=cuda).manual_seed(4)
+    a = torch.randn(m, k, device=cuda, generator=g).to(FP8)
+    b = torch.randn(n, k, device=cuda, generator=g).to(FP8)
+    sa = torch.randint(118, 136, (m, k // 32), device=cuda, generator=g, dtype=torch.uint8)
+    sb = torch.randint(120, 134, (n, k // 32), device=cuda, generator=g, dtype=torch.uint8)
+    want = gemm(a, b, a_scale_mx=sa, b_scale_mx=sb)
+    assert lib.wk_mx_scales_tiled_bytes(m, k) == m * k // 32
+    ta = torch.empty(lib.wk_mx_scales_tiled_bytes(m, k), dtype=torch.uint8, device=cuda)
+    tb = torch.empty(lib.wk_mx_scales_tiled_bytes(n, k), dtype=torch.uint8, device=cuda)
+    stream = _lib.stream_ptr(cuda)
+    assert lib.wk_tile_mx_scales(sa.data_ptr(), m, k, ta.data_ptr(), stream) == 0
+    assert lib.wk_tile_mx_scales(sb.data_ptr(), n, k, tb.data_ptr(), stream) == 0
+    for pair in (2, 1):
+        got = torch.full((m, n), -3.0, dtype=torch.bfloat16, device=cuda)
+        x = _MxArgs()
+        x.a, x.b, x.out = a.data_ptr(), b.data_ptr(), got.data_ptr()
+        x.a_scale_mx, x.b_scale_mx, x.a_scale_tiled, x.b_scale_tiled = ta.data_ptr(), tb.data_ptr(), 1, 1
+        x.workspace, x.workspace_bytes = None, 0
+        x.m, x.n, x.k, x.cta_pair = m, n, k, pair
+        assert lib.wk_gemm_mxfp8(ctypes.byref(x), stream) == 0
+        assert torch.equal(got, want), pair
+    x.a_scale_tiled = 0  # a row-major tensor again, but no workspace to re-tile it into
+    assert lib.wk_gemm_mxfp8(ctypes.byref(x), stream) == -1
+    # a prepared launch re-reads a's scales at every launch and keeps b's
+    sa2, sb2 = sa.clone(), sb.clone()
+    launch, out = make_gemm(a, b, a_scale_mx=sa2, b_scale_mx=sb2)
+    sa2 += 1
+    sb2 += 1
+    launch()
+    assert torch.equal(out.float(), want.float() * 2)

@@ -35,6 +35,8 @@ SIGNATURES = {
     "wk_attn_bwd_bf16": (_i32, [_ptr, _ptr]),
     "wk_gemm_mxfp8_workspace_bytes": (_i64, [_i32, _i32, _i32]),
     "wk_gemm_mxfp8": (_i32, [_ptr, _ptr]),
+    "wk_mx_scales_tiled_bytes": (_i64, [_i32, _i32]),
+    "wk_tile_mx_scales": (_i32, [_ptr, _i32, _i32, _ptr, _ptr]),
     "wk_gemm_mxfp8_noalloc": (_i32, [_ptr, _ptr]),
     "wk_gemm_mxfp8_noalloc_max_bytes": (_i64, []),
     "wk_gemm_mxfp8_noalloc_status": (_i32, []),

@@ -119,6 +119,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // The launch may overlap the end of the kernel that re-tiles the scales (programmatic stream serialisation):
+      // nothing is loaded before that kernel has completed.
+      pdl_wait();
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         const TileCoord tc = tile_coord(tile, num_m, num_n, p.group_m);
         const int nb_atoms = min(2, n_atoms_total - tc.n_blk * 2);  // 1 on a 128-wide edge tile
@@ -280,6 +283,20 @@ extern "C" int64_t wk_gemm_mxfp8_workspace_bytes(int m, int n, int k) {
   return (static_cast<int64_t>(m) + n) * (k / 32) + 32;
 }
 
+extern "C" int64_t wk_mx_scales_tiled_bytes(int rows, int k) {
+  if (rows < 0 || k < 0 || rows % 128 || k % 128) return WK_E_ARG;
+  return static_cast<int64_t>(rows) * (k / 32);
+}
+
+extern "C" int wk_tile_mx_scales(const void* s, int rows, int k, void* dst, void* stream) {
+  using namespace wk;
+  if (rows < 0 || k < 0 || rows % 128 || k % 128 || !dst || !aligned16(dst)) return WK_E_ARG;
+  if (s && (reinterpret_cast<uintptr_t>(s) & 3)) return WK_E_ARG;
+  if (rows == 0 || k == 0) return 0;
+  if (int unsupported = require_sm100()) return unsupported;
+  return swizzle(s, dst, rows, k, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
   using namespace wk;
   if (!a) return WK_E_ARG;
@@ -287,26 +304,41 @@ extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
   if (m < 0 || n < 0 || k < 0 || m % BM || n % 128 || k % BK) return WK_E_ARG;
   if (m == 0 || n == 0) return 0;
   if (k == 0) return WK_E_ARG;
-  if (!a->a || !a->b || !a->out || !a->workspace) return WK_E_ARG;
+  if (!a->a || !a->b || !a->out) return WK_E_ARG;
   if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->out) || !aligned16(a->workspace)) return WK_E_ARG;
+  const bool a_tiled = a->a_scale_tiled != 0, b_tiled = a->b_scale_tiled != 0;
+  if (!a->workspace && !(a_tiled && b_tiled)) return WK_E_ARG;  // scratch for whatever is still row-major
+  if (a_tiled && (!a->a_scale_mx || !aligned16(a->a_scale_mx))) return WK_E_ARG;
+  if (b_tiled && (!a->b_scale_mx || !aligned16(a->b_scale_mx))) return WK_E_ARG;
   if (a->a_scale_mx && (reinterpret_cast<uintptr_t>(a->a_scale_mx) & 3)) return WK_E_ARG;
   if (a->b_scale_mx && (reinterpret_cast<uintptr_t>(a->b_scale_mx) & 3)) return WK_E_ARG;
   if ((a->q_mx == nullptr) != (a->s_mx == nullptr)) return WK_E_ARG;
   if (a->q_mx && !aligned16(a->q_mx)) return WK_E_ARG;
   if (!epilogue_args_ok(a)) return WK_E_ARG;
   if (a->cta_pair < 0 || a->cta_pair > 2) return WK_E_ARG;
-  if (a->workspace_bytes < wk_gemm_mxfp8_workspace_bytes(m, n, k)) return WK_E_ARG;
+  if (a->workspace && a->workspace_bytes < wk_gemm_mxfp8_workspace_bytes(m, n, k)) return WK_E_ARG;
   if (int unsupported = require_sm100()) return unsupported;
   int* status = status_word();
   if (!status) return WK_E_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  uint8_t* sfa = static_cast<uint8_t*>(a->workspace);
-  uint8_t* sfb = sfa + ((static_cast<int64_t>(m) * (k / 32) + 15) / 16) * 16;
-  int r = swizzle(a->a_scale_mx, sfa, m, k, st);
-  if (r) return r;
-  r = swizzle(a->b_scale_mx, sfb, n, k, st);
-  if (r) return r;
+  // scale tensors the caller has already tiled (wk_tile_mx_scales) are read where they are; the others are
+  // re-tiled into the workspace first
+  const uint8_t* sfa = static_cast<const uint8_t*>(a->a_scale_mx);
+  const uint8_t* sfb = static_cast<const uint8_t*>(a->b_scale_mx);
+  int r = 0;
+  if (!a_tiled) {
+    uint8_t* dst = static_cast<uint8_t*>(a->workspace);
+    r = swizzle(a->a_scale_mx, dst, m, k, st);
+    if (r) return r;
+    sfa = dst;
+  }
+  if (!b_tiled) {
+    uint8_t* dst = static_cast<uint8_t*>(a->workspace) + ((static_cast<int64_t>(m) * (k / 32) + 15) / 16) * 16;
+    r = swizzle(a->b_scale_mx, dst, n, k, st);
+    if (r) return r;
+    sfb = dst;
+  }
 
   GemmParams p;
   p.out = a->out;
@@ -318,7 +350,7 @@ extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
   p.K = k;
   p.group_m = 8;
   p.status = status;
-  if (a->cta_pair == 1) return launch_gemm_mxfp8_2sm(a->a, a->b, p, st);
+  if (a->cta_pair == 1) return launch_gemm_mxfp8_2sm(a->a, a->b, p, st, !(a_tiled && b_tiled));
 
   CUtensorMap ta, tb;
   {
@@ -340,8 +372,18 @@ extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
   const int sms = sm_count();
   if (sms <= 0) return WK_E_CUDA;
   const int grid = num_tiles < sms ? num_tiles : sms;
-  gemm_mxfp8_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(ta, tb, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
+  // after a re-tiling launch: start under its tail (the producer waits for it before the first load)
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = (a_tiled && b_tiled) ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, gemm_mxfp8_kernel, ta, tb, p) == cudaSuccess ? 0 : WK_E_CUDA;
 }
 
 // ---------------------------------------------------------------------------
@@ -399,6 +441,8 @@ extern "C" int wk_gemm_mxfp8_noalloc(const wk_gemm_mx_args* a, void* stream) {
   if ((a->q_mx == nullptr) != (a->s_mx == nullptr)) return WK_E_ARG;
   if (a->q_mx && !aligned16(a->q_mx)) return WK_E_ARG;
   if (!epilogue_args_ok(a)) return WK_E_ARG;
+  // scales that are already tiled need no scratch at all: such a caller uses wk_gemm_mxfp8 with a NULL workspace
+  if (a->a_scale_tiled || a->b_scale_tiled) return WK_E_ARG;
   // the fixed array bounds the problem size: (M + N) * K / 32 scale bytes must fit
   if (wk_gemm_mxfp8_workspace_bytes(m, n, k) > kNoAllocScratchBytes) return WK_E_TOO_LARGE;
   int dev = 0;

@@ -32,7 +32,8 @@ struct GemmParams {
   int* status;
 };
 
-// the CTA-pair kernel; a and b as the caller passed them, p filled in
-int launch_gemm_mxfp8_2sm(const void* a, const void* b, const GemmParams& p, cudaStream_t stream);
+// the CTA-pair kernel; a and b as the caller passed them, p filled in; `after_retile`: a kernel that re-tiles scales
+// was just enqueued, and this launch may start under its tail
+int launch_gemm_mxfp8_2sm(const void* a, const void* b, const GemmParams& p, cudaStream_t stream, bool after_retile);
 
 }  // namespace wk

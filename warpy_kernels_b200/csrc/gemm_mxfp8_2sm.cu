@@ -120,6 +120,7 @@ gemm_mxfp8_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      pdl_wait();  // the launch may overlap the end of the kernel that re-tiles the scales: load nothing before it is done
       for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
         const TileCoord tc = tile_coord(tile, num_m, num_n, p.group_m);
         const int a_rows = tc.m_blk * 2 + rank;  // in units of 128 rows
@@ -266,7 +267,7 @@ gemm_mxfp8_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
 // Launches the CTA-pair kernel.  The caller has checked the arguments (M and N multiples of 128, K of 128) and
 // re-tiled the scale factors into p.sfa / p.sfb.
-int launch_gemm_mxfp8_2sm(const void* a, const void* b, const GemmParams& p, cudaStream_t stream) {
+int launch_gemm_mxfp8_2sm(const void* a, const void* b, const GemmParams& p, cudaStream_t stream, bool after_retile) {
   CUtensorMap ta, tb, tsa, tsb;
   const uint32_t box[2] = {Q_BK, 128};
   {
@@ -303,8 +304,17 @@ int launch_gemm_mxfp8_2sm(const void* a, const void* b, const GemmParams& p, cud
   const int num_tiles = ((p.M + Q_BM - 1) / Q_BM) * ((p.N + Q_BN - 1) / Q_BN);
   const int max_pairs = sms / 2;
   const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
-  gemm_mxfp8_2sm_kernel<<<2 * pairs, Q_THREADS, Q_SMEM_BYTES, stream>>>(ta, tb, tsa, tsb, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(Q_THREADS);
+  cfg.dynamicSmemBytes = Q_SMEM_BYTES;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = after_retile ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, gemm_mxfp8_2sm_kernel, ta, tb, tsa, tsb, p) == cudaSuccess ? 0 : WK_E_CUDA;
 }
 
 }  // namespace wk

@@ -34,6 +34,7 @@ class _MxArgs(ctypes.Structure):
         ("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32),
         *_EPILOGUE_FIELDS, ("out_f16", ctypes.c_int32),
         ("pre_out", ctypes.c_void_p), ("pre_in", ctypes.c_void_p), ("cta_pair", ctypes.c_int32),
+        ("a_scale_tiled", ctypes.c_int32), ("b_scale_tiled", ctypes.c_int32),
     ]
 
 
@@ -134,7 +135,9 @@ def make_gemm(
             256 x 256 tiles fill the GPU about as well as 128 x 256 ones, for fp8 inputs single CTAs. The results
             are bit-identical either way.
         b_scale_mx: ``[N, K / 32]`` uint8 ue8m0 scales of ``b``. Not in the reference (which scales only ``a``);
-            ``None`` gives the reference's behaviour.
+            ``None`` gives the reference's behaviour. ``b`` plays the weights: its scales are re-tiled into the
+            kernels' layout once, when the launch is prepared, so ``launch()`` does not see later in-place changes
+            to this tensor (those of ``a_scale_mx`` are re-read at every launch).
 
     Returns:
         ``(launch, out)``, or ``(launch, out, pre)`` if ``act="gelu"``, where ``pre`` is ``None`` unless
@@ -240,17 +243,24 @@ def make_gemm(
 
     else:
         ws_bytes = lib.wk_gemm_mxfp8_workspace_bytes(m, n, k)
-        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)  # re-tiled scale factors
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)  # the scales of a, re-tiled at every launch
+        # b plays the weights: its scales (unit scales if none are given) are re-tiled once, here, into the layout the
+        # kernels read; like every make_* closure, launch() then does not see later in-place changes to b_scale_mx
+        b_tiled = torch.empty(lib.wk_mx_scales_tiled_bytes(n, k), dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(lib.wk_tile_mx_scales(ptr(b_scale_mx), n, k, b_tiled.data_ptr(), _lib.stream_ptr(dev)),
+                       "gemm (fp8 scales)")
         args = _MxArgs()
         args.a, args.b, args.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
-        args.a_scale_mx, args.b_scale_mx = ptr(a_scale_mx), ptr(b_scale_mx)
+        args.a_scale_mx, args.b_scale_mx = ptr(a_scale_mx), b_tiled.data_ptr()
+        args.a_scale_tiled, args.b_scale_tiled = 0, 1
         args.q_mx, args.s_mx = ptr(q_mx), ptr(s_mx)
         args.workspace, args.workspace_bytes = workspace.data_ptr(), ws_bytes
         args.m, args.n, args.k = m, n, k
         args.out_f16 = int(odt == torch.float16)
         args.cta_pair = 0 if cta_pair is None else 1 if cta_pair else 2
         fill_epilogue(args)
-        keep = (a, b, out, a_scale_mx, b_scale_mx, scale_a, scale_b, workspace, pre_out, pre_in, q_mx, s_mx)
+        keep = (a, b, out, a_scale_mx, b_tiled, scale_a, scale_b, workspace, pre_out, pre_in, q_mx, s_mx)
 
         def launch():
             with torch.cuda.device(dev):
