@@ -101,6 +101,9 @@ typedef struct {
   int32_t cta_pair; /* 1: the CTA-pair kernel (tcgen05 cta_group::2, one 256 x 256 tile per two SMs).  2: never pairs.
                        0: the library's choice (pairs when the 256 x 256 tiles fill the GPU about as well as
                        128 x 256 ones).  The results are bit-identical either way. */
+  int32_t group_m;  /* the reference's tuning option of that name (warpy_kernels/gemm/api.py:55, base.py:87-103):
+                       output tiles are visited in groups of group_m tile rows that sweep all tile columns, so the
+                       CTAs running at the same time share operand rows in L2.  0 = 8.  Any value gives the same bits. */
 } wk_gemm16_args;
 
 int wk_gemm_16bit(const wk_gemm16_args* args, void* stream);
@@ -149,6 +152,7 @@ typedef struct {
                             for it (16-byte aligned): the layout the kernels read, made once for scales that do not
                             change from call to call (weights).  0: row-major, re-tiled into the workspace per call. */
   int32_t b_scale_tiled; /* the same for b_scale_mx.  With both set the workspace may be NULL. */
+  int32_t group_m;       /* as in wk_gemm16_args; 0 = 8 */
 } wk_gemm_mx_args;
 
 int64_t wk_gemm_mxfp8_workspace_bytes(int m, int n, int k);

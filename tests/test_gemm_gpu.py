@@ -513,11 +513,12 @@ def test_autotune_gemm_times_both_kernels_and_stores_the_winner(cuda, kind, tmp_
     a, b = torch.randn(m, k, device=cuda, generator=g), torch.randn(n, k, device=cuda, generator=g)
     a, b = (a.to(FP8), b.to(FP8)) if kind == "fp8" else (a.bfloat16(), b.bfloat16())
     best, results = autotune_gemm(a, b, iters=3, verbose=False)
-    assert best in ({"cta_pair": False}, {"cta_pair": True}) and len(results) == 2
+    assert best["cta_pair"] in (False, True) and best["group_m"] in (8, 32) and len(results) == 4
     assert all(isinstance(t, float) for _, t in results)
     key = f"{'gemm_fp8' if kind == 'fp8' else 'gemm'}|m={m}|n={n}|k={k}|sm100"
     assert json.load(open(tmp_path / "tune.json")) == {key: best}
-    assert torch.equal(gemm(a, b), gemm(a, b, cta_pair=best["cta_pair"]))  # the cache entry is what runs by default
+    assert torch.equal(gemm(a, b), gemm(a, b, **best))  # the cache entry is what runs by default
+    assert torch.equal(gemm(a, b), gemm(a, b, cta_pair=False, group_m=3))  # any grouping gives the same bits
 
 
 def test_mx_scales_tiled_once_through_the_c_abi(cuda):

@@ -211,7 +211,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }  // namespace
 
 // the CTA-pair kernel (gemm_bf16_2sm.cu)
-int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n, int k, int f16, int a_trans,
+int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n, int k, int group_m, int f16, int a_trans,
                           int b_trans, const Epilogue& e, int* status, cudaStream_t stream);
 }  // namespace wk
 
@@ -263,7 +263,8 @@ extern "C" int wk_gemm_16bit(const wk_gemm16_args* g, void* stream) {
   // cta_pair: 1 the CTA-pair kernel, 2 this file's kernel, 0 whichever should finish
   // first: a pair works through a 256 x 256 tile about 10 % faster than two SMs through two 128 x 256 tiles
   // (1.53 against 1.40 PFLOP/s at 8192^3), but a small problem fills 148 SMs better with the smaller tiles
-  if (g->cta_pair < 0 || g->cta_pair > 2) return WK_E_ARG;
+  if (g->cta_pair < 0 || g->cta_pair > 2 || g->group_m < 0) return WK_E_ARG;
+  const int group_m = g->group_m ? g->group_m : 8;
   const int sms = sm_count();
   if (sms <= 0) return WK_E_CUDA;
   const int num_tiles = (m / BM) * ((n + BN - 1) / BN);
@@ -277,12 +278,12 @@ extern "C" int wk_gemm_16bit(const wk_gemm16_args* g, void* stream) {
     pair = pair_tiles > sms && pair_waves * 10 < single_waves * 11;
   }
   if (pair) {
-    return launch_gemm_16bit_2sm(g->a, g->b, g->out, m, n, k, g->f16, g->a_trans, g->b_trans, e, status,
+    return launch_gemm_16bit_2sm(g->a, g->b, g->out, m, n, k, group_m, g->f16, g->a_trans, g->b_trans, e, status,
                                  static_cast<cudaStream_t>(stream));
   }
   if (allow_smem(reinterpret_cast<const void*>(gemm_bf16_kernel), SMEM_BYTES)) return WK_E_CUDA;
   const int grid = num_tiles < sms ? num_tiles : sms;
-  gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ta, tb, g->out, m, n, k, 8,
+  gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ta, tb, g->out, m, n, k, group_m,
                                                                                      g->f16, g->a_trans, g->b_trans, e, status);
   return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
 }

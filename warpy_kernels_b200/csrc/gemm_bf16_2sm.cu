@@ -234,7 +234,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 }  // namespace
 
 // Launches the CTA-pair kernel.  The caller has checked the arguments; M and N are multiples of 128, K of 64.
-int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n, int k, int f16, int a_trans,
+int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n, int k, int group_m, int f16, int a_trans,
                           int b_trans, const Epilogue& e, int* status, cudaStream_t stream) {
   const CUtensorMapDataType dt = f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap ta, tb;
@@ -259,7 +259,7 @@ int launch_gemm_16bit_2sm(const void* a, const void* b, void* out, int m, int n,
   const int num_tiles = ((m + P_BM - 1) / P_BM) * ((n + P_BN - 1) / P_BN);
   const int max_pairs = sms / 2;
   const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
-  gemm_bf16_2sm_kernel<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(ta, tb, out, m, n, k, 8, f16, a_trans, b_trans, e,
+  gemm_bf16_2sm_kernel<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(ta, tb, out, m, n, k, group_m, f16, a_trans, b_trans, e,
                                                                         status);
   return cudaGetLastError() == cudaSuccess ? 0 : WK_E_CUDA;
 }

@@ -348,7 +348,8 @@ extern "C" int wk_gemm_mxfp8(const wk_gemm_mx_args* a, void* stream) {
   p.M = m;
   p.N = n;
   p.K = k;
-  p.group_m = 8;
+  if (a->group_m < 0) return WK_E_ARG;
+  p.group_m = a->group_m ? a->group_m : 8;
   p.status = status;
   if (a->cta_pair == 1) return launch_gemm_mxfp8_2sm(a->a, a->b, p, st, !(a_tiled && b_tiled));
 

@@ -34,7 +34,7 @@ class _MxArgs(ctypes.Structure):
         ("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32),
         *_EPILOGUE_FIELDS, ("out_f16", ctypes.c_int32),
         ("pre_out", ctypes.c_void_p), ("pre_in", ctypes.c_void_p), ("cta_pair", ctypes.c_int32),
-        ("a_scale_tiled", ctypes.c_int32), ("b_scale_tiled", ctypes.c_int32),
+        ("a_scale_tiled", ctypes.c_int32), ("b_scale_tiled", ctypes.c_int32), ("group_m", ctypes.c_int32),
     ]
 
 
@@ -47,6 +47,7 @@ class _Gemm16Args(ctypes.Structure):
         ("pre_out", ctypes.c_void_p), ("pre_in", ctypes.c_void_p),
         ("q_mx", ctypes.c_void_p), ("s_mx", ctypes.c_void_p),
         ("a_trans", ctypes.c_int32), ("b_trans", ctypes.c_int32), ("cta_pair", ctypes.c_int32),
+        ("group_m", ctypes.c_int32),
     ]
 
 
@@ -81,7 +82,7 @@ def make_gemm(
     out=None,
     bk=None,
     stages=3,
-    group_m=8,
+    group_m=None,
     min_blocks=1,
     bn=128,
     frag_pipe=False,
@@ -111,7 +112,10 @@ def make_gemm(
         out: Optional contiguous ``[M, N]`` bf16 output, 16-byte aligned. Allocated if ``None``.
         bk: K elements per pipeline stage in the reference; here only the divisibility rule ``K % bk == 0`` is
             kept. Defaults to 64 for bf16 and 128 for fp8.
-        stages, group_m, min_blocks, frag_pipe, tma, warp_spec, persistent, setmaxnreg: Accepted for
+        group_m: Output tiles are visited in groups of ``group_m`` tile rows that sweep all tile columns, as in the
+            reference; it decides which operand rows the CTAs that run together share in L2. ``None`` takes the tuned
+            value for the shape (``autotune_gemm``), else 8. The result does not depend on it.
+        stages, min_blocks, frag_pipe, tma, warp_spec, persistent, setmaxnreg: Accepted for
             compatibility and ignored: the sm_100a kernels are always TMA-fed, warp-specialised and persistent.
         bn: Output columns per CTA in the reference, 128 or 256; ``N`` must be a multiple of it.
         scale_a: Float32 CUDA tensor that scales ``a``: one element (used for fp8 inputs only), or ``M`` elements
@@ -207,9 +211,13 @@ def make_gemm(
         scale_b = scale_b if col_scale else None
     if col_scale and scale_b.data_ptr() % 16:
         scale_b = scale_b.clone()  # the kernel reads column scales as 16-byte vectors
-    if cta_pair is None:
-        # the kernel autotune_gemm found fastest for this shape, if it was run; else the library's own choice
-        cta_pair = (tune_lookup(gemm_tune_key("gemm_fp8" if fp8 else "gemm", m, n, k)) or {}).get("cta_pair")
+    if cta_pair is None or group_m is None:
+        # what autotune_gemm found fastest for this shape, if it was run; else the library's own choice
+        tuned = tune_lookup(gemm_tune_key("gemm_fp8" if fp8 else "gemm", m, n, k)) or {}
+        cta_pair = tuned.get("cta_pair") if cta_pair is None else cta_pair
+        group_m = tuned.get("group_m") if group_m is None else group_m
+    if group_m is not None and (not isinstance(group_m, int) or group_m < 1):
+        raise ValueError("group_m must be a positive integer")
     _check_mx("a_scale_mx", a_scale_mx, m, k, fp8)
     _check_mx("b_scale_mx", b_scale_mx, n, k, fp8)
     q_mx = torch.empty(m, n, dtype=torch.float8_e4m3fn, device=a.device) if out_mx else None
@@ -232,6 +240,7 @@ def make_gemm(
         args.f16 = int(a.dtype == torch.float16)
         args.a_trans, args.b_trans = int(bool(a_trans)), int(bool(b_trans))
         args.cta_pair = 0 if cta_pair is None else 1 if cta_pair else 2
+        args.group_m = int(group_m or 0)
         fill_epilogue(args)
         keep = (a, b, out, scale_a, scale_b, pre_out, pre_in, q_mx, s_mx)  # inputs and outputs stay alive
 
@@ -259,6 +268,7 @@ def make_gemm(
         args.m, args.n, args.k = m, n, k
         args.out_f16 = int(odt == torch.float16)
         args.cta_pair = 0 if cta_pair is None else 1 if cta_pair else 2
+        args.group_m = int(group_m or 0)
         fill_epilogue(args)
         keep = (a, b, out, a_scale_mx, b_tiled, scale_a, scale_b, workspace, pre_out, pre_in, q_mx, s_mx)
 
@@ -285,11 +295,12 @@ def gemm(a, b, out=None, **kwargs):
 
 
 def candidates_for(fp8):
-    """The kernel variants ``autotune_gemm`` times: single CTAs (128 x 256 tiles) and CTA pairs (``tcgen05``
-    ``cta_group::2``, 256 x 256 tiles over two SMs), for 16-bit and for fp8 inputs alike.  The counterpart of the
+    """The variants ``autotune_gemm`` times: single CTAs (128 x 256 tiles) or CTA pairs (``tcgen05``
+    ``cta_group::2``, 256 x 256 tiles over two SMs), each with tile groups of 8 and of 32 rows (``group_m``: few
+    rows suit a narrow output, many a wide one), for 16-bit and for fp8 inputs alike.  The counterpart of the
     reference's ``candidates_for`` (``warpy_kernels/gemm/configs.py``), whose knobs tune its SM80-SM120 kernels."""
-    del fp8  # the same two kernels exist for both input types
-    return [{"cta_pair": False}, {"cta_pair": True}]
+    del fp8  # the same kernels exist for both input types
+    return [{"cta_pair": pair, "group_m": g} for pair in (False, True) for g in (8, 32)]
 
 
 def autotune_gemm(a, b, candidates=None, iters=20, verbose=True, **kwargs):
