@@ -11,7 +11,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libwarpy_b200.so")
+# the library built next to this file; WARPY_KERNELS_B200_LIB points at another build of it (e.g. one with a probe)
+LIB_PATH = os.environ.get("WARPY_KERNELS_B200_LIB") or os.path.join(_HERE, "libwarpy_b200.so")
 
 _i32, _i64, _ptr, _str = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_char_p
 
