@@ -451,39 +451,46 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BN, BM / 2);
       const uint32_t st_tmem = tmem_base + A_ST_COL;
       const uint32_t dpt_tmem = tmem_base + A_DPT_COL;
-      auto q_desc_of = [&](uint32_t g) { return smem_desc_sw128(stage_smem + (g % A_STAGES) * A_STAGE_BYTES, 16, 1024); };
+      // Descriptors as (low word, shared high word): the tiles' low words are set up once, a K step or a row block
+      // is one 32-bit add (this thread shares its scheduler with four busy element-wise warps, so what it spends on
+      // operand set-up delays every product of the tile).
+      const uint32_t desc_hi = smem_desc_sw128_hi(1024);
+      const uint32_t k_lo0 = smem_desc_lo(k_smem(0), 16), k_lo1 = smem_desc_lo(k_smem(1), 16);
+      const uint32_t v_lo0 = smem_desc_lo(v_smem(0), 16), v_lo1 = smem_desc_lo(v_smem(1), 16);
+      const uint32_t q_lo0 = smem_desc_lo(stage_smem, 16), q_lo1 = smem_desc_lo(stage_smem + A_STAGE_BYTES, 16);
+      static_assert(A_STAGES == 2, "two stages of Q / dO8 tiles");
+      const uint32_t idesc_ts = make_idesc_mx_major(BN, DH, 0, 0, 0, 1);
       // S^T = K Q^T and dP^T = V dO8^T for queries [64 h, 64 h + 64) of tile g (K and V in buffers kb): rows 64 h..
       // of the Q and dO8 tiles are 64 x 128 bytes further on (+512 in descriptor units)
       auto ss_half = [&](uint32_t g, int kb, int h) {
-        const uint64_t k_desc = smem_desc_sw128(k_smem(kb), 16, 1024);
-        const uint64_t v_desc = smem_desc_sw128(v_smem(kb), 16, 1024);
-        const uint64_t q_desc = q_desc_of(g) + 512 * h;
-        const uint64_t do_desc = q_desc + (TILE_BYTES >> 4);
+        const uint32_t k_lo = kb ? k_lo1 : k_lo0, v_lo = kb ? v_lo1 : v_lo0;
+        const uint32_t q_lo = ((g & 1) ? q_lo1 : q_lo0) + 512 * h;
+        const uint32_t do_lo = q_lo + (TILE_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k)
-          if (32 * k < DH) mma_f8_ss(st_tmem + HALF_COLS * h, k_desc + 2 * k, q_desc + 2 * k, idesc_ss, k != 0);
+        for (int k = 0; k < DH / 32; ++k)
+          mma_f8_ss_w(st_tmem + HALF_COLS * h, k_lo + 2 * k, q_lo + 2 * k, desc_hi, idesc_ss, k != 0);
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k)
-          if (32 * k < DH) mma_f8_ss(dpt_tmem + HALF_COLS * h, v_desc + 2 * k, do_desc + 2 * k, idesc_ss, k != 0);
+        for (int k = 0; k < DH / 32; ++k)
+          mma_f8_ss_w(dpt_tmem + HALF_COLS * h, v_lo + 2 * k, do_lo + 2 * k, desc_hi, idesc_ss, k != 0);
         tc_commit(s_full(h));
       };
       // dV += (P g)^T dO8 and dK += dS^T Q8 over the same 64 queries (`it`: the tile's number inside its key block).
       // B operands: the dO8 / Q8 tiles again, now read MN-major (K = queries, 32 per step = 4096 bytes, N = head dim)
       auto ts_half = [&](uint32_t g, int it, int h) {
-        const uint64_t q_desc = q_desc_of(g);
-        const uint64_t do_desc = q_desc + (TILE_BYTES >> 4);
+        const uint32_t q_lo = (g & 1) ? q_lo1 : q_lo0;
+        const uint32_t do_lo = q_lo + (TILE_BYTES >> 4);
         // block k of the half keeps its codes and scale words inside its own 32 columns
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const uint32_t bb = st_tmem + HALF_COLS * h + 32 * k;
-          mma_mxf8_ts(tmem_base + A_DV_COL, bb, do_desc + 256 * (2 * h + k), make_idesc_mx_major(BN, DH, 0, 0, 0, 1),
-                      bb + A_SF_P, bb + A_SF_UNIT, (it | h | k) != 0);
+          mma_mxf8_ts_w(tmem_base + A_DV_COL, bb, do_lo + 256 * (2 * h + k), desc_hi, idesc_ts, bb + A_SF_P,
+                        bb + A_SF_UNIT, (it | h | k) != 0);
         }
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const uint32_t bb = st_tmem + HALF_COLS * h + 32 * k;
-          mma_mxf8_ts(tmem_base + A_DK_COL, dpt_tmem + HALF_COLS * h + 32 * k, q_desc + 256 * (2 * h + k),
-                      make_idesc_mx_major(BN, DH, 0, 0, 0, 1), bb + A_SF_DS, bb + A_SF_UNIT, (it | h | k) != 0);
+          mma_mxf8_ts_w(tmem_base + A_DK_COL, dpt_tmem + HALF_COLS * h + 32 * k, q_lo + 256 * (2 * h + k), desc_hi,
+                        idesc_ts, bb + A_SF_DS, bb + A_SF_UNIT, (it | h | k) != 0);
         }
       };
       auto wait_tile = [&](uint32_t g) {  // the Q / dO8 / records of tile g have landed
@@ -802,30 +809,32 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const uint32_t s_tmem = tmem_base + B_S_COL;
       const uint32_t dp_tmem = tmem_base + B_DP_COL;
       bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
-      const uint64_t q_desc = smem_desc_sw128(q_smem, 16, 1024);
-      const uint64_t do_desc = smem_desc_sw128(do_smem, 16, 1024);
-      auto k_desc_of = [&](int j) { return smem_desc_sw128(stage_smem + (j % B_STAGES) * B_STAGE_BYTES, 16, 1024); };
+      // descriptors as (low word, shared high word), as in the dK/dV kernel
+      const uint32_t desc_hi = smem_desc_sw128_hi(1024);
+      const uint32_t q_lo = smem_desc_lo(q_smem, 16), do_lo = smem_desc_lo(do_smem, 16);
+      const uint32_t idesc_ts = make_idesc_mx_major(BM, DH, 0, 0, 0, 1);
+      auto k_lo_of = [&](int j) { return smem_desc_lo(stage_smem + (j % B_STAGES) * B_STAGE_BYTES, 16); };
       // S = Q K^T and dP = dO8 V^T for keys [64 h, 64 h + 64) of tile j (rows 64 h.. of the K and V tiles: +512 in
       // descriptor units)
       auto ss_half = [&](int j, int h) {
-        const uint64_t k_desc = k_desc_of(j) + 512 * h;
-        const uint64_t v_desc = k_desc + (TILE_BYTES >> 4);
+        const uint32_t k_lo = k_lo_of(j) + 512 * h;
+        const uint32_t v_lo = k_lo + (TILE_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k)
-          if (32 * k < DH) mma_f8_ss(s_tmem + HALF_COLS * h, q_desc + 2 * k, k_desc + 2 * k, idesc_ss, k != 0);
+        for (int k = 0; k < DH / 32; ++k)
+          mma_f8_ss_w(s_tmem + HALF_COLS * h, q_lo + 2 * k, k_lo + 2 * k, desc_hi, idesc_ss, k != 0);
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k)
-          if (32 * k < DH) mma_f8_ss(dp_tmem + HALF_COLS * h, do_desc + 2 * k, v_desc + 2 * k, idesc_ss, k != 0);
+        for (int k = 0; k < DH / 32; ++k)
+          mma_f8_ss_w(dp_tmem + HALF_COLS * h, do_lo + 2 * k, v_lo + 2 * k, desc_hi, idesc_ss, k != 0);
         tc_commit(s_full(h));
       };
       // dQ += dS K over the same 64 keys: A = dS codes in the dP columns, B = the K tile read MN-major
       auto ts_half = [&](int j, int h) {
-        const uint64_t k_desc = k_desc_of(j);
+        const uint32_t k_lo = k_lo_of(j);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const uint32_t bb = s_tmem + HALF_COLS * h + 32 * k;  // the block's scale words sit in its own S columns
-          mma_mxf8_ts(tmem_base + B_DQ_COL, dp_tmem + HALF_COLS * h + 32 * k, k_desc + 256 * (2 * h + k),
-                      make_idesc_mx_major(BM, DH, 0, 0, 0, 1), bb + B_SF_DS, bb + B_SF_UNIT, (j | h | k) != 0);
+          mma_mxf8_ts_w(tmem_base + B_DQ_COL, dp_tmem + HALF_COLS * h + 32 * k, k_lo + 256 * (2 * h + k), desc_hi,
+                        idesc_ts, bb + B_SF_DS, bb + B_SF_UNIT, (j | h | k) != 0);
         }
       };
       ok = ok && mbar_wait(kv_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD);

@@ -313,6 +313,17 @@ __device__ __forceinline__ uint64_t smem_desc_plain(uint32_t saddr, uint32_t lbo
   return d;
 }
 
+// The same descriptor as two 32-bit words.  A thread that issues MMAs shares its scheduler with busy warps, so
+// every instruction it spends on operand set-up delays the tensor pipe; the high word (stride offset, version,
+// swizzle mode) is one constant for all tiles of a kernel, and moving the start address by a K step or a row
+// block is one 32-bit add on the low word (the 14-bit address field cannot carry: shared memory ends below 256 KiB).
+__device__ __forceinline__ uint32_t smem_desc_sw128_hi(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+
 // Instruction descriptor for kind::f16 / kind::f8f6f4 with an fp32 accumulator.
 //   fmt: kind::f16  0 = f16, 1 = bf16;  kind::f8f6f4  0 = e4m3, 1 = e5m2
 //   major: 0 = K-major, 1 = MN-major
@@ -365,6 +376,18 @@ __device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with the descriptors given as (low word, shared high word).
+__device__ __forceinline__ void mma_f8_ss_w(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
                                           uint32_t idesc, uint32_t accumulate) {
@@ -396,6 +419,19 @@ __device__ __forceinline__ void mma_mxf8_ts(uint32_t d_tmem, uint32_t a_tmem, ui
       "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], [%1], %2, %3, [%4], "
       "[%5], p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// Block-scaled, A from TMEM, B given as (low word, high word).
+__device__ __forceinline__ void mma_mxf8_ts_w(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t desc_hi,
+                                              uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %7, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], [%1], db, %4, [%5], "
+      "[%6], p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
       : "memory");
 }
 // Copy 32 rows x 16 bytes from shared memory into 4 TMEM columns of every 32-lane
