@@ -25,6 +25,9 @@ SHAPES = [
     (1, 2, 1, 512, 128, 128),
     (1, 2, 1, 512, 128, 64),
     (1, 8, 2, 384, 640, 128),
+    # more key blocks than SMs: the dK/dV CTAs that start take over the blocks of those that have not
+    (3, 8, 8, 1024, 1024, 128),
+    (5, 8, 4, 1024, 1024, 64),
 ]
 
 

@@ -35,18 +35,47 @@
 // Tensor-core bound: 10 . B . Hq . Nq . Nk . d flops of algorithmic work (half when causal).
 #include <math.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "host_common.h"
 
 namespace wk {
 namespace {
 
+// Cycle probe of the two main kernels (compile with -DWK_BWD_PROBE; never part of the shipped library): lane 0 of a
+// warp adds the cycles it spent between two marks to a counter, slots 0..23 for the dK/dV kernel and 24..47 for the
+// dQ kernel.
+#ifdef WK_BWD_PROBE
+__device__ unsigned long long g_bwd_probe[48];
+// per-warp accumulators in shared memory (lane 0 only), flushed to the global counters once at the end
+#define PROBE_SMEM __shared__ unsigned long long probe_acc[18][24]
+#define PROBE_DECL long long probe_t = clock64()
+#define PROBE(slot)                                                                        \
+  do {                                                                                     \
+    const long long probe_now = clock64();                                                 \
+    if ((threadIdx.x & 31) == 0) probe_acc[threadIdx.x >> 5][slot] += probe_now - probe_t; \
+    probe_t = probe_now;                                                                   \
+  } while (0)
+#define PROBE_COUNT(slot) do { if ((threadIdx.x & 31) == 0) probe_acc[threadIdx.x >> 5][slot] += 1; } while (0)
+#define PROBE_INIT do { if ((threadIdx.x & 31) == 0) for (int i = 0; i < 24; ++i) probe_acc[threadIdx.x >> 5][i] = 0; } while (0)
+#define PROBE_FLUSH(base) do { if ((threadIdx.x & 31) == 0) for (int i = 0; i < 24; ++i) if (probe_acc[threadIdx.x >> 5][i]) atomicAdd(&g_bwd_probe[(base) + i], probe_acc[threadIdx.x >> 5][i]); } while (0)
+#else
+#define PROBE_SMEM
+#define PROBE_DECL
+#define PROBE(slot)
+#define PROBE_COUNT(slot)
+#define PROBE_INIT
+#define PROBE_FLUSH(base)
+#endif
+
 constexpr int BM = 128;  // queries per tile
 constexpr int BN = 128;  // keys per tile
 constexpr int D = 128;  // bytes per row of a tile in shared memory (the largest head dimension)
 constexpr int TILE_BYTES = 128 * 128;
 constexpr int SF_BYTES = 512;
-constexpr int THREADS = 576;          // TMA warp, MMA warp, 16 element-wise warps (four threads per row)
+constexpr int THREADS = 640;          // four warps with one working thread each (loads, MMAs), 16 element-wise warps
+constexpr int FIRST_EW_WARP = 4;
 constexpr int HALF_THREADS = 256;     // the element-wise threads of one 64-column half of a tile: two per row
 constexpr int HALF_COLS = 64;
 constexpr int TMEM_COLS = 512;
@@ -282,18 +311,25 @@ struct BwdParams {
 // ---------------------------------------------------------------------------
 // 2. dK / dV
 // ---------------------------------------------------------------------------
-constexpr int A_STAGES = 2;
+constexpr int A_STAGES = 4;
 constexpr int A_STAT_BYTES = BM * 8;
 constexpr int A_STAGE_BYTES = 2 * TILE_BYTES + A_STAT_BYTES;
-// Requested size is padded past half an SM's shared memory: each CTA allocates all 512 TMEM columns, so a second
-// resident CTA could only spin in tcgen05.alloc.
 constexpr int SCHED_SLOTS = 4;  // answers of the launch control in flight
-constexpr int A_SMEM_NEED = 4 * TILE_BYTES + A_STAGES * A_STAGE_BYTES + 1024 + 512;
-constexpr int A_SMEM_BYTES = A_SMEM_NEED > 120 * 1024 ? A_SMEM_NEED : 120 * 1024;
-constexpr int A_ST_COL = 0, A_DPT_COL = 128, A_DV_COL = 256, A_DK_COL = 384;
-// scale-factor columns inside the consumed S^T columns; the two threads of a row own 4 columns each
-// Inside the 32 S^T columns of a block, once its thread has read them: codes in 0..7, then the scale words
-constexpr int A_SF_P = 8, A_SF_UNIT = 12, A_SF_DS = 16;
+// More than half an SM's shared memory: each CTA allocates all 512 TMEM columns, so a second resident CTA could
+// only spin in tcgen05.alloc.
+constexpr int A_SMEM_BYTES = 4 * TILE_BYTES + A_STAGES * A_STAGE_BYTES + 1024 + 512;
+static_assert(A_SMEM_BYTES > 120 * 1024 && A_SMEM_BYTES <= 227 * 1024, "one CTA per SM");
+static_assert(A_STAGE_BYTES % 1024 == 0, "tiles of a stage start on swizzle-atom boundaries");
+// TMEM columns.  One buffer for the scores of 64 queries (S^T and dP^T), which the two groups of element-wise
+// threads take turns on; the e4m3 codes they produce and the codes' scale words live apart from it, so that the
+// buffer is free for the next product as soon as its scores are in registers.  Unit = 64 queries of a tile (h = 0,
+// 1); block k = 0, 1 of a unit = 32 queries = the K extent of one block-scaled product.
+constexpr int A_ST_COL = 0, A_DPT_COL = 64;
+constexpr int A_PC_COL = 128;   // (P g)^T codes: 8 columns per (h, k)
+constexpr int A_DSC_COL = 160;  // dS^T codes, the same
+constexpr int A_SF_COL = 192;   // per (h, k) 8 columns: the P scales in 0..3, the dS scales in 4..7
+constexpr int A_SF_UNIT_COL = 224;  // scale 1 for the B operands, written once
+constexpr int A_DV_COL = 256, A_DK_COL = 384;
 
 template <int DH>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -311,11 +347,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   auto kv_empty = [&](int kb) { return bar_base + 8u * (2 + kb); };  // the S products of the block have read K and V
   auto q_full = [&](int s) { return bar_base + 8u * (4 + s); };
   auto q_empty = [&](int s) { return bar_base + 8u * (4 + A_STAGES + s); };
-  // the two 64-query halves of a tile are handed back and forth separately (h = 0, 1)
-  auto s_full = [&](int h) { return bar_base + 8u * (4 + 2 * A_STAGES + h); };
-  auto p_full = [&](int h) { return bar_base + 8u * (6 + 2 * A_STAGES + h); };
-  const uint32_t acc_full = bar_base + 8u * (8 + 2 * A_STAGES);  // dK and dV of the block are complete
-  const uint32_t acc_free = acc_full + 8;                        // and every element-wise thread has read its part
+  // per group of element-wise threads (h = 0, 1: the group takes the units with that h)
+  const uint32_t unit_bars = bar_base + 8u * (4 + 2 * A_STAGES);
+  auto s_full = [&](int h) { return unit_bars + 8u * h; };         // the unit's S^T and dP^T are in the buffer
+  auto s_free = [&](int h) { return unit_bars + 8u * (2 + h); };   // ... and now in the group's registers
+  auto p_full = [&](int h) { return unit_bars + 8u * (4 + h); };   // the unit's codes and scales are in TMEM
+  auto ts_done = [&](int h) { return unit_bars + 8u * (6 + h); };  // ... and the dV / dK products have read them
+  const uint32_t acc_full = unit_bars + 8u * 8;  // dK and dV of the block are complete
+  const uint32_t acc_free = acc_full + 8;        // and every element-wise thread has read its part
   auto sched_full = [&](int i) { return acc_free + 8u * (1 + i); };                  // answer i has landed
   auto sched_empty = [&](int i) { return acc_free + 8u * (1 + SCHED_SLOTS + i); };  // and everybody has read it
   const uint32_t tmem_slot = acc_free + 8u * (1 + 2 * SCHED_SLOTS);
@@ -323,6 +362,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
+  PROBE_SMEM;
+  PROBE_INIT;
   const int group = p.Hq / p.Hkv;
   const int shift = p.Nk - p.Nq;
   const int num_m = (p.Nq + BM - 1) / BM;
@@ -338,13 +379,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     }
     for (int h = 0; h < 2; ++h) {
       mbar_init(s_full(h), 1);
+      mbar_init(s_free(h), HALF_THREADS);
       mbar_init(p_full(h), HALF_THREADS);
+      mbar_init(ts_done(h), 1);
     }
     mbar_init(acc_full, 1);
     mbar_init(acc_free, 2 * HALF_THREADS);
     for (int i = 0; i < SCHED_SLOTS; ++i) {
       mbar_init(sched_full(i), 1);
-      mbar_init(sched_empty(i), 2 + 2 * HALF_THREADS);  // the TMA thread, the MMA thread, the element-wise threads
+      mbar_init(sched_empty(i), 4 + 2 * HALF_THREADS);  // the TMA thread, three MMA threads, the element-wise threads
     }
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
@@ -440,151 +483,149 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 2) {
     if (lane == 0) {
-      // A tile is processed as two halves of 64 queries, each with its own pair of barriers, so that the tensor
-      // pipe works on one half while the element-wise warps of the other half are busy:
-      //   S^T, dP^T (h) -> element-wise (h) -> dV, dK += (h) -> S^T, dP^T of the next tile (h) -> ...
-      // All MMAs come from this one thread, so the products of the next tile overwrite a half's columns only
-      // after the products that read its codes (the tensor pipe runs in issue order).  The next tile may be the
-      // first one of the next key block: its S^T and dP^T are under way while this block's dK and dV are stored.
+      // The CTA's work is a sequence of units: 64 queries (h = 0, 1) of a query tile of a key block, block after
+      // block.  Unit n = 2 g + h (g: tiles so far) goes to element-wise group h.  This thread issues the scores of
+      // the units with its h (warp 1: h = 0, warp 2: h = 1) into the one score buffer, each as soon as the other
+      // group holds the unit before it in registers; a third thread (warp 3) issues the sums.  Three issuing
+      // threads because a barrier operation costs a thread 100 cycles and more while shared memory is busy: one
+      // thread cannot wait, issue and commit for every unit in the time the element-wise threads need for it.
+      const int h = warp - 1;
       constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BN, BM / 2);
       const uint32_t st_tmem = tmem_base + A_ST_COL;
       const uint32_t dpt_tmem = tmem_base + A_DPT_COL;
       // Descriptors as (low word, shared high word): the tiles' low words are set up once, a K step or a row block
-      // is one 32-bit add (this thread shares its scheduler with four busy element-wise warps, so what it spends on
-      // operand set-up delays every product of the tile).
+      // is one 32-bit add.
       const uint32_t desc_hi = smem_desc_sw128_hi(1024);
       const uint32_t k_lo0 = smem_desc_lo(k_smem(0), 16), k_lo1 = smem_desc_lo(k_smem(1), 16);
       const uint32_t v_lo0 = smem_desc_lo(v_smem(0), 16), v_lo1 = smem_desc_lo(v_smem(1), 16);
-      const uint32_t q_lo0 = smem_desc_lo(stage_smem, 16), q_lo1 = smem_desc_lo(stage_smem + A_STAGE_BYTES, 16);
-      static_assert(A_STAGES == 2, "two stages of Q / dO8 tiles");
-      const uint32_t idesc_ts = make_idesc_mx_major(BN, DH, 0, 0, 0, 1);
-      // S^T = K Q^T and dP^T = V dO8^T for queries [64 h, 64 h + 64) of tile g (K and V in buffers kb): rows 64 h..
-      // of the Q and dO8 tiles are 64 x 128 bytes further on (+512 in descriptor units)
-      auto ss_half = [&](uint32_t g, int kb, int h) {
-        const uint32_t k_lo = kb ? k_lo1 : k_lo0, v_lo = kb ? v_lo1 : v_lo0;
-        const uint32_t q_lo = ((g & 1) ? q_lo1 : q_lo0) + 512 * h;
-        const uint32_t do_lo = q_lo + (TILE_BYTES >> 4);
-#pragma unroll
-        for (int k = 0; k < DH / 32; ++k)
-          mma_f8_ss_w(st_tmem + HALF_COLS * h, k_lo + 2 * k, q_lo + 2 * k, desc_hi, idesc_ss, k != 0);
-#pragma unroll
-        for (int k = 0; k < DH / 32; ++k)
-          mma_f8_ss_w(dpt_tmem + HALF_COLS * h, v_lo + 2 * k, do_lo + 2 * k, desc_hi, idesc_ss, k != 0);
-        tc_commit(s_full(h));
-      };
-      // dV += (P g)^T dO8 and dK += dS^T Q8 over the same 64 queries (`it`: the tile's number inside its key block).
-      // B operands: the dO8 / Q8 tiles again, now read MN-major (K = queries, 32 per step = 4096 bytes, N = head dim)
-      auto ts_half = [&](uint32_t g, int it, int h) {
-        const uint32_t q_lo = (g & 1) ? q_lo1 : q_lo0;
-        const uint32_t do_lo = q_lo + (TILE_BYTES >> 4);
-        // block k of the half keeps its codes and scale words inside its own 32 columns
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const uint32_t bb = st_tmem + HALF_COLS * h + 32 * k;
-          mma_mxf8_ts_w(tmem_base + A_DV_COL, bb, do_lo + 256 * (2 * h + k), desc_hi, idesc_ts, bb + A_SF_P,
-                        bb + A_SF_UNIT, (it | h | k) != 0);
-        }
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const uint32_t bb = st_tmem + HALF_COLS * h + 32 * k;
-          mma_mxf8_ts_w(tmem_base + A_DK_COL, dpt_tmem + HALF_COLS * h + 32 * k, q_lo + 256 * (2 * h + k), desc_hi,
-                        idesc_ts, bb + A_SF_DS, bb + A_SF_UNIT, (it | h | k) != 0);
-        }
-      };
-      auto wait_tile = [&](uint32_t g) {  // the Q / dO8 / records of tile g have landed
-        return mbar_wait(q_full(g % A_STAGES), (g / A_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD);
-      };
-      // moves on to the next key block that has query tiles; false when the list is exhausted
+      // rows 64 h.. of the Q and dO8 tiles are 64 x 128 bytes further on (+512 in descriptor units)
+      const uint32_t q_lo0 = smem_desc_lo(stage_smem, 16) + 512 * h;
       bool have = blk.n_iter > 0;
-      auto advance = [&]() {
-        have = false;
-        while (ok && next_block()) {
-          if (blk.n_iter > 0) {
-            have = true;
+      while (ok && !have && next_block()) have = blk.n_iter > 0;
+      int ci = 0;      // blocks with work so far
+      uint32_t g = 0;  // tiles so far
+      PROBE_DECL;
+      while (ok && have) {
+        const int kb = ci & 1, n_iter = blk.n_iter;
+        const uint32_t k_lo = kb ? k_lo1 : k_lo0, v_lo = kb ? v_lo1 : v_lo0;
+        if (!mbar_wait(kv_full(kb), (ci >> 1) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        for (int it = 0; it < n_iter; ++it, ++g) {
+          const int s = g % A_STAGES;
+          if (!mbar_wait(q_full(s), (g / A_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) {
+            ok = false;
             break;
           }
-        }
-        return have;
-      };
-      if (!have) advance();
-      int ci = 0;       // the current block's number among those with work
-      uint32_t g = 0;   // tiles so far
-      if (have) {
-        ok = mbar_wait(kv_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD) && wait_tile(0);
-        if (ok) {
+          PROBE(0);
+          // the unit before this one (the other group's) has left the score buffer
+          const uint32_t n = 2 * g + h;
+          if (n >= 1 && !mbar_wait(s_free(h ^ 1), ((n - 1) >> 1) & 1, p.status, WK_ERR_TIMEOUT_P)) {
+            ok = false;
+            break;
+          }
+          PROBE(1);
           tc_fence_after();
-          ss_half(0, 0, 0);
-          ss_half(0, 0, 1);
+          // S^T = K Q^T and dP^T = V dO8^T for queries [64 h, 64 h + 64) of the tile
+          const uint32_t q_lo = q_lo0 + s * (A_STAGE_BYTES >> 4);
+          const uint32_t do_lo = q_lo + (TILE_BYTES >> 4);
+#pragma unroll
+          for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(st_tmem, k_lo + 2 * k, q_lo + 2 * k, desc_hi, idesc_ss, k != 0);
+#pragma unroll
+          for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(dpt_tmem, v_lo + 2 * k, do_lo + 2 * k, desc_hi, idesc_ss, k != 0);
+          tc_commit(s_full(h));
+          PROBE(2);
+          PROBE_COUNT(6);
         }
+        if (!ok) break;
+        // Every S product of the block has been issued (this thread's are the last ones: the other thread's
+        // results were read before this thread's last unit could go into the buffer)
+        if (h == 1) tc_commit(kv_empty(kb));
+        ++ci;
+        have = false;
+        while (ok && !have && next_block()) have = blk.n_iter > 0;
       }
+    }
+    __syncwarp();
+  } else if (warp == 3) {
+    if (lane == 0) {
+      // dV += (P g)^T dO8 and dK += dS^T Q8, unit after unit, each as soon as its group has written the codes.
+      // B operands: the dO8 / Q8 tiles again, now read MN-major (K = queries, 32 per step = 4096 bytes, N = head
+      // dimension)
+      const uint32_t desc_hi = smem_desc_sw128_hi(1024);
+      const uint32_t q_lo0 = smem_desc_lo(stage_smem, 16);
+      const uint32_t idesc_ts = make_idesc_mx_major(BN, DH, 0, 0, 0, 1);
+      const uint32_t unit_sf = tmem_base + A_SF_UNIT_COL;
+      bool have = blk.n_iter > 0;
+      while (ok && !have && next_block()) have = blk.n_iter > 0;
+      int ci = 0;
+      uint32_t g = 0;
+      PROBE_DECL;
       while (ok && have) {
         const int n_iter = blk.n_iter;
-        const int kb = ci & 1;
-        bool next_ready = false;  // the next block is known (blk describes it) and its K and V have landed
         for (int it = 0; ok && it < n_iter; ++it, ++g) {
-          const bool last = it + 1 == n_iter;
-          if (last) {
-            // look ahead: the first tile of the next block takes the place of this block's next tile
-            next_ready = advance();
-            if (!ok) break;
-            if (next_ready && !mbar_wait(kv_full(kb ^ 1), ((ci + 1) >> 1) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) {
-              ok = false;
-              break;
-            }
-          }
-          const bool more = !last || next_ready;
-          const int kb_next = last ? kb ^ 1 : kb;
-          if (!mbar_wait(p_full(0), g & 1, p.status, WK_ERR_TIMEOUT_P)) {
+          const int s = g % A_STAGES;
+          const uint32_t q_lo = q_lo0 + s * (A_STAGE_BYTES >> 4);
+          const uint32_t do_lo = q_lo + (TILE_BYTES >> 4);
+          // the tile has landed (the score threads saw that long ago; this thread reads the tile too)
+          if (!mbar_wait(q_full(s), (g / A_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) {
             ok = false;
             break;
           }
-          // the element-wise threads have read the previous block's dK and dV
-          if (it == 0 && ci >= 1 && !mbar_wait(acc_free, (ci - 1) & 1, p.status, WK_ERR_TIMEOUT_TMEM)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          ts_half(g, it, 0);
-          if (more) {
-            if (!wait_tile(g + 1)) {
+          PROBE(0);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (!mbar_wait(p_full(h), g & 1, p.status, WK_ERR_TIMEOUT_P)) {
               ok = false;
               break;
             }
+            PROBE(3);
+            // the element-wise threads have read the previous block's dK and dV
+            if (it == 0 && h == 0 && ci >= 1 && !mbar_wait(acc_free, (ci - 1) & 1, p.status, WK_ERR_TIMEOUT_TMEM)) {
+              ok = false;
+              break;
+            }
+            PROBE(4);
             tc_fence_after();
-            ss_half(g + 1, kb_next, 0);
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+              mma_mxf8_ts_w(tmem_base + A_DV_COL, tmem_base + A_PC_COL + 8 * (2 * h + k), do_lo + 256 * (2 * h + k),
+                            desc_hi, idesc_ts, tmem_base + A_SF_COL + 8 * (2 * h + k), unit_sf, (it | h | k) != 0);
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+              mma_mxf8_ts_w(tmem_base + A_DK_COL, tmem_base + A_DSC_COL + 8 * (2 * h + k), q_lo + 256 * (2 * h + k),
+                            desc_hi, idesc_ts, tmem_base + A_SF_COL + 8 * (2 * h + k) + 4, unit_sf, (it | h | k) != 0);
+            tc_commit(ts_done(h));
+            PROBE(5);
+            PROBE_COUNT(6);
           }
-          if (!mbar_wait(p_full(1), g & 1, p.status, WK_ERR_TIMEOUT_P)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          ts_half(g, it, 1);
-          tc_commit(q_empty(g % A_STAGES));
-          if (more) ss_half(g + 1, kb_next, 1);
-          // the S products of this block's last tile were issued one tile ago (or just now, for a single tile)
-          if (last) {
-            tc_commit(kv_empty(kb));
-            tc_commit(acc_full);
-          }
+          // every product that reads the stage is complete when this fires (the scores were read long ago)
+          tc_commit(q_empty(s));
         }
-        have = next_ready;
+        if (!ok) break;
+        tc_commit(acc_full);
         ++ci;
+        have = false;
+        while (ok && !have && next_block()) have = blk.n_iter > 0;
       }
     }
     __syncwarp();
   } else {
     const int quad = warp & 3;
-    const int c = (warp - 2) >> 2;   // which block of 32 of the tile's 128 columns this thread handles
-    const int half = c >> 1;         // the half the block is handed over with
+    const int c = (warp - FIRST_EW_WARP) >> 2;  // which block of 32 of the tile's 128 queries this thread handles
+    const int half = c >> 1;         // the unit (and the group) the block belongs to
     const int r = quad * 32 + lane;  // key row of the tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    // this thread's block: scores in columns [32 c, 32 c + 32) of both buffers
-    const uint32_t st_tmem = tmem_base + lane_addr + A_ST_COL + 32 * c;
-    const uint32_t dpt_tmem = tmem_base + lane_addr + A_DPT_COL + 32 * c;
+    // the block's scores in the buffer; where its codes and scale words go
+    const uint32_t st_tmem = tmem_base + lane_addr + A_ST_COL + 32 * (c & 1);
+    const uint32_t dpt_tmem = tmem_base + lane_addr + A_DPT_COL + 32 * (c & 1);
+    const uint32_t pc_tmem = tmem_base + lane_addr + A_PC_COL + 8 * c;
+    const uint32_t dsc_tmem = tmem_base + lane_addr + A_DSC_COL + 8 * c;
+    const uint32_t sf_tmem = tmem_base + lane_addr + A_SF_COL + 8 * c + quad;
+    if (c == 0) tmem_st4(tmem_base + lane_addr + A_SF_UNIT_COL, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
     int ci = -1;     // key blocks with work so far
     uint32_t g = 0;  // tiles so far
+    PROBE_DECL;
 
     for (;;) {
     const int n0 = blk.n0, n_iter = blk.n_iter;
@@ -603,6 +644,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         ok = false;
         break;
       }
+      PROBE(8);
       tc_fence_after();
       // the tile's row records: arrays log2(g) - L and -sum(dO8 . O) of 128 queries each, read four at a time
       const uint32_t stat = stage_smem + s * A_STAGE_BYTES + 2 * TILE_BYTES;
@@ -616,8 +658,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         tmem_ld32(st_tmem, sraw);
         tmem_ld32(dpt_tmem, draw);
         tc_wait_ld();
+        // the scores are in registers: the buffer may take the next unit
+        tc_fence_before();
+        mbar_arrive(s_free(half));
+        PROBE(9);
         uint64_t pt[16], ds[16];  // (P g)^T and dS^T of this key for 32 queries, as packed pairs
         const uint64_t beta2 = pack_f32x2(beta, beta);
+        // two copies of the loop, with and without the mask, behind one branch per tile (as predicated code the
+        // comparisons and selects take two issue slots per score in every tile)
+        auto scores_to_ds = [&](auto masked) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           // the same addresses for every thread: shared-memory broadcasts
@@ -628,7 +677,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[4 * i + 2]), __uint_as_float(sraw[4 * i + 3])), beta2,
                                  pack_f32x2(el.z, el.w)), x2, x3);
           float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
-          if (tile_masked) {
+          if constexpr (decltype(masked)::value) {
             if (c * 32 + 4 * i + 0 < first_col) p0 = 0.f;
             if (c * 32 + 4 * i + 1 < first_col) p1 = 0.f;
             if (c * 32 + 4 * i + 2 < first_col) p2 = 0.f;
@@ -642,25 +691,37 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
               mul_f32x2(pt[2 * i + 1], fma_f32x2(pack_f32x2(__uint_as_float(draw[4 * i + 2]), __uint_as_float(draw[4 * i + 3])),
                                                  sv2, pack_f32x2(nd.z, nd.w)));
         }
+        };
+        if (tile_masked) scores_to_ds(std::true_type{});
+        else scores_to_ds(std::false_type{});
         float inv_p, inv_d;
         const uint32_t bp = block_scale(max_bits_nonneg(pt), inv_p);  // P >= 0 and g > 0
         const uint32_t bd = block_scale(absmax_bits(ds), inv_d);
-        // the codes go to the first columns of the block, which its scores have just left
-        quantize_block_to_tmem(pt, st_tmem, inv_p);
-        quantize_block_to_tmem(ds, dpt_tmem, inv_d);
+        PROBE(10);
+        // the products of the group's previous unit have read its codes and scale words
+        if (g >= 1 && !mbar_wait_warp(ts_done(half), (g - 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        PROBE(11);
+        tc_fence_after();
+        quantize_block_to_tmem(pt, pc_tmem, inv_p);
+        quantize_block_to_tmem(ds, dsc_tmem, inv_d);
         sf_p = bp;
         sf_d = bd;
       }
       // scale factors straight into TMEM: the MMA reads the scale of row r from lane r, column r / 32
-      tmem_st1(st_tmem + A_SF_P + quad, sf_p);
-      tmem_st4(st_tmem + A_SF_UNIT, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-      tmem_st1(st_tmem + A_SF_DS + quad, sf_d);
+      tmem_st1(sf_tmem, sf_p);
+      tmem_st1(sf_tmem + 4, sf_d);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(p_full(half));
+      PROBE(12);
+      PROBE_COUNT(15);
     }
 
     if (n_iter > 0 && ok) ok = mbar_wait_warp(acc_full, ci & 1, p.status, WK_ERR_TIMEOUT_MMA);
+    PROBE(13);
     if (ok) {
       tc_fence_after();
       const float dk_scale = p.softmax_scale * p.q_descale[sc];
@@ -700,9 +761,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
     }
+    PROBE(14);
     if (!ok || !next_block()) break;
+    PROBE(16);
     }
   }
+  PROBE_FLUSH(0);
 
   tc_fence_before();
   __syncthreads();
@@ -715,12 +779,18 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 // ---------------------------------------------------------------------------
 // 3. dQ
 // ---------------------------------------------------------------------------
-constexpr int B_STAGES = 2;
+constexpr int B_STAGES = 4;
 constexpr int B_STAGE_BYTES = 2 * TILE_BYTES;  // K tile, V tile
-constexpr int B_SMEM_NEED = 2 * TILE_BYTES + B_STAGES * B_STAGE_BYTES + 2 * SF_BYTES + 1024 + 256;
-constexpr int B_SMEM_BYTES = B_SMEM_NEED > 120 * 1024 ? B_SMEM_NEED : 120 * 1024;
+constexpr int B_SMEM_BYTES = 2 * TILE_BYTES + B_STAGES * B_STAGE_BYTES + 1024 + 256;
+static_assert(B_SMEM_BYTES > 120 * 1024 && B_SMEM_BYTES <= 227 * 1024, "one CTA per SM");
+// TMEM columns: the scores of a whole key tile, dQ, and apart from the scores the dS codes and their scale words,
+// twice each (tiles alternate), so that the score columns are free for the next tile's products as soon as the
+// element-wise threads hold the scores in registers.
 constexpr int B_S_COL = 0, B_DP_COL = 128, B_DQ_COL = 256;
-constexpr int B_SF_DS = 8, B_SF_UNIT = 12;
+constexpr int B_DSC_COL = 384;      // dS codes: per tile buffer 32 columns, 8 per block of 32 keys
+constexpr int B_SF_COL = 448;       // their scales: per tile buffer 16 columns, 4 per block of 32 keys
+constexpr int B_SF_UNIT_COL = 480;  // scale 1 for the B operand, written once
+constexpr int EW_THREADS = 2 * HALF_THREADS;
 
 template <int DH>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -732,20 +802,22 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const uint32_t q_smem = smem_base;
   const uint32_t do_smem = q_smem + TILE_BYTES;
   const uint32_t stage_smem = do_smem + TILE_BYTES;
-  const uint32_t sfd_smem = stage_smem + B_STAGES * B_STAGE_BYTES;
-  const uint32_t sfu_smem = sfd_smem + SF_BYTES;
-  const uint32_t bar_base = sfu_smem + SF_BYTES;
+  const uint32_t bar_base = stage_smem + B_STAGES * B_STAGE_BYTES;
   const uint32_t q_full = bar_base;
   auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + B_STAGES + s); };
-  // the two 64-key halves of a tile are handed back and forth separately (h = 0, 1)
-  auto s_full = [&](int h) { return bar_base + 8u * (1 + 2 * B_STAGES + h); };
-  auto p_full = [&](int h) { return bar_base + 8u * (3 + 2 * B_STAGES + h); };
-  const uint32_t acc_full = bar_base + 8u * (5 + 2 * B_STAGES);
+  const uint32_t s_full = bar_base + 8u * (1 + 2 * B_STAGES);  // S and dP of a tile are in TMEM
+  const uint32_t s_free = s_full + 8;                          // ... and now in the element-wise threads' registers
+  const uint32_t p_full = s_full + 16;                         // the tile's dS codes and scales are in TMEM
+  auto ts_done = [&](int i) { return s_full + 24 + 8u * i; };  // ... and the dQ products have read them (buffer i)
+  const uint32_t acc_full = s_full + 40;
   const uint32_t tmem_slot = acc_full + 8;
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
+  PROBE_SMEM;
+  PROBE_INIT;
+  PROBE_DECL;
   const int m_blk = gridDim.x - 1 - blockIdx.x;
   const int hq = blockIdx.y;
   const int b = blockIdx.z;
@@ -764,10 +836,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
-    for (int h = 0; h < 2; ++h) {
-      mbar_init(s_full(h), 1);
-      mbar_init(p_full(h), HALF_THREADS);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(s_free, EW_THREADS);
+    mbar_init(p_full, EW_THREADS);
+    mbar_init(ts_done(0), 1);
+    mbar_init(ts_done(1), 1);
     mbar_init(acc_full, 1);
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
@@ -782,6 +855,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  PROBE(20);
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
@@ -803,76 +877,83 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
-      // Key tiles are processed as two halves of 64 keys, as in the dK/dV kernel: the tensor pipe works on one
-      // half while the element-wise warps of the other are busy.
-      constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BM, BN / 2);
+      // S = Q K^T and dP = dO8 V^T of key tile j, issued as soon as the element-wise threads hold tile j - 1's
+      // scores in registers, so that the next tile's scores are waiting when they are done with the current one.
+      // The dQ products come from another thread (warp 2): a barrier operation costs a thread 100 cycles and more
+      // while shared memory is busy.
+      constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BM, BN);
       const uint32_t s_tmem = tmem_base + B_S_COL;
       const uint32_t dp_tmem = tmem_base + B_DP_COL;
-      bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
       // descriptors as (low word, shared high word), as in the dK/dV kernel
       const uint32_t desc_hi = smem_desc_sw128_hi(1024);
       const uint32_t q_lo = smem_desc_lo(q_smem, 16), do_lo = smem_desc_lo(do_smem, 16);
-      const uint32_t idesc_ts = make_idesc_mx_major(BM, DH, 0, 0, 0, 1);
-      auto k_lo_of = [&](int j) { return smem_desc_lo(stage_smem + (j % B_STAGES) * B_STAGE_BYTES, 16); };
-      // S = Q K^T and dP = dO8 V^T for keys [64 h, 64 h + 64) of tile j (rows 64 h.. of the K and V tiles: +512 in
-      // descriptor units)
-      auto ss_half = [&](int j, int h) {
-        const uint32_t k_lo = k_lo_of(j) + 512 * h;
-        const uint32_t v_lo = k_lo + (TILE_BYTES >> 4);
-#pragma unroll
-        for (int k = 0; k < DH / 32; ++k)
-          mma_f8_ss_w(s_tmem + HALF_COLS * h, q_lo + 2 * k, k_lo + 2 * k, desc_hi, idesc_ss, k != 0);
-#pragma unroll
-        for (int k = 0; k < DH / 32; ++k)
-          mma_f8_ss_w(dp_tmem + HALF_COLS * h, do_lo + 2 * k, v_lo + 2 * k, desc_hi, idesc_ss, k != 0);
-        tc_commit(s_full(h));
-      };
-      // dQ += dS K over the same 64 keys: A = dS codes in the dP columns, B = the K tile read MN-major
-      auto ts_half = [&](int j, int h) {
-        const uint32_t k_lo = k_lo_of(j);
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const uint32_t bb = s_tmem + HALF_COLS * h + 32 * k;  // the block's scale words sit in its own S columns
-          mma_mxf8_ts_w(tmem_base + B_DQ_COL, dp_tmem + HALF_COLS * h + 32 * k, k_lo + 256 * (2 * h + k), desc_hi,
-                        idesc_ts, bb + B_SF_DS, bb + B_SF_UNIT, (j | h | k) != 0);
-        }
-      };
-      ok = ok && mbar_wait(kv_full(0), 0, p.status, WK_ERR_TIMEOUT_LOAD);
-      if (ok) {
-        tc_fence_after();
-        ss_half(0, 0);
-        ss_half(0, 1);
-      }
+      const uint32_t k_lo0 = smem_desc_lo(stage_smem, 16);
+      bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int s = j % B_STAGES;
-        const bool more = j + 1 < n_tiles;
-        if (!mbar_wait(p_full(0), j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
+        if (!mbar_wait(kv_full(s), (j / B_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        PROBE(0);
+        if (j >= 1 && !mbar_wait(s_free, (j - 1) & 1, p.status, WK_ERR_TIMEOUT_P)) break;
+        // The dQ products of tile j - 2 have read their codes: whoever sees this tile's scores may overwrite that
+        // buffer of codes (the element-wise threads do not ask again; they arrived for those products long ago)
+        if (j >= 2 && !mbar_wait(ts_done(j & 1), ((j >> 1) - 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) break;
+        PROBE(1);
         tc_fence_after();
-        ts_half(j, 0);
-        if (more) {
-          if (!mbar_wait(kv_full((j + 1) % B_STAGES), ((j + 1) / B_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
-          tc_fence_after();
-          ss_half(j + 1, 0);
-        }
-        if (!mbar_wait(p_full(1), j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
-        tc_fence_after();
-        ts_half(j, 1);
-        tc_commit(kv_empty(s));
-        if (more) ss_half(j + 1, 1);
-        if (!more) tc_commit(acc_full);
+        const uint32_t k_lo = k_lo0 + s * (B_STAGE_BYTES >> 4);
+        const uint32_t v_lo = k_lo + (TILE_BYTES >> 4);
+#pragma unroll
+        for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(s_tmem, q_lo + 2 * k, k_lo + 2 * k, desc_hi, idesc_ss, k != 0);
+#pragma unroll
+        for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(dp_tmem, do_lo + 2 * k, v_lo + 2 * k, desc_hi, idesc_ss, k != 0);
+        tc_commit(s_full);
+        PROBE(2);
       }
     }
     __syncwarp();
+  } else if (warp == 2) {
+    if (lane == 0 && n_tiles > 0) {
+      // dQ += dS K over tile j, as soon as the tile's codes are written: A = the dS codes, B = the K tile read
+      // MN-major (32 keys per step = 4096 bytes)
+      const uint32_t desc_hi = smem_desc_sw128_hi(1024);
+      const uint32_t idesc_ts = make_idesc_mx_major(BM, DH, 0, 0, 0, 1);
+      const uint32_t k_lo0 = smem_desc_lo(stage_smem, 16);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % B_STAGES;
+        // the tile has landed (the score thread saw that long ago; this thread reads the tile too)
+        if (!mbar_wait(kv_full(s), (j / B_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        PROBE(0);
+        if (!mbar_wait(p_full, j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
+        PROBE(3);
+        tc_fence_after();
+        const uint32_t k_lo = k_lo0 + s * (B_STAGE_BYTES >> 4);
+        const uint32_t codes = tmem_base + B_DSC_COL + 32 * (j & 1), sf = tmem_base + B_SF_COL + 16 * (j & 1);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_mxf8_ts_w(tmem_base + B_DQ_COL, codes + 8 * k, k_lo + 256 * k, desc_hi, idesc_ts, sf + 4 * k,
+                        tmem_base + B_SF_UNIT_COL, (j | k) != 0);
+        tc_commit(ts_done(j & 1));
+        // every product that reads the stage is complete when this fires (the scores were read long ago)
+        tc_commit(kv_empty(s));
+        if (j + 1 == n_tiles) tc_commit(acc_full);
+        PROBE(5);
+        PROBE_COUNT(6);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 3) {
+    // no work: the warp only keeps the element-wise warps on TMEM lane quarter (warp & 3)
   } else {
     const int quad = warp & 3;
-    const int c = (warp - 2) >> 2;  // which block of 32 of the tile's 128 columns this thread handles
-    const int half = c >> 1;        // the half the block is handed over with
+    const int c = (warp - FIRST_EW_WARP) >> 2;  // which block of 32 of the tile's 128 keys this thread handles
     const int r = quad * 32 + lane;
     const int row = m0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     // this thread's block: scores in columns [32 c, 32 c + 32) of both buffers
     const uint32_t s_tmem = tmem_base + lane_addr + B_S_COL + 32 * c;
     const uint32_t dp_tmem = tmem_base + lane_addr + B_DP_COL + 32 * c;
+    const uint32_t dsc_tmem = tmem_base + lane_addr + B_DSC_COL + 8 * c;
+    const uint32_t sf_tmem = tmem_base + lane_addr + B_SF_COL + 4 * c + quad;
+    if (c == 0) tmem_st4(tmem_base + lane_addr + B_SF_UNIT_COL, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
     const int sc = b * p.Hkv + hkv;
     const float sq = p.q_descale[sc], sk = p.k_descale[sc];
     const float beta = p.softmax_scale * sq * sk * LOG2E;
@@ -883,10 +964,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     bool ok = true;
 
     for (int j = 0; j < n_tiles; ++j) {
-      if (!mbar_wait_warp(s_full(half), j & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+      if (!mbar_wait_warp(s_full, j & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
         ok = false;
         break;
       }
+      PROBE(8);
       tc_fence_after();
       const int limit = row_limit - j * BN;  // columns > limit are masked
       // uniform over the CTA: does this tile contain any masked score?
@@ -897,35 +979,49 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tmem_ld32(s_tmem, sraw);
         tmem_ld32(dp_tmem, draw);
         tc_wait_ld();
+        // the scores are in registers: the columns may take the next tile
+        tc_fence_before();
+        mbar_arrive(s_free);
+        PROBE(9);
         uint64_t ds[16];  // dS of this query for 32 keys, as packed pairs
         const uint64_t beta2 = pack_f32x2(beta, beta), nl2 = pack_f32x2(neg_l, neg_l), z2 = pack_f32x2(gsv, gsv),
                        nd2 = pack_f32x2(neg_d, neg_d);
+        // two copies of the loop, with and without the mask, behind one branch per tile
+        auto scores_to_ds = [&](auto masked) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float x0, x1;
           unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sraw[2 * i]), __uint_as_float(sraw[2 * i + 1])), beta2, nl2),
                        x0, x1);
           float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-          if (tile_masked) {
+          if constexpr (decltype(masked)::value) {
             if (c * 32 + 2 * i > limit) p0 = 0.f;
             if (c * 32 + 2 * i + 1 > limit) p1 = 0.f;
           }
           ds[i] = mul_f32x2(pack_f32x2(p0, p1),
                             fma_f32x2(pack_f32x2(__uint_as_float(draw[2 * i]), __uint_as_float(draw[2 * i + 1])), z2, nd2));
         }
+        };
+        if (tile_masked) scores_to_ds(std::true_type{});
+        else scores_to_ds(std::false_type{});
         float inv_d;
         const uint32_t bd = block_scale(absmax_bits(ds), inv_d);
-        quantize_block_to_tmem(ds, dp_tmem, inv_d);
+        PROBE(10);
+        // the products of the tile before the previous one have read this buffer of codes and scale words: the
+        // score thread waited for them before it issued this tile's scores
+        quantize_block_to_tmem(ds, dsc_tmem + 32 * (j & 1), inv_d);
         sf_d = bd;
       }
-      tmem_st1(s_tmem + B_SF_DS + quad, sf_d);
-      tmem_st4(s_tmem + B_SF_UNIT, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+      tmem_st1(sf_tmem + 16 * (j & 1), sf_d);
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(p_full(half));
+      mbar_arrive(p_full);
+      PROBE(12);
+      PROBE_COUNT(15);
     }
 
     if (n_tiles > 0 && ok) ok = mbar_wait_warp(acc_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
+    PROBE(13);
     if (ok) {
       tc_fence_after();
       const float scale = p.softmax_scale * sk;
@@ -956,12 +1052,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
   }
 
+  PROBE(14);
+  PROBE_COUNT(21);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  PROBE_FLUSH(24);
 }
 
 // Rows of `d` bytes under boxes of 128: with head dimension 64 TMA fills the upper half of every row with zeros.
@@ -975,6 +1074,18 @@ int make_map4(CUtensorMap* m, const void* base, int d, int n, int h, int b, cons
 
 }  // namespace
 }  // namespace wk
+
+#ifdef WK_BWD_PROBE
+extern "C" int wk_bwd_probe_read(unsigned long long* out, int clear) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return -2;
+  if (cudaMemcpyFromSymbol(out, wk::g_bwd_probe, 48 * sizeof(unsigned long long)) != cudaSuccess) return -2;
+  if (clear) {
+    unsigned long long zero[48] = {};
+    if (cudaMemcpyToSymbol(wk::g_bwd_probe, zero, sizeof(zero)) != cudaSuccess) return -2;
+  }
+  return 0;
+}
+#endif
 
 extern "C" int64_t wk_attn_bwd_fp8_workspace_bytes(int B, int Hq, int Nq) {
   if (B < 0 || Hq < 0 || Nq < 0) return WK_E_ARG;
