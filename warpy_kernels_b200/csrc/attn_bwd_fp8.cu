@@ -19,13 +19,14 @@
 //  2. attn_bwd_dkdv_kernel: a key block = 128 keys of one (batch, kv head), K and V resident in shared
 //     memory, loop over the group's query heads and query tiles.  The grid has one CTA per key block; the
 //     CTAs that start take over the blocks of those that have not (launch control, common.cuh), with K and V
-//     double-buffered and the next block's first S^T / dP^T under way while dK and dV are stored.  Per tile:
-//       S^T = K Q^T and dP^T = V dO8^T            (tcgen05.mma kind::f8f6f4, into TMEM)
-//       threads (four per key): P^T . g and dS^T as MXFP8 (e4m3 codes back into TMEM, one
-//                              power-of-two scale per key and 32 queries, also into TMEM)
+//     double-buffered and the next block's first scores under way while dK and dV are stored.  Per 64 queries:
+//       S^T = K Q^T and dP^T = V dO8^T            (tcgen05.mma kind::f8f6f4, into one score buffer in TMEM)
+//       threads (four per key): scores into registers (the buffer is free again), then P^T . g and dS^T as
+//                              MXFP8: e4m3 codes and one power-of-two scale per key and 32 queries into TMEM
+//                              columns of their own
 //       dV += (P g)^T dO8 and dK += dS^T Q8       (kind::mxf8f6f4, A from TMEM, B = the same
 //                                                  Q / dO8 tiles read MN-major)
-//     dV and dK stay in TMEM for the whole CTA (4 x 128 columns in use).
+//     dV and dK stay in TMEM for the whole CTA (484 of 512 columns in use).
 //  3. attn_bwd_dq_kernel: CTA = 128 queries of one (batch, query head), loop over key tiles,
 //     recomputes S and dP, dQ += dS K in TMEM.  Recomputing instead of reducing dQ across
 //     key blocks costs two more products but needs no atomics, no fp32 dQ buffer, no
@@ -51,17 +52,34 @@ __device__ unsigned long long g_bwd_probe[48];
 // per-warp accumulators in shared memory (lane 0 only), flushed to the global counters once at the end
 #define PROBE_SMEM __shared__ unsigned long long probe_acc[18][24]
 #define PROBE_DECL long long probe_t = clock64()
+// With -DWK_BWD_TRACE as well, the CTA with grid index (0, 0, 0) also writes the time of every mark (first 256 per warp).
+#ifdef WK_BWD_TRACE
+__device__ unsigned long long g_bwd_trace[2][20][256];
+#define TRACE_VARS(which)                                                                \
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0; \
+  const int trace_which = which;                                                         \
+  int trace_n = 0
+#define TRACE(slot)                                                                      \
+  if (trace_on && trace_n < 256)                                                         \
+  g_bwd_trace[trace_which][threadIdx.x >> 5][trace_n++] =                                \
+      (static_cast<unsigned long long>(slot) << 56) | (static_cast<unsigned long long>(probe_now) & 0xffffffffffffffull)
+#else
+#define TRACE_VARS(which)
+#define TRACE(slot)
+#endif
 #define PROBE(slot)                                                                        \
   do {                                                                                     \
     const long long probe_now = clock64();                                                 \
     if ((threadIdx.x & 31) == 0) probe_acc[threadIdx.x >> 5][slot] += probe_now - probe_t; \
     probe_t = probe_now;                                                                   \
+    TRACE(slot);                                                                           \
   } while (0)
 #define PROBE_COUNT(slot) do { if ((threadIdx.x & 31) == 0) probe_acc[threadIdx.x >> 5][slot] += 1; } while (0)
 #define PROBE_INIT do { if ((threadIdx.x & 31) == 0) for (int i = 0; i < 24; ++i) probe_acc[threadIdx.x >> 5][i] = 0; } while (0)
 #define PROBE_FLUSH(base) do { if ((threadIdx.x & 31) == 0) for (int i = 0; i < 24; ++i) if (probe_acc[threadIdx.x >> 5][i]) atomicAdd(&g_bwd_probe[(base) + i], probe_acc[threadIdx.x >> 5][i]); } while (0)
 #else
 #define PROBE_SMEM
+#define TRACE_VARS(which)
 #define PROBE_DECL
 #define PROBE(slot)
 #define PROBE_COUNT(slot)
@@ -364,6 +382,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int lane = threadIdx.x % 32;
   PROBE_SMEM;
   PROBE_INIT;
+  TRACE_VARS(0);
   const int group = p.Hq / p.Hkv;
   const int shift = p.Nk - p.Nq;
   const int num_m = (p.Nq + BM - 1) / BM;
@@ -817,6 +836,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const int lane = threadIdx.x % 32;
   PROBE_SMEM;
   PROBE_INIT;
+  TRACE_VARS(1);
   PROBE_DECL;
   const int m_blk = gridDim.x - 1 - blockIdx.x;
   const int hq = blockIdx.y;
@@ -1075,6 +1095,16 @@ int make_map4(CUtensorMap* m, const void* base, int d, int n, int h, int b, cons
 }  // namespace
 }  // namespace wk
 
+#ifdef WK_BWD_TRACE
+extern "C" int wk_bwd_trace_read(unsigned long long* out) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return -2;
+  if (cudaMemcpyFromSymbol(out, wk::g_bwd_trace, sizeof(unsigned long long) * 2 * 20 * 256) != cudaSuccess) return -2;
+  unsigned long long* zero = static_cast<unsigned long long*>(calloc(2 * 20 * 256, sizeof(unsigned long long)));
+  cudaMemcpyToSymbol(wk::g_bwd_trace, zero, sizeof(unsigned long long) * 2 * 20 * 256);
+  free(zero);
+  return 0;
+}
+#endif
 #ifdef WK_BWD_PROBE
 extern "C" int wk_bwd_probe_read(unsigned long long* out, int clear) {
   if (cudaDeviceSynchronize() != cudaSuccess) return -2;
