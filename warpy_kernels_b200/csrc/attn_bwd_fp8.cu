@@ -27,9 +27,10 @@
 //       dV += (P g)^T dO8 and dK += dS^T Q8       (kind::mxf8f6f4, A from TMEM, B = the same
 //                                                  Q / dO8 tiles read MN-major)
 //     dV and dK stay in TMEM for the whole CTA (484 of 512 columns in use).
-//  3. attn_bwd_dq_kernel: CTA = 128 queries of one (batch, query head), loop over key tiles,
-//     recomputes S and dP, dQ += dS K in TMEM.  Recomputing instead of reducing dQ across
-//     key blocks costs two more products but needs no atomics, no fp32 dQ buffer, no
+//  3. attn_bwd_dq_kernel: a query block = 128 queries of one (batch, query head), loop over key tiles,
+//     recomputes S and dP, dQ += dS K in TMEM; the grid has one CTA per query block and the CTAs that start
+//     take over the blocks of those that have not, as in the dK/dV kernel.  Recomputing instead of reducing dQ
+//     across key blocks costs two more products but needs no atomics, no fp32 dQ buffer, no
 //     post-pass, and is deterministic (the reference: bwd_sm120.py:742-756 red.global.add /
 //     bwd_common.py:307-403 post kernel).
 //
@@ -800,7 +801,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 // ---------------------------------------------------------------------------
 constexpr int B_STAGES = 4;
 constexpr int B_STAGE_BYTES = 2 * TILE_BYTES;  // K tile, V tile
-constexpr int B_SMEM_BYTES = 2 * TILE_BYTES + B_STAGES * B_STAGE_BYTES + 1024 + 256;
+constexpr int B_SMEM_BYTES = 4 * TILE_BYTES + B_STAGES * B_STAGE_BYTES + 1024 + 512;
 static_assert(B_SMEM_BYTES > 120 * 1024 && B_SMEM_BYTES <= 227 * 1024, "one CTA per SM");
 // TMEM columns: the scores of a whole key tile, dQ, and apart from the scores the dS codes and their scale words,
 // twice each (tiles alternate), so that the score columns are free for the next tile's products as soon as the
@@ -818,19 +819,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                    const __grid_constant__ BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t q_smem = smem_base;
-  const uint32_t do_smem = q_smem + TILE_BYTES;
-  const uint32_t stage_smem = do_smem + TILE_BYTES;
+  // Q and dO8 of a query block: two buffers, the blocks of the CTA's list alternate between them
+  auto q_smem = [&](int qb) { return smem_base + qb * 2 * TILE_BYTES; };
+  auto do_smem = [&](int qb) { return smem_base + qb * 2 * TILE_BYTES + TILE_BYTES; };
+  const uint32_t stage_smem = smem_base + 4 * TILE_BYTES;
   const uint32_t bar_base = stage_smem + B_STAGES * B_STAGE_BYTES;
-  const uint32_t q_full = bar_base;
-  auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bar_base + 8u * (1 + B_STAGES + s); };
-  const uint32_t s_full = bar_base + 8u * (1 + 2 * B_STAGES);  // S and dP of a tile are in TMEM
+  auto q_full = [&](int qb) { return bar_base + 8u * qb; };
+  auto q_empty = [&](int qb) { return bar_base + 8u * (2 + qb); };  // every product of the block has read Q and dO8
+  auto kv_full = [&](int s) { return bar_base + 8u * (4 + s); };
+  auto kv_empty = [&](int s) { return bar_base + 8u * (4 + B_STAGES + s); };
+  const uint32_t s_full = bar_base + 8u * (4 + 2 * B_STAGES);  // S and dP of a tile are in TMEM
   const uint32_t s_free = s_full + 8;                          // ... and now in the element-wise threads' registers
   const uint32_t p_full = s_full + 16;                         // the tile's dS codes and scales are in TMEM
   auto ts_done = [&](int i) { return s_full + 24 + 8u * i; };  // ... and the dQ products have read them (buffer i)
-  const uint32_t acc_full = s_full + 40;
-  const uint32_t tmem_slot = acc_full + 8;
+  const uint32_t acc_full = s_full + 40;                       // dQ of the block is complete
+  const uint32_t acc_free = s_full + 48;                       // and every element-wise thread has read its part
+  auto sched_full = [&](int i) { return acc_free + 8u * (1 + i); };                  // answer i has landed
+  auto sched_empty = [&](int i) { return acc_free + 8u * (1 + SCHED_SLOTS + i); };  // and everybody has read it
+  const uint32_t tmem_slot = acc_free + 8u * (1 + 2 * SCHED_SLOTS);
+  auto sched_resp = [&](int i) { return acc_free + 8u * (4 + 2 * SCHED_SLOTS) + 16u * i; };  // 16-byte answers, 16-byte aligned
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -838,20 +845,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   PROBE_INIT;
   TRACE_VARS(1);
   PROBE_DECL;
-  const int m_blk = gridDim.x - 1 - blockIdx.x;
-  const int hq = blockIdx.y;
-  const int b = blockIdx.z;
-  const int hkv = hq / (p.Hq / p.Hkv);
-  const int m0 = m_blk * BM;
   const int shift = p.Nk - p.Nq;
-  int n_tiles = (p.Nk + BN - 1) / BN;
-  if (p.causal) {
-    const int last_key = min(m0 + BM, p.Nq) - 1 + shift;
-    n_tiles = last_key < 0 ? 0 : min(n_tiles, last_key / BN + 1);
-  }
+  const int group = p.Hq / p.Hkv;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    for (int qb = 0; qb < 2; ++qb) {
+      mbar_init(q_full(qb), 1);
+      mbar_init(q_empty(qb), 1);
+    }
     for (int s = 0; s < B_STAGES; ++s) {
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
@@ -862,6 +863,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     mbar_init(ts_done(0), 1);
     mbar_init(ts_done(1), 1);
     mbar_init(acc_full, 1);
+    mbar_init(acc_free, EW_THREADS);
+    for (int i = 0; i < SCHED_SLOTS; ++i) {
+      mbar_init(sched_full(i), 1);
+      mbar_init(sched_empty(i), 3 + EW_THREADS);  // the TMA thread, two MMA threads, the element-wise threads
+    }
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
     prefetch_tmap(&tmap_k);
@@ -879,84 +885,189 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
+  // The CTA's list of query blocks: its own grid index first, then the indices of CTAs that have not started, handed
+  // out by the launch control (common.cuh) one at a time, in launch order (the blocks with the most key tiles
+  // first).  Tiles and blocks are counted through the CTA's whole life; every barrier parity below derives from
+  // those running counts.
+  struct QueryBlock {
+    int m0, hq, b, hkv, n_tiles;
+  } blk;
+  auto set_block = [&](uint32_t x, uint32_t y, uint32_t z) {
+    blk.m0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(x)) * BM;
+    blk.hq = y;
+    blk.b = z;
+    blk.hkv = blk.hq / group;
+    int n = (p.Nk + BN - 1) / BN;
+    if (p.causal) {
+      const int last_key = min(blk.m0 + BM, p.Nq) - 1 + shift;
+      n = last_key < 0 ? 0 : min(n, last_key / BN + 1);
+    }
+    blk.n_tiles = n;
+  };
+  set_block(blockIdx.x, blockIdx.y, blockIdx.z);
+  bool ok = true;
+  uint32_t n_answers = 0;  // answers read so far
+  // Reads the next answer of the launch control: false if no block was left (or the wait gave up: ok is false then).
+  auto next_block = [&]() {
+    const int slot = n_answers % SCHED_SLOTS;
+    if (!mbar_wait(sched_full(slot), (n_answers / SCHED_SLOTS) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) {
+      ok = false;
+      return false;
+    }
+    uint32_t x, y, z;
+    const bool got = launch_control_answer(sched_resp(slot), x, y, z);
+    // the slot's next answer is written through the async proxy: order this read before it
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_arrive(sched_empty(slot));
+    ++n_answers;
+    if (got) set_block(x, y, z);
+    return got;
+  };
+
   if (warp == 0) {
-    if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(q_full, 2 * TILE_BYTES);
-      tma_load_4d(q_smem, &tmap_q, q_full, 0, m0, hq, b);
-      tma_load_4d(do_smem, &tmap_do, q_full, 0, m0, hq, b);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % B_STAGES;
-        const uint32_t ph = (j / B_STAGES) & 1;
-        if (!mbar_wait(kv_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
-        const uint32_t base = stage_smem + s * B_STAGE_BYTES;
-        mbar_expect_tx(kv_full(s), B_STAGE_BYTES);
-        tma_load_4d(base, &tmap_k, kv_full(s), 0, j * BN, hkv, b);
-        tma_load_4d(base + TILE_BYTES, &tmap_v, kv_full(s), 0, j * BN, hkv, b);
+    if (lane == 0) {
+      int ci = -1;      // blocks with work so far
+      uint32_t jt = 0;  // tiles so far
+      for (;;) {
+        if (blk.n_tiles > 0) {
+          ++ci;
+          const int qb = ci & 1;
+          // the products of the block before the previous one have read this pair of buffers
+          if (ci >= 2 && !mbar_wait(q_empty(qb), ((ci >> 1) - 1) & 1, p.status, WK_ERR_TIMEOUT_EMPTY)) break;
+          mbar_expect_tx(q_full(qb), 2 * TILE_BYTES);
+          tma_load_4d(q_smem(qb), &tmap_q, q_full(qb), 0, blk.m0, blk.hq, blk.b);
+          tma_load_4d(do_smem(qb), &tmap_do, q_full(qb), 0, blk.m0, blk.hq, blk.b);
+          for (int j = 0; j < blk.n_tiles; ++j, ++jt) {
+            const int s = jt % B_STAGES;
+            const uint32_t ph = (jt / B_STAGES) & 1;
+            if (!mbar_wait(kv_empty(s), ph ^ 1, p.status, WK_ERR_TIMEOUT_EMPTY)) {
+              ok = false;
+              break;
+            }
+            const uint32_t base = stage_smem + s * B_STAGE_BYTES;
+            mbar_expect_tx(kv_full(s), B_STAGE_BYTES);
+            tma_load_4d(base, &tmap_k, kv_full(s), 0, j * BN, blk.hkv, blk.b);
+            tma_load_4d(base + TILE_BYTES, &tmap_v, kv_full(s), 0, j * BN, blk.hkv, blk.b);
+          }
+          if (!ok) break;
+        }
+        // this block's loads are on their way: ask for another block
+        const int slot = n_answers % SCHED_SLOTS;
+        if (n_answers >= SCHED_SLOTS &&
+            !mbar_wait(sched_empty(slot), ((n_answers / SCHED_SLOTS) - 1) & 1, p.status, WK_ERR_TIMEOUT_EMPTY))
+          break;
+        mbar_expect_tx(sched_full(slot), 16);
+        launch_control_try_cancel(sched_resp(slot), sched_full(slot));
+        if (!next_block()) break;
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0 && n_tiles > 0) {
-      // S = Q K^T and dP = dO8 V^T of key tile j, issued as soon as the element-wise threads hold tile j - 1's
-      // scores in registers, so that the next tile's scores are waiting when they are done with the current one.
-      // The dQ products come from another thread (warp 2): a barrier operation costs a thread 100 cycles and more
-      // while shared memory is busy.
+    if (lane == 0) {
+      // S = Q K^T and dP = dO8 V^T of a key tile, issued as soon as the element-wise threads hold the tile before
+      // it in registers (across query blocks too), so that the next tile's scores are waiting when they are done
+      // with the current one.  The dQ products come from another thread (warp 2): a thread that waits, issues and
+      // commits for both is the bottleneck.
       constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BM, BN);
       const uint32_t s_tmem = tmem_base + B_S_COL;
       const uint32_t dp_tmem = tmem_base + B_DP_COL;
       // descriptors as (low word, shared high word), as in the dK/dV kernel
       const uint32_t desc_hi = smem_desc_sw128_hi(1024);
-      const uint32_t q_lo = smem_desc_lo(q_smem, 16), do_lo = smem_desc_lo(do_smem, 16);
+      const uint32_t q_lo0 = smem_desc_lo(q_smem(0), 16), q_lo1 = smem_desc_lo(q_smem(1), 16);
       const uint32_t k_lo0 = smem_desc_lo(stage_smem, 16);
-      bool ok = mbar_wait(q_full, 0, p.status, WK_ERR_TIMEOUT_LOAD);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        const int s = j % B_STAGES;
-        if (!mbar_wait(kv_full(s), (j / B_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
-        PROBE(0);
-        if (j >= 1 && !mbar_wait(s_free, (j - 1) & 1, p.status, WK_ERR_TIMEOUT_P)) break;
-        // The dQ products of tile j - 2 have read their codes: whoever sees this tile's scores may overwrite that
-        // buffer of codes (the element-wise threads do not ask again; they arrived for those products long ago)
-        if (j >= 2 && !mbar_wait(ts_done(j & 1), ((j >> 1) - 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) break;
-        PROBE(1);
-        tc_fence_after();
-        const uint32_t k_lo = k_lo0 + s * (B_STAGE_BYTES >> 4);
-        const uint32_t v_lo = k_lo + (TILE_BYTES >> 4);
+      bool have = blk.n_tiles > 0;
+      while (ok && !have && next_block()) have = blk.n_tiles > 0;
+      int ci = 0;
+      uint32_t jt = 0;
+      while (ok && have) {
+        const int qb = ci & 1, n_tiles = blk.n_tiles;
+        const uint32_t q_lo = qb ? q_lo1 : q_lo0, do_lo = q_lo + (TILE_BYTES >> 4);
+        if (!mbar_wait(q_full(qb), (ci >> 1) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
+        for (int j = 0; j < n_tiles; ++j, ++jt) {
+          const int s = jt % B_STAGES;
+          if (!mbar_wait(kv_full(s), (jt / B_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) {
+            ok = false;
+            break;
+          }
+          PROBE(0);
+          if (jt >= 1 && !mbar_wait(s_free, (jt - 1) & 1, p.status, WK_ERR_TIMEOUT_P)) {
+            ok = false;
+            break;
+          }
+          // The dQ products of the tile before the previous one have read their codes: whoever sees this tile's
+          // scores may overwrite that buffer of codes (the element-wise threads do not ask again)
+          if (jt >= 2 && !mbar_wait(ts_done(jt & 1), ((jt >> 1) - 1) & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          PROBE(1);
+          tc_fence_after();
+          const uint32_t k_lo = k_lo0 + s * (B_STAGE_BYTES >> 4);
+          const uint32_t v_lo = k_lo + (TILE_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(s_tmem, q_lo + 2 * k, k_lo + 2 * k, desc_hi, idesc_ss, k != 0);
+          for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(s_tmem, q_lo + 2 * k, k_lo + 2 * k, desc_hi, idesc_ss, k != 0);
 #pragma unroll
-        for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(dp_tmem, do_lo + 2 * k, v_lo + 2 * k, desc_hi, idesc_ss, k != 0);
-        tc_commit(s_full);
-        PROBE(2);
+          for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(dp_tmem, do_lo + 2 * k, v_lo + 2 * k, desc_hi, idesc_ss, k != 0);
+          tc_commit(s_full);
+          PROBE(2);
+        }
+        if (!ok) break;
+        ++ci;
+        have = false;
+        while (ok && !have && next_block()) have = blk.n_tiles > 0;
       }
     }
     __syncwarp();
   } else if (warp == 2) {
-    if (lane == 0 && n_tiles > 0) {
-      // dQ += dS K over tile j, as soon as the tile's codes are written: A = the dS codes, B = the K tile read
+    if (lane == 0) {
+      // dQ += dS K over a tile, as soon as the tile's codes are written: A = the dS codes, B = the K tile read
       // MN-major (32 keys per step = 4096 bytes)
       const uint32_t desc_hi = smem_desc_sw128_hi(1024);
       const uint32_t idesc_ts = make_idesc_mx_major(BM, DH, 0, 0, 0, 1);
       const uint32_t k_lo0 = smem_desc_lo(stage_smem, 16);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % B_STAGES;
-        // the tile has landed (the score thread saw that long ago; this thread reads the tile too)
-        if (!mbar_wait(kv_full(s), (j / B_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
-        PROBE(0);
-        if (!mbar_wait(p_full, j & 1, p.status, WK_ERR_TIMEOUT_P)) break;
-        PROBE(3);
-        tc_fence_after();
-        const uint32_t k_lo = k_lo0 + s * (B_STAGE_BYTES >> 4);
-        const uint32_t codes = tmem_base + B_DSC_COL + 32 * (j & 1), sf = tmem_base + B_SF_COL + 16 * (j & 1);
+      bool have = blk.n_tiles > 0;
+      while (ok && !have && next_block()) have = blk.n_tiles > 0;
+      int ci = 0;
+      uint32_t jt = 0;
+      while (ok && have) {
+        const int qb = ci & 1, n_tiles = blk.n_tiles;
+        for (int j = 0; j < n_tiles; ++j, ++jt) {
+          const int s = jt % B_STAGES;
+          // the tile has landed (the score thread saw that long ago; this thread reads the tile too)
+          if (!mbar_wait(kv_full(s), (jt / B_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) {
+            ok = false;
+            break;
+          }
+          PROBE(17);
+          if (!mbar_wait(p_full, jt & 1, p.status, WK_ERR_TIMEOUT_P)) {
+            ok = false;
+            break;
+          }
+          PROBE(3);
+          // the element-wise threads have read the previous block's dQ
+          if (j == 0 && ci >= 1 && !mbar_wait(acc_free, (ci - 1) & 1, p.status, WK_ERR_TIMEOUT_TMEM)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t k_lo = k_lo0 + s * (B_STAGE_BYTES >> 4);
+          const uint32_t codes = tmem_base + B_DSC_COL + 32 * (jt & 1), sf = tmem_base + B_SF_COL + 16 * (jt & 1);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_mxf8_ts_w(tmem_base + B_DQ_COL, codes + 8 * k, k_lo + 256 * k, desc_hi, idesc_ts, sf + 4 * k,
-                        tmem_base + B_SF_UNIT_COL, (j | k) != 0);
-        tc_commit(ts_done(j & 1));
-        // every product that reads the stage is complete when this fires (the scores were read long ago)
-        tc_commit(kv_empty(s));
-        if (j + 1 == n_tiles) tc_commit(acc_full);
-        PROBE(5);
-        PROBE_COUNT(6);
+          for (int k = 0; k < 4; ++k)
+            mma_mxf8_ts_w(tmem_base + B_DQ_COL, codes + 8 * k, k_lo + 256 * k, desc_hi, idesc_ts, sf + 4 * k,
+                          tmem_base + B_SF_UNIT_COL, (j | k) != 0);
+          tc_commit(ts_done(jt & 1));
+          // every product that reads the stage is complete when this fires (the scores were read long ago)
+          tc_commit(kv_empty(s));
+          PROBE(5);
+          PROBE_COUNT(6);
+        }
+        if (!ok) break;
+        tc_commit(acc_full);
+        tc_commit(q_empty(qb));  // and every product that reads the block's Q and dO8
+        ++ci;
+        have = false;
+        while (ok && !have && next_block()) have = blk.n_tiles > 0;
       }
     }
     __syncwarp();
@@ -966,7 +1077,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int quad = warp & 3;
     const int c = (warp - FIRST_EW_WARP) >> 2;  // which block of 32 of the tile's 128 keys this thread handles
     const int r = quad * 32 + lane;
-    const int row = m0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     // this thread's block: scores in columns [32 c, 32 c + 32) of both buffers
     const uint32_t s_tmem = tmem_base + lane_addr + B_S_COL + 32 * c;
@@ -974,17 +1084,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const uint32_t dsc_tmem = tmem_base + lane_addr + B_DSC_COL + 8 * c;
     const uint32_t sf_tmem = tmem_base + lane_addr + B_SF_COL + 4 * c + quad;
     if (c == 0) tmem_st4(tmem_base + lane_addr + B_SF_UNIT_COL, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-    const int sc = b * p.Hkv + hkv;
+    int ci = -1;      // query blocks with work so far
+    uint32_t jt = 0;  // tiles so far
+
+    for (;;) {
+    const int m0 = blk.m0, n_tiles = blk.n_tiles, hq = blk.hq, b = blk.b;
+    const int row = m0 + r;
+    const int sc = b * p.Hkv + blk.hkv;
     const float sq = p.q_descale[sc], sk = p.k_descale[sc];
     const float beta = p.softmax_scale * sq * sk * LOG2E;
     const float* rec = p.qstat + ((static_cast<int64_t>(b) * p.Hq + hq) * p.nq_pad + m0) * 2 + r;
     const float neg_l = rec[0], neg_d = rec[128];  // log2(g) - L and -sum(dO8 . O) of this query
     const float gsv = p.v_descale[sc];  // dP = sv . dP8 in units of g
     const int row_limit = min(p.causal ? row + shift : p.Nk - 1, p.Nk - 1);
-    bool ok = true;
+    if (n_tiles > 0) ++ci;
 
-    for (int j = 0; j < n_tiles; ++j) {
-      if (!mbar_wait_warp(s_full, j & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
+    for (int j = 0; j < n_tiles; ++j, ++jt) {
+      if (!mbar_wait_warp(s_full, jt & 1, p.status, WK_ERR_TIMEOUT_MMA)) {
         ok = false;
         break;
       }
@@ -1029,10 +1145,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         PROBE(10);
         // the products of the tile before the previous one have read this buffer of codes and scale words: the
         // score thread waited for them before it issued this tile's scores
-        quantize_block_to_tmem(ds, dsc_tmem + 32 * (j & 1), inv_d);
+        quantize_block_to_tmem(ds, dsc_tmem + 32 * (jt & 1), inv_d);
         sf_d = bd;
       }
-      tmem_st1(sf_tmem + 16 * (j & 1), sf_d);
+      tmem_st1(sf_tmem + 16 * (jt & 1), sf_d);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(p_full);
@@ -1040,7 +1156,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       PROBE_COUNT(15);
     }
 
-    if (n_tiles > 0 && ok) ok = mbar_wait_warp(acc_full, 0, p.status, WK_ERR_TIMEOUT_MMA);
+    if (n_tiles > 0 && ok) ok = mbar_wait_warp(acc_full, ci & 1, p.status, WK_ERR_TIMEOUT_MMA);
     PROBE(13);
     if (ok) {
       tc_fence_after();
@@ -1049,9 +1165,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 #pragma unroll 1
       {
         uint32_t v[32];
-        if (n_tiles > 0) {
+        if (n_tiles > 0) {  // uniform: TMEM loads are warp-wide
           tmem_ld32(tmem_base + lane_addr + B_DQ_COL + c * 32, v);
           tc_wait_ld();
+          // dQ is in registers: the next block's first product may overwrite it
+          tc_fence_before();
+          mbar_arrive(acc_free);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0;
@@ -1070,10 +1189,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
       }
     }
+    PROBE(14);
+    PROBE_COUNT(21);
+    if (!ok || !next_block()) break;
+    }
   }
 
-  PROBE(14);
-  PROBE_COUNT(21);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
