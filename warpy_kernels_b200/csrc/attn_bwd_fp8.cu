@@ -391,14 +391,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   if (threadIdx.x == 0) {
     for (int kb = 0; kb < 2; ++kb) {
       mbar_init(kv_full(kb), 1);
-      mbar_init(kv_empty(kb), 1);
+      mbar_init(kv_empty(kb), 2);  // both score threads
     }
     for (int s = 0; s < A_STAGES; ++s) {
       mbar_init(q_full(s), 1);
       mbar_init(q_empty(s), 1);
     }
     for (int h = 0; h < 2; ++h) {
-      mbar_init(s_full(h), 1);
+      mbar_init(s_full(h), 2);  // S^T and dP^T come from two threads
       mbar_init(s_free(h), HALF_THREADS);
       mbar_init(p_full(h), HALF_THREADS);
       mbar_init(ts_done(h), 1);
@@ -506,22 +506,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   } else if (warp == 1 || warp == 2) {
     if (lane == 0) {
       // The CTA's work is a sequence of units: 64 queries (h = 0, 1) of a query tile of a key block, block after
-      // block.  Unit n = 2 g + h (g: tiles so far) goes to element-wise group h.  This thread issues the scores of
-      // the units with its h (warp 1: h = 0, warp 2: h = 1) into the one score buffer, each as soon as the other
-      // group holds the unit before it in registers; a third thread (warp 3) issues the sums.  Three issuing
-      // threads because a barrier operation costs a thread 100 cycles and more while shared memory is busy: one
-      // thread cannot wait, issue and commit for every unit in the time the element-wise threads need for it.
-      const int h = warp - 1;
+      // block.  Unit n = 2 g + h (g: tiles so far) goes to element-wise group h.  The scores of a unit go into the
+      // one score buffer as soon as the other group holds the unit before it in registers: S^T = K Q^T from this
+      // thread in warp 1, dP^T = V dO8^T from the one in warp 2, side by side (the time from the buffer's release
+      // to its next scores is on every unit's critical path, and one thread needs ~90 cycles per MMA it issues
+      // here); a third thread (warp 3) issues the sums.
+      const int which = warp - 1;  // 0: S^T, 1: dP^T
       constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BN, BM / 2);
-      const uint32_t st_tmem = tmem_base + A_ST_COL;
-      const uint32_t dpt_tmem = tmem_base + A_DPT_COL;
+      const uint32_t d_tmem = tmem_base + (which == 0 ? A_ST_COL : A_DPT_COL);
       // Descriptors as (low word, shared high word): the tiles' low words are set up once, a K step or a row block
       // is one 32-bit add.
       const uint32_t desc_hi = smem_desc_sw128_hi(1024);
-      const uint32_t k_lo0 = smem_desc_lo(k_smem(0), 16), k_lo1 = smem_desc_lo(k_smem(1), 16);
-      const uint32_t v_lo0 = smem_desc_lo(v_smem(0), 16), v_lo1 = smem_desc_lo(v_smem(1), 16);
-      // rows 64 h.. of the Q and dO8 tiles are 64 x 128 bytes further on (+512 in descriptor units)
-      const uint32_t q_lo0 = smem_desc_lo(stage_smem, 16) + 512 * h;
+      const uint32_t a_lo0 = smem_desc_lo(which == 0 ? k_smem(0) : v_smem(0), 16);
+      const uint32_t a_lo1 = smem_desc_lo(which == 0 ? k_smem(1) : v_smem(1), 16);
+      // B: the Q tile of the stage for S^T, the dO8 tile behind it for dP^T
+      const uint32_t b_lo0 = smem_desc_lo(stage_smem, 16) + (which == 0 ? 0 : (TILE_BYTES >> 4));
       bool have = blk.n_iter > 0;
       while (ok && !have && next_block()) have = blk.n_iter > 0;
       int ci = 0;      // blocks with work so far
@@ -529,38 +528,37 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       PROBE_DECL;
       while (ok && have) {
         const int kb = ci & 1, n_iter = blk.n_iter;
-        const uint32_t k_lo = kb ? k_lo1 : k_lo0, v_lo = kb ? v_lo1 : v_lo0;
+        const uint32_t a_lo = kb ? a_lo1 : a_lo0;
         if (!mbar_wait(kv_full(kb), (ci >> 1) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
-        for (int it = 0; it < n_iter; ++it, ++g) {
+        for (int it = 0; ok && it < n_iter; ++it, ++g) {
           const int s = g % A_STAGES;
           if (!mbar_wait(q_full(s), (g / A_STAGES) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) {
             ok = false;
             break;
           }
           PROBE(0);
-          // the unit before this one (the other group's) has left the score buffer
-          const uint32_t n = 2 * g + h;
-          if (n >= 1 && !mbar_wait(s_free(h ^ 1), ((n - 1) >> 1) & 1, p.status, WK_ERR_TIMEOUT_P)) {
-            ok = false;
-            break;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            // the unit before this one (the other group's) has left the score buffer
+            const uint32_t n = 2 * g + h;
+            if (n >= 1 && !mbar_wait(s_free(h ^ 1), ((n - 1) >> 1) & 1, p.status, WK_ERR_TIMEOUT_P)) {
+              ok = false;
+              break;
+            }
+            PROBE(1);
+            tc_fence_after();
+            // queries [64 h, 64 h + 64) of the tile: rows 64 h.. of the Q and dO8 tiles are 64 x 128 bytes further on
+            // (+512 in descriptor units)
+            const uint32_t b_lo = b_lo0 + s * (A_STAGE_BYTES >> 4) + 512 * h;
+#pragma unroll
+            for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(d_tmem, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc_ss, k != 0);
+            tc_commit(s_full(h));
+            PROBE(2);
+            PROBE_COUNT(6);
           }
-          PROBE(1);
-          tc_fence_after();
-          // S^T = K Q^T and dP^T = V dO8^T for queries [64 h, 64 h + 64) of the tile
-          const uint32_t q_lo = q_lo0 + s * (A_STAGE_BYTES >> 4);
-          const uint32_t do_lo = q_lo + (TILE_BYTES >> 4);
-#pragma unroll
-          for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(st_tmem, k_lo + 2 * k, q_lo + 2 * k, desc_hi, idesc_ss, k != 0);
-#pragma unroll
-          for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(dpt_tmem, v_lo + 2 * k, do_lo + 2 * k, desc_hi, idesc_ss, k != 0);
-          tc_commit(s_full(h));
-          PROBE(2);
-          PROBE_COUNT(6);
         }
         if (!ok) break;
-        // Every S product of the block has been issued (this thread's are the last ones: the other thread's
-        // results were read before this thread's last unit could go into the buffer)
-        if (h == 1) tc_commit(kv_empty(kb));
+        tc_commit(kv_empty(kb));  // this thread's products of the block have all been issued
         ++ci;
         have = false;
         while (ok && !have && next_block()) have = blk.n_iter > 0;
