@@ -855,7 +855,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
-    mbar_init(s_full, 1);
+    mbar_init(s_full, 2);  // S and dP come from two threads
     mbar_init(s_free, EW_THREADS);
     mbar_init(p_full, EW_THREADS);
     mbar_init(ts_done(0), 1);
@@ -864,7 +864,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     mbar_init(acc_free, EW_THREADS);
     for (int i = 0; i < SCHED_SLOTS; ++i) {
       mbar_init(sched_full(i), 1);
-      mbar_init(sched_empty(i), 3 + EW_THREADS);  // the TMA thread, two MMA threads, the element-wise threads
+      mbar_init(sched_empty(i), 4 + EW_THREADS);  // the TMA thread, three MMA threads, the element-wise threads
     }
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
@@ -960,26 +960,29 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 3) {
     if (lane == 0) {
-      // S = Q K^T and dP = dO8 V^T of a key tile, issued as soon as the element-wise threads hold the tile before
-      // it in registers (across query blocks too), so that the next tile's scores are waiting when they are done
-      // with the current one.  The dQ products come from another thread (warp 2): a thread that waits, issues and
-      // commits for both is the bottleneck.
+      // The scores of a key tile, issued as soon as the element-wise threads hold the tile before it in registers
+      // (across query blocks too), so that the next tile's scores are waiting when they are done with the current
+      // one: S = Q K^T from this thread in warp 1, dP = dO8 V^T from the one in warp 3, side by side (the time from
+      // the columns' release to the next scores is on the critical path, and one thread needs ~90 cycles per MMA
+      // it issues here).  The dQ products come from a third thread (warp 2).
+      const int which = warp == 1 ? 0 : 1;  // 0: S, 1: dP
       constexpr uint32_t idesc_ss = make_idesc(0, 0, 0, 0, BM, BN);
-      const uint32_t s_tmem = tmem_base + B_S_COL;
-      const uint32_t dp_tmem = tmem_base + B_DP_COL;
+      const uint32_t d_tmem = tmem_base + (which == 0 ? B_S_COL : B_DP_COL);
       // descriptors as (low word, shared high word), as in the dK/dV kernel
       const uint32_t desc_hi = smem_desc_sw128_hi(1024);
-      const uint32_t q_lo0 = smem_desc_lo(q_smem(0), 16), q_lo1 = smem_desc_lo(q_smem(1), 16);
-      const uint32_t k_lo0 = smem_desc_lo(stage_smem, 16);
+      const uint32_t a_lo0 = smem_desc_lo(which == 0 ? q_smem(0) : do_smem(0), 16);
+      const uint32_t a_lo1 = smem_desc_lo(which == 0 ? q_smem(1) : do_smem(1), 16);
+      // B: the K tile of the stage for S, the V tile behind it for dP
+      const uint32_t b_lo0 = smem_desc_lo(stage_smem, 16) + (which == 0 ? 0 : (TILE_BYTES >> 4));
       bool have = blk.n_tiles > 0;
       while (ok && !have && next_block()) have = blk.n_tiles > 0;
       int ci = 0;
       uint32_t jt = 0;
       while (ok && have) {
         const int qb = ci & 1, n_tiles = blk.n_tiles;
-        const uint32_t q_lo = qb ? q_lo1 : q_lo0, do_lo = q_lo + (TILE_BYTES >> 4);
+        const uint32_t a_lo = qb ? a_lo1 : a_lo0;
         if (!mbar_wait(q_full(qb), (ci >> 1) & 1, p.status, WK_ERR_TIMEOUT_LOAD)) break;
         for (int j = 0; j < n_tiles; ++j, ++jt) {
           const int s = jt % B_STAGES;
@@ -1000,12 +1003,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           }
           PROBE(1);
           tc_fence_after();
-          const uint32_t k_lo = k_lo0 + s * (B_STAGE_BYTES >> 4);
-          const uint32_t v_lo = k_lo + (TILE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + s * (B_STAGE_BYTES >> 4);
 #pragma unroll
-          for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(s_tmem, q_lo + 2 * k, k_lo + 2 * k, desc_hi, idesc_ss, k != 0);
-#pragma unroll
-          for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(dp_tmem, do_lo + 2 * k, v_lo + 2 * k, desc_hi, idesc_ss, k != 0);
+          for (int k = 0; k < DH / 32; ++k) mma_f8_ss_w(d_tmem, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc_ss, k != 0);
           tc_commit(s_full);
           PROBE(2);
         }
@@ -1069,8 +1069,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       }
     }
     __syncwarp();
-  } else if (warp == 3) {
-    // no work: the warp only keeps the element-wise warps on TMEM lane quarter (warp & 3)
   } else {
     const int quad = warp & 3;
     const int c = (warp - FIRST_EW_WARP) >> 2;  // which block of 32 of the tile's 128 keys this thread handles
